@@ -1,0 +1,284 @@
+"""TEST INFRASTRUCTURE ONLY: numpy front end of the C oracle (``oracle.c``).
+
+Every wrapper takes/returns numpy arrays (int64 / int32 / float32, C
+contiguous) and mirrors one reference interface; see ``oracle.c`` for the
+reference file:line each function follows.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SRC = os.path.join(HERE, "oracle.c")
+LIB = os.path.join(HERE, "liboracle.so")
+
+_lib = None
+
+I64P = C.POINTER(C.c_int64)
+I32P = C.POINTER(C.c_int32)
+F32P = C.POINTER(C.c_float)
+
+
+def build(force: bool = False) -> str:
+    if force or not os.path.exists(LIB) or os.path.getmtime(LIB) < os.path.getmtime(SRC):
+        subprocess.check_call(["gcc", "-O2", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC", SRC, "-o", LIB, "-lm"])
+    return LIB
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        for name in ("orc_mapper_new", "orc_swap_new", "orc_filter_new"):
+            getattr(_lib, name).restype = C.c_void_p
+        for name in ("orc_unique_sorted", "orc_mapper_size", "orc_mapper_ids2indices_unique", "orc_bucketize",
+                     "orc_swap_occupied", "orc_filter_num_evict", "orc_filter_count_of"):
+            getattr(_lib, name).restype = C.c_int64
+    return _lib
+
+
+def _i64(a):
+    a = np.ascontiguousarray(a, dtype=np.int64)
+    return a
+
+
+def p64(a):
+    return a.ctypes.data_as(I64P) if a is not None else None
+
+
+def p32(a):
+    return a.ctypes.data_as(I32P) if a is not None else None
+
+
+def pf(a):
+    return a.ctypes.data_as(F32P) if a is not None else None
+
+
+# ----------------------------------------------------------------------------- A1
+def unique_sorted(ids):
+    ids = _i64(ids)
+    n = ids.size
+    uniq = np.empty(max(n, 1), np.int64)
+    inv = np.empty(max(n, 1), np.int64)
+    u = lib().orc_unique_sorted(p64(ids), C.c_int64(n), p64(uniq), p64(inv))
+    return uniq[:u].copy(), inv[:n].copy()
+
+
+# ----------------------------------------------------------------------------- A2
+class IdsMapper:
+    """Restatement of ``hybrid::IdsMapper`` (same method names as the torch class)."""
+
+    def __init__(self, init_max_index: int, only_device_mem: bool = True):
+        self._h = C.c_void_p(lib().orc_mapper_new(C.c_int64(init_max_index), C.c_int(int(only_device_mem))))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().orc_mapper_free(self._h)
+            self._h = None
+
+    def size(self) -> int:
+        return lib().orc_mapper_size(self._h)
+
+    def ids2indices_unique(self, ids):
+        ids = _i64(ids)
+        n = ids.size
+        hi = np.empty(max(n, 1), np.int64)
+        uniq = np.empty(max(n, 1), np.int64)
+        inv = np.empty(max(n, 1), np.int64)
+        u = lib().orc_mapper_ids2indices_unique(self._h, p64(ids), C.c_int64(n), p64(hi), p64(uniq), p64(inv))
+        if u < 0:
+            raise RuntimeError({1: "Invalid key value", 2: "Ids map reached maxIndex"}.get(-u, "error"))
+        return hi[:n].copy(), uniq[:u].copy(), inv[:n].copy()
+
+    def ids2indices_unique_out(self, ids, hash_indices, offset, unique, unique_ids, unique_inverse, unique_offset,
+                               table_id: int):
+        rc = lib().orc_mapper_unique_out(self._h, p64(ids), p64(hash_indices), p64(offset), p64(unique),
+                                         p64(unique_ids), p64(unique_inverse), p64(unique_offset),
+                                         C.c_int64(table_id))
+        if rc != 0:
+            raise RuntimeError({1: "Invalid key value", 2: "Ids map reached maxIndex"}.get(rc, "error"))
+
+
+# ----------------------------------------------------------------------------- A3
+def bucketize(lengths, indices, num_features: int, world: int, sequence=True, do_unique=False, return_count=False):
+    lengths = _i64(lengths)
+    indices = _i64(indices)
+    n = indices.size
+    new_lengths = np.zeros(lengths.size * world, np.int64)
+    new_indices = np.empty(n, np.int64)
+    perm = np.empty(n, np.int64)
+    counts = np.empty(n, np.int64) if (sequence and do_unique and return_count) else None
+    k = lib().orc_bucketize(p64(lengths), C.c_int64(lengths.size), p64(indices), C.c_int64(n),
+                            C.c_int64(num_features), C.c_int64(world), C.c_int(int(sequence)),
+                            C.c_int(int(do_unique)), C.c_int(int(return_count)), p64(new_lengths),
+                            p64(new_indices), p64(perm), p64(counts))
+    return new_lengths, new_indices[:k].copy(), perm, (counts[:k].copy() if counts is not None else np.empty(0, np.int64))
+
+
+# ----------------------------------------------------------------------------- A4
+class SwapManager:
+    def __init__(self, cache_size: int, mem_start_offset: int = 0):
+        self._h = C.c_void_p(lib().orc_swap_new(C.c_int64(cache_size), C.c_int64(mem_start_offset)))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().orc_swap_free(self._h)
+            self._h = None
+
+    def compute_swap_info(self, keys):
+        keys = _i64(keys)
+        n = keys.size
+        m = max(n, 1)
+        bo, sik, sio, sok, soo = (np.empty(m, np.int64) for _ in range(5))
+        nin, nout = C.c_int64(0), C.c_int64(0)
+        rc = lib().orc_swap_compute(self._h, p64(keys), C.c_int64(n), p64(bo), p64(sik), p64(sio), C.byref(nin),
+                                    p64(sok), p64(soo), C.byref(nout))
+        if rc != 0:
+            raise RuntimeError("cacheSize_ too small")
+        return (sok[:nout.value].copy(), soo[:nout.value].copy(), sik[:nin.value].copy(), sio[:nin.value].copy(),
+                bo[:n].copy())
+
+    def remove_keys(self, keys):
+        keys = _i64(keys)
+        lib().orc_swap_remove(self._h, p64(keys), C.c_int64(keys.size))
+
+    def occupied(self) -> int:
+        return lib().orc_swap_occupied(self._h)
+
+
+# ----------------------------------------------------------------------------- A5
+class FeatureFilter:
+    def __init__(self, admit_threshold: int = -1, evict_threshold: int = 0, evict_step_interval: int = 0):
+        self._h = C.c_void_p(lib().orc_filter_new(C.c_int64(admit_threshold), C.c_uint64(evict_threshold),
+                                                  C.c_uint64(evict_step_interval)))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().orc_filter_free(self._h)
+            self._h = None
+
+    def statistics_key_count(self, keys, counts=None):
+        keys = _i64(keys)
+        counts = _i64(counts) if counts is not None else None
+        lib().orc_filter_statistics(self._h, p64(keys), p64(counts), C.c_int64(keys.size))
+
+    def count_filter(self, keys):
+        keys = _i64(keys).copy()
+        lib().orc_filter_count_filter(self._h, p64(keys), C.c_int64(keys.size))
+        return keys
+
+    def record_timestamp(self, keys, ts):
+        keys = _i64(keys)
+        ts = _i64(ts)
+        lib().orc_filter_record_timestamp(self._h, p64(keys), p64(ts), C.c_int64(keys.size))
+
+    def evict_keys(self):
+        n = lib().orc_filter_num_evict(self._h)
+        out = np.empty(max(n, 1), np.int64)
+        lib().orc_filter_get_evict(self._h, p64(out))
+        return out[:n].copy()
+
+    def clear_evict(self):
+        lib().orc_filter_clear_evict(self._h)
+
+    def count_of(self, key: int) -> int:
+        return lib().orc_filter_count_of(self._h, C.c_int64(key))
+
+
+# ----------------------------------------------------------------------------- A6
+def tbe_forward(weights, weights_offsets, D_offsets, indices, offsets, T, B, total_D, max_D, pooling_mode):
+    weights = np.ascontiguousarray(weights, np.float32)
+    indices = _i64(indices)
+    offsets = _i64(offsets)
+    wo = _i64(weights_offsets)
+    do = np.ascontiguousarray(D_offsets, np.int32)
+    if pooling_mode == 2:
+        out = np.zeros((indices.size, max_D), np.float32)
+    else:
+        out = np.zeros((B, total_D), np.float32)
+    lib().orc_tbe_forward(pf(weights), p64(wo), p32(do), p64(indices), p64(offsets), C.c_int64(T), C.c_int64(B),
+                          C.c_int32(total_D), C.c_int32(max_D), C.c_int(pooling_mode), pf(out))
+    return out
+
+
+# ----------------------------------------------------------------------------- A7
+def adam_beta2sqrt(beta1, beta2, it):
+    out = C.c_float(0)
+    lib().orc_adam_host_scalars(C.c_float(beta1), C.c_float(beta2), C.c_int64(it), C.byref(out))
+    return out.value
+
+
+def tbe_backward(grad_output, weights, momentum1, momentum2, weights_offsets, D_offsets, hash_size_cumsum, indices,
+                 offsets, T, B, total_D, max_D, pooling_mode, optimizer, lr, eps=0.0, beta1=0.9, beta2=0.999, it=1,
+                 unique_ids=None, unique_offsets=None, unique_inverse=None, gradient_clipping=False,
+                 max_gradient=0.0):
+    """In place on ``weights`` / ``momentum1`` / ``momentum2`` (float32 numpy arrays)."""
+    for a in (weights, momentum1, momentum2):
+        assert a is None or (a.dtype == np.float32 and a.flags.c_contiguous)
+    go = np.ascontiguousarray(grad_output, np.float32)
+    uid = _i64(unique_ids) if unique_ids is not None else None
+    uoff = _i64(unique_offsets) if unique_ids is not None else None
+    uinv = _i64(unique_inverse) if unique_ids is not None else None
+    rc = lib().orc_tbe_backward(pf(go), pf(weights), pf(momentum1), pf(momentum2), p64(_i64(weights_offsets)),
+                                p32(np.ascontiguousarray(D_offsets, np.int32)), p64(_i64(hash_size_cumsum)),
+                                p64(_i64(indices)), p64(_i64(offsets)), p64(uid), p64(uoff), p64(uinv),
+                                C.c_int64(T), C.c_int64(B), C.c_int32(total_D), C.c_int32(max_D),
+                                C.c_int(pooling_mode), C.c_int(optimizer), C.c_float(lr), C.c_float(eps),
+                                C.c_float(beta1), C.c_float(beta2), C.c_int64(it), C.c_int(int(gradient_clipping)),
+                                C.c_float(max_gradient))
+    assert rc == 0
+
+
+# ----------------------------------------------------------------------------- A8-A10
+def gather_rows(table, slots, D):
+    slots = _i64(slots)
+    out = np.empty((slots.size, D), np.float32)
+    lib().orc_gather_rows(pf(table), p64(slots), C.c_int64(slots.size), C.c_int32(D), pf(out))
+    return out
+
+
+def scatter_rows(table, slots, D, rows):
+    slots = _i64(slots)
+    rows = np.ascontiguousarray(rows, np.float32)
+    lib().orc_scatter_rows(pf(table), p64(slots), C.c_int64(slots.size), C.c_int32(D), pf(rows))
+
+
+def lookup_by_address(addresses, dim):
+    addresses = _i64(addresses)
+    out = np.empty((addresses.size, dim), np.float32)
+    lib().orc_lookup_by_address(p64(addresses), C.c_int64(addresses.size), C.c_int32(dim), pf(out))
+    return out
+
+
+def update_by_address(addresses, dim, rows, update_type):
+    addresses = _i64(addresses)
+    rows = np.ascontiguousarray(rows, np.float32)
+    lib().orc_update_by_address(p64(addresses), C.c_int64(addresses.size), C.c_int32(dim), pf(rows),
+                                C.c_int(update_type))
+
+
+def lazy_adam(grad, indices, m, v, var, lr, beta1, beta2, eps):
+    grad = np.ascontiguousarray(grad, np.float32)
+    indices = np.ascontiguousarray(indices, np.int32)
+    dim = grad.shape[1]
+    lib().orc_lazy_adam(pf(grad), p32(indices), C.c_int64(indices.size), C.c_int32(dim), pf(m), pf(v), pf(var),
+                        C.c_float(lr), C.c_float(beta1), C.c_float(beta2), C.c_float(eps))
+
+
+def sgd(grad, indices, var, lr, weight_decay=None):
+    grad = np.ascontiguousarray(grad, np.float32)
+    indices = _i64(indices)
+    dim = grad.shape[1]
+    lib().orc_sgd(pf(grad), p64(indices), C.c_int64(indices.size), C.c_int32(dim), pf(var), C.c_float(lr),
+                  C.c_float(weight_decay or 0.0), C.c_int(int(weight_decay is not None)))
+
+
+def restore(unique_indices, unique_inverse, unique_offset, offsets_per_table):
+    ui, inv, uo, opt = map(_i64, (unique_indices, unique_inverse, unique_offset, offsets_per_table))
+    out = np.empty(inv.size, np.int64)
+    lib().orc_restore(p64(ui), p64(inv), p64(uo), p64(opt), C.c_int64(opt.size - 1), p64(out))
+    return out

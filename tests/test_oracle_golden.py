@@ -1,0 +1,191 @@
+"""The CPU oracle (oracle/oracle.c) against the golden fixtures that were produced by the
+reference's own compiled host code and by the torch golden its operator test uses
+(tests/golden/make_golden.py)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import port
+
+from tests.golden.driver import run_cache_driver
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+def test_ids_mapper_unique_out_matches_reference(golden_dir):
+    g = _load(golden_dir, "ids_mapper.npz")
+    T = 3
+    mappers = [port.IdsMapper(4096, True) for _ in range(T)]
+    for s in range(3):
+        ids = g[f"s{s}_ids"]
+        offset = g[f"s{s}_offset"]
+        n = ids.size
+        hi, uq, uid, inv = (np.full(max(n, 1), -7, np.int64) for _ in range(4))
+        uoff = np.zeros(T + 1, np.int64)
+        for t in range(T):
+            mappers[t].ids2indices_unique_out(ids, hi, offset, uq, uid, inv, uoff, t)
+        U = int(uoff[-1])
+        np.testing.assert_array_equal(uoff, g[f"s{s}_unique_offset"])
+        np.testing.assert_array_equal(hi[:n], g[f"s{s}_hash_indices"])
+        np.testing.assert_array_equal(uq[:U], g[f"s{s}_unique"])
+        np.testing.assert_array_equal(uid[:U], g[f"s{s}_unique_ids"])
+        np.testing.assert_array_equal(inv[:n], g[f"s{s}_unique_inverse"])
+
+
+def test_ids2indices_unique_sorted_matches_reference(golden_dir):
+    g = _load(golden_dir, "ids_mapper.npz")
+    m = port.IdsMapper(100000, True)
+    for s in range(2):
+        hi, uq, inv = m.ids2indices_unique(g[f"u{s}_ids"])
+        np.testing.assert_array_equal(hi, g[f"u{s}_hash_indices"])
+        np.testing.assert_array_equal(uq, g[f"u{s}_unique"])
+        np.testing.assert_array_equal(inv, g[f"u{s}_inverse"])
+        # invariants of the reference's verify_unique (hybrid_torchrec/test/dt/test_ids_process.py:36-50)
+        assert np.all(np.diff(uq) > 0)
+        np.testing.assert_array_equal(uq[inv], hi)
+
+
+def test_ids_mapper_errors():
+    m = port.IdsMapper(4, True)
+    with pytest.raises(RuntimeError, match="Invalid key"):
+        m.ids2indices_unique(np.array([1, -5], np.int64))
+    with pytest.raises(RuntimeError, match="maxIndex"):
+        m.ids2indices_unique(np.arange(10, 20, dtype=np.int64))
+
+
+def test_bucketize_matches_reference(golden_dir):
+    g = _load(golden_dir, "bucketize.npz")
+    for c in range(int(g["n_cases"][0])):
+        W, F, B, do_unique, ret_count = (int(x) for x in g[f"c{c}_meta"])
+        nl, ni, perm, cnt = port.bucketize(g[f"c{c}_lengths"], g[f"c{c}_indices"], F, W, True, bool(do_unique),
+                                           bool(ret_count))
+        np.testing.assert_array_equal(nl, g[f"c{c}_new_lengths"])
+        np.testing.assert_array_equal(ni, g[f"c{c}_new_indices"])
+        np.testing.assert_array_equal(perm, g[f"c{c}_unbucketize_permute"])
+        np.testing.assert_array_equal(cnt, g[f"c{c}_ids_counts"])
+
+
+def test_cache_policy_matches_reference(golden_dir):
+    g = _load(golden_dir, "cache.npz")
+    for c in range(int(g["n_cases"][0])):
+        cache, admit, evict_thr, interval, steps = (int(x) for x in g[f"c{c}_meta"])
+        keys = [g[f"c{c}_s{s}_keys"] for s in range(steps)]
+        admit_on = admit != -1
+        swap = port.SwapManager(cache, 1 if admit_on else 0)
+        filt = port.FeatureFilter(admit, evict_thr, interval) if (admit_on or evict_thr) else None
+        rec = run_cache_driver(swap, filt, keys, interval)
+        for s, r in enumerate(rec):
+            for k, v in r.items():
+                np.testing.assert_array_equal(v, g[f"c{c}_s{s}_{k}"], err_msg=f"case {c} step {s} {k}")
+
+
+def test_cache_too_small_raises():
+    swap = port.SwapManager(4, 0)
+    swap.compute_swap_info(np.array([1, 2, 3, 4], np.int64))
+    with pytest.raises(RuntimeError, match="too small"):
+        swap.compute_swap_info(np.array([5], np.int64))  # every slot was used one step ago
+
+
+def _tbe_layout(specs):
+    rows = [int(r) for r, _ in specs]
+    dims = [int(d) for _, d in specs]
+    wo = np.concatenate([[0], np.cumsum([r * d for r, d in zip(rows, dims)])])[:-1].astype(np.int64)
+    do = np.concatenate([[0], np.cumsum(dims)]).astype(np.int32)
+    hs = np.concatenate([[0], np.cumsum(rows)]).astype(np.int64)
+    return rows, dims, wo, do, hs
+
+
+@pytest.mark.parametrize("with_unique", [False, True])
+def test_tbe_matches_torch_golden(golden_dir, with_unique):
+    """4 epochs of forward + fused backward; outputs and final weights vs nn.EmbeddingBag + torch.optim
+    at the reference test's gate (isclose 1e-4/1e-4)."""
+    g = _load(golden_dir, "tbe_torch.npz")
+    specs = g["specs"]
+    rows, dims, wo, do, hs = _tbe_layout(specs)
+    T = len(rows)
+    total_D, max_D = int(do[-1]), max(dims)
+    for c in range(int(g["n_cases"][0])):
+        mode, opt, B, epochs = (int(x) for x in g[f"c{c}_meta"])
+        w = g[f"c{c}_w0"].astype(np.float32).copy()
+        m1 = np.full_like(w, 0.1 if opt == 1 else 0.0)
+        m2 = np.zeros_like(w)
+        lr = {1: 0.05, 2: 0.01, 3: 0.05}[opt]
+        for e in range(epochs):
+            idx, offs = g[f"c{c}_e{e}_indices"], g[f"c{c}_e{e}_offsets"]
+            out = port.tbe_forward(w, wo, do, idx, offs, T, B, total_D, max_D, mode)
+            np.testing.assert_allclose(out, g[f"c{c}_e{e}_out"], rtol=1e-4, atol=1e-4)
+            kw = {}
+            if with_unique:
+                uids, invs, uoff = [], [], [0]
+                for t in range(T):
+                    seg = idx[offs[t * B]:offs[(t + 1) * B]]
+                    u, inv = port.unique_sorted(seg)
+                    uids.append(u)
+                    invs.append(inv)
+                    uoff.append(uoff[-1] + u.size)
+                kw = dict(unique_ids=np.concatenate(uids), unique_offsets=np.array(uoff, np.int64),
+                          unique_inverse=np.concatenate(invs))
+            port.tbe_backward(out, w, m1, m2, wo, do, hs, idx, offs, T, B, total_D, max_D, mode, opt, lr, eps=1e-8,
+                              beta1=0.9, beta2=0.999, it=e + 1, **kw)  # loss = sum(out^2)/2 -> grad = out
+        np.testing.assert_allclose(w, g[f"c{c}_w_final"], rtol=1e-4, atol=1e-4, err_msg=f"case {c}")
+
+
+def test_hand_examples_from_reference_tests():
+    # hybrid_torchrec/test/dt/test_batched_embedding_kernel.py:42-46
+    w = np.arange(4 * 2, dtype=np.float32)
+    out = port.tbe_forward(w, [0], [0, 2], [0, 1, 2, 3, 1], [0, 2, 4, 5], 1, 3, 2, 2, 0)
+    np.testing.assert_array_equal(out, np.array([[2, 4], [10, 12], [2, 3]], np.float32))
+    # hybrid_torchrec/test/dt/test_emb_lookup_optimizer.py:43-47 (hash indices 11,22,11,33,22,33)
+    u, inv = port.unique_sorted([11, 22, 11, 33, 22, 33])
+    np.testing.assert_array_equal(u, [11, 22, 33])
+    np.testing.assert_array_equal(inv, [0, 1, 0, 2, 1, 2])
+
+
+def test_lazy_adam_matches_reference_numpy_golden():
+    """cust_op/test/aclnn_lazy_adam_test/tf/scripts/gen_data.py:90-128 (uniform(1,2) data,
+    beta .9/.999, lr 1e-3, eps 1e-7), gate 1e-6 (verify_result.py:21-41)."""
+    rng = np.random.default_rng(5)
+    rows, dim, n = 2000, 32, 564
+    m = rng.uniform(1, 2, (rows, dim)).astype(np.float32)
+    v = rng.uniform(1, 2, (rows, dim)).astype(np.float32)
+    var = rng.uniform(1, 2, (rows, dim)).astype(np.float32)
+    g = rng.uniform(1, 2, (n, dim)).astype(np.float32)
+    idx = rng.permutation(rows)[:n].astype(np.int32)
+    idx[3] = -1
+    b1, b2, lr, eps = 0.9, 0.999, 1e-3, 1e-7
+    em, ev, evar = m.copy(), v.copy(), var.copy()
+    ok = idx >= 0
+    r = idx[ok]
+    em[r] = b1 * m[r] + (1 - b1) * g[ok]
+    ev[r] = b2 * v[r] + (1 - b2) * g[ok] * g[ok]
+    evar[r] = var[r] + (-lr * em[r]) / (np.sqrt(np.abs(ev[r])) + eps)
+    port.lazy_adam(g, idx, m, v, var, lr, b1, b2, eps)
+    for a, b in ((m, em), (v, ev), (var, evar)):
+        np.testing.assert_allclose(a, b, rtol=1e-6, atol=1e-6)
+
+
+def test_by_address_and_restore():
+    rng = np.random.default_rng(6)
+    table = rng.standard_normal((100, 8)).astype(np.float32)
+    base = table.ctypes.data
+    slots = rng.integers(0, 100, 40)
+    addr = (base + slots * 8 * 4).astype(np.int64)
+    addr[5] = 0
+    out = port.lookup_by_address(addr, 8)
+    exp = table[slots].copy()
+    exp[5] = 0
+    np.testing.assert_array_equal(out, exp)
+    uniq_slots = rng.permutation(100)[:20]
+    addr = (base + uniq_slots * 8 * 4).astype(np.int64)
+    upd = rng.standard_normal((20, 8)).astype(np.float32)
+    before = table.copy()
+    port.update_by_address(addr, 8, upd, 0)
+    np.testing.assert_array_equal(table[uniq_slots], before[uniq_slots] + upd)
+    port.update_by_address(addr, 8, upd, 1)
+    np.testing.assert_array_equal(table[uniq_slots], upd)
+    ui = np.array([5, 9, 7, 100, 200], np.int64)
+    h = port.restore(ui, [0, 1, 1, 1, 0, 1], [0, 3, 5], [0, 3, 6])
+    np.testing.assert_array_equal(h, [5, 9, 9, 200, 100, 200])
