@@ -1,0 +1,336 @@
+/*
+ * recsdk_b200 -- C ABI of the B200 (sm_100a) sparse-embedding hot path.
+ *
+ * Every entry point is plain C: device pointers, sizes, scalars and a CUDA
+ * stream (passed as void*).  No entry point allocates, frees or synchronises;
+ * work is enqueued on the given stream and the call returns.  Scratch memory is
+ * caller-provided: ask the matching *_workspace_bytes() function, allocate once,
+ * pass it in (the same two-call shape as the reference's aclnn GetWorkspaceSize
+ * + execute pair, cust_op/framework/torch_plugin/torch_library/2.6.0/common/
+ * pytorch_npu_helper.hpp:512-561).
+ *
+ * Return value: RECSDK_OK or a RECSDK_ERR_* for errors the host can see
+ * (bad arguments, workspace too small, launch failure).  Errors that only the
+ * device can see (negative key, table full, cache too small, index out of
+ * range) are written to a caller-provided device status block, see
+ * recsdk_status_t; the host reads it when it wants to (the torch/python layer
+ * does so where the reference would raise).
+ *
+ * All reference citations are paths inside the reference project.
+ */
+#ifndef RECSDK_B200_H
+#define RECSDK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RECSDK_API __attribute__((visibility("default")))
+
+/* ---- status codes (host return values and device status block) ---------- */
+enum {
+    RECSDK_OK = 0,
+    RECSDK_ERR_INVALID_ARG = 1,     /* null pointer, negative size, unsupported mode */
+    RECSDK_ERR_WORKSPACE = 2,       /* workspace smaller than *_workspace_bytes()     */
+    RECSDK_ERR_CUDA = 3,            /* kernel launch / runtime error                  */
+    RECSDK_ERR_NEGATIVE_KEY = 4,    /* hybrid_torchrec/src/ids_process/ids_mapper.cpp:45,83  "Invalid key value" */
+    RECSDK_ERR_TABLE_FULL = 5,      /* ids_mapper.cpp:48-50,93-97 "Ids map reached maxIndex"               */
+    RECSDK_ERR_CACHE_TOO_SMALL = 6, /* torchrec_embcache/csrc/embedding_cache/swap_manager.cpp:114-116      */
+    RECSDK_ERR_INDEX_RANGE = 7,     /* a row index / slot / offset outside its table                        */
+    RECSDK_ERR_HASH_FULL = 8,       /* open-addressing key table has no free entry left                     */
+    RECSDK_ERR_TOO_LARGE = 9        /* size beyond a stated maximum                                         */
+};
+
+/* Device status block: 4 x int64 {code, detail0, detail1, reserved}.  The first
+ * error wins (atomicCAS on code).  Zero it before use (recsdk_status_clear). */
+#define RECSDK_STATUS_WORDS 4
+RECSDK_API int recsdk_status_clear(int64_t* dev_status, void* stream);
+
+RECSDK_API const char* recsdk_error_string(int code);
+RECSDK_API int recsdk_version(void);
+
+/* ---- enums shared with the reference operator API ------------------------
+ * cust_op/framework/torch_plugin/torch_library/2.6.0/split_embedding_codegen_forward_unweighted/
+ * split_embedding_codegen_forward_unweighted.h:18-39 */
+enum { RECSDK_POOL_SUM = 0, RECSDK_POOL_MEAN = 1, RECSDK_POOL_NONE = 2 };
+enum { RECSDK_OPT_ADAGRAD = 1, RECSDK_OPT_ADAM = 2, RECSDK_OPT_SGD = 3 };
+
+/* =========================================================================
+ * A6  pooled embedding gather (forward)
+ * replaces aclnnSplitEmbeddingCodegenForwardUnweighted, called from
+ * .../split_embedding_codegen_forward_unweighted.cpp:24-71 (kernel:
+ * ascendc_op/ai_core_op/split_embedding_codegen_forward_unweighted/v220/op_kernel/
+ * split_embedding_codegen_forward_unweighted_kernel.h:226-241,299-343).
+ *
+ * out[b, D_offsets[t]:D_offsets[t+1]] = sum (or mean) over the bag (t,b) of
+ * dev_weights[weights_offsets[t] + idx*D_t : +D_t], rows added in index order
+ * starting from 0.0f; empty bag -> zeros.  NONE: out[i, 0:D_t] = row(i), the
+ * rest of the max_D-wide output row is zero.  `indices` is what the reference
+ * calls hash_indices when those are given.  Every element of `out` is written.
+ * ========================================================================= */
+typedef struct {
+    const float* dev_weights;       /* flat, all tables                         */
+    const int64_t* weights_offsets; /* [T] element offset of each feature's table */
+    const int32_t* D_offsets;       /* [T+1]                                    */
+    const int64_t* indices;         /* [N]                                      */
+    const int64_t* offsets;         /* [T*B+1], feature-major: offsets[t*B+b]   */
+    float* out;                     /* [B,total_D]  (NONE: [N,max_D])           */
+    int64_t T, B, N;
+    int32_t total_D, max_D;
+    int32_t pooling_mode;
+    int64_t weights_numel; /* >0: rows are bounds-checked against it, violations -> status, row read as 0 */
+    int64_t* dev_status;   /* optional */
+} recsdk_tbe_forward_args;
+RECSDK_API int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream);
+
+/* =========================================================================
+ * A1  sorted unique + inverse
+ * replaces hybrid::UniqueParallel (hybrid_torchrec/src/ids_process/unique.cpp:55-127).
+ * unique_out ascending, inverse_out[i] = rank of ids[i]; *num_unique_out (device)
+ * receives U.  key_bits: number of significant low bits of the ids (<= 64;
+ * pass 64 when unknown) -- the sort only walks those.  ids must be >= 0.
+ * ========================================================================= */
+RECSDK_API size_t recsdk_unique_sorted_workspace_bytes(int64_t n);
+RECSDK_API int recsdk_unique_sorted(const int64_t* ids, int64_t n, int key_bits, int64_t* unique_out,
+                                    int64_t* inverse_out, int64_t* num_unique_out, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
+/* =========================================================================
+ * A7  fused backward: gradient segment-sum over deduplicated rows + sparse
+ * Adagrad / Adam / SGD row update, in place.
+ * replaces aclnnBackwardCodegenAdagradUnweightedExact (optim_type 1/2/3), called from
+ * .../backward_codegen_{adagrad,adam,sgd}_unweighted_exact.cpp (adam: :354-412);
+ * kernels ascendc_op/ai_core_op/backward_codegen_adagrad_unweighted_exact/v220/op_kernel/
+ * backward_codegen_unweighted_exact_kernel_unique.h:113-268 (segment-sum),
+ * backward_codegen_adagrad_unweighted_exact_kernel_unique.h:50-62 (Adagrad),
+ * backward_codegen_adam_unweighted_exact_kernel_unique.h:70-96 (Adam),
+ * backward_codegen_sgd_unweighted_exact_kernel.h:107-124 (SGD); Adam host
+ * scalars op_host/backward_codegen_adagrad_unweighted_exact.cpp:84-111.
+ *
+ * With unique_ids/unique_offsets/unique_inverse (all three or none) the
+ * caller's dedup is used: G[inverse[i] + unique_offsets[t]] += grad row of i,
+ * row u of feature t lives at weights_offsets[t] + unique_ids[u]*D_t.
+ * Without them the op dedups internally on hash_size_cumsum[t] + idx.
+ *
+ * Reduction order (the reference uses unordered atomics; here it is fixed):
+ * the contributions of one row are taken in ascending index position;
+ * reduce_chunk == 0: one sequential sum from 0.0f.  reduce_chunk == C > 0: runs
+ * longer than C are split into consecutive chunks of C, each summed
+ * sequentially from 0.0f, and the chunk sums are then summed sequentially from
+ * 0.0f.  Both are run-to-run deterministic; C = 64 is the fast default (hot
+ * rows do not serialise on one warp).
+ * ========================================================================= */
+typedef struct {
+    const float* grad_output; /* [B,total_D]  (NONE: [N,max_D]) */
+    float* dev_weights;
+    float* momentum1; /* Adagrad accumulator / Adam m ; NULL for SGD */
+    float* momentum2; /* Adam v ; else NULL */
+    const int64_t* weights_offsets;  /* [T]   */
+    const int32_t* D_offsets;        /* [T+1] */
+    const int64_t* hash_size_cumsum; /* [T+1] (used when unique_* are NULL) */
+    const int64_t* indices;          /* [N]   */
+    const int64_t* offsets;          /* [T*B+1] */
+    const int64_t* unique_ids;       /* [U] or NULL */
+    const int64_t* unique_offsets;   /* [T+1] or NULL */
+    const int64_t* unique_inverse;   /* [N] or NULL */
+    int64_t T, B, N;
+    int64_t num_unique_capacity; /* numel of unique_ids (upper bound of U); 0 when NULL */
+    int32_t total_D, max_D;
+    int32_t pooling_mode, optimizer;
+    int32_t total_hash_size_bits; /* bits needed for hash_size_cumsum[T]; 0 = derive as 64 */
+    int32_t reduce_chunk;         /* 0 or 64 */
+    float learning_rate, eps, beta1, beta2;
+    int64_t iter; /* Adam step count t >= 1 */
+    int32_t gradient_clipping;
+    float max_gradient;
+    int64_t weights_numel; /* >0: bounds check */
+    int64_t* dev_status;   /* optional */
+    void* workspace;
+    size_t workspace_bytes;
+    /* optional profiling hooks: cudaEvent_t handles recorded on `stream` right before and right
+     * after the launch of the row-update kernel (the dominant kernel of the step); NULL = off */
+    void* ev_update_start;
+    void* ev_update_stop;
+} recsdk_tbe_backward_args;
+RECSDK_API size_t recsdk_tbe_backward_workspace_bytes(int64_t N, int32_t max_D);
+RECSDK_API int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stream);
+
+/* Adam step-size scalar exactly as the reference host computes it in float:
+ * sqrt(1-beta2^t)/(1-beta1^t)  (op_host/...cpp:98-102). */
+RECSDK_API float recsdk_adam_beta2sqrt(float beta1, float beta2, int64_t iter);
+
+/* =========================================================================
+ * A8  row gather / row assign by slot (swap-out / swap-in of cache rows)
+ * replaces HybridSplitTableBatchedEmbeddingBagsCodegen.{gather_embs,gather_momentum,
+ * scatter_update_embs,scatter_update_momentum}
+ * (hybrid_torchrec/hybrid_torchrec/distributed/batched_embedding_kernel.py:297-345).
+ * Rows are moved with bulk async copies (TMA) through shared memory when
+ * D*4 is a multiple of 16 bytes, else with plain loads.
+ * ========================================================================= */
+RECSDK_API int recsdk_gather_rows(const float* table, const int64_t* slots, int64_t k, int32_t D, float* out,
+                                  int64_t table_rows, int64_t* dev_status, void* stream);
+RECSDK_API int recsdk_scatter_rows(float* table, const int64_t* slots, int64_t k, int32_t D, const float* rows,
+                                   int64_t table_rows, int64_t* dev_status, void* stream);
+
+/* =========================================================================
+ * A9  TF-flavour operators (signatures of cust_op/framework/tf_plugin/src/
+ * cust_embedding_by_address.cpp:19-52, lazy_adam.cpp:20-35, sgd.cpp:19-28)
+ * ========================================================================= */
+/* EmbeddingLookupByAddress: out[i,:] = *(float*)address[i], address 0 -> zeros
+ * (ascendc_op/ai_core_op/cust_op_by_addr/v220/op_kernel/embedding_lookup_by_address.cpp:106-145).
+ * Addresses are device addresses of fp32 rows. */
+RECSDK_API int recsdk_lookup_by_address(const int64_t* addresses, int64_t n, int32_t embedding_dim, float* out,
+                                        void* stream);
+/* EmbeddingUpdateByAddress: update_type 0 -> row += embedding[i] (atomic), else row = embedding[i];
+ * address 0 skipped (.../embedding_update_by_address.cpp:100-190). */
+RECSDK_API int recsdk_update_by_address(const int64_t* addresses, int64_t n, int32_t embedding_dim,
+                                        const float* embedding, int32_t update_type, void* stream);
+/* LazyAdam: m,v,var rows at indices[i] updated with gradient[i]; lr is already bias corrected;
+ * negative index skipped; indices must be unique
+ * (ascendc_op/ai_core_op/fused_lazy_adam/v220/op_kernel/lazy_adam.cpp:138-207). */
+RECSDK_API int recsdk_lazy_adam(const float* gradient, const int32_t* indices, int64_t n, int32_t dim, float* m,
+                                float* v, float* var, float lr, float beta1, float beta2, float epsilon,
+                                void* stream);
+/* Sgd: var[indices[i]] += (gradient[i] (+ weight_decay*var)) * -lr, atomic add, duplicates accumulate
+ * (ascendc_op/ai_core_op/fused_sgd/v220/op_kernel/sgd_kernel.h:78-190).  With weight decay the
+ * updates are staged in `workspace` (n*dim*4 bytes) so that every occurrence of a duplicated
+ * index sees the original var, as the reference's gather-compute-scatter does; without it
+ * workspace may be NULL. */
+RECSDK_API int recsdk_sgd(const float* gradient, const int64_t* indices, int64_t n, int32_t dim, float* var,
+                          float lr, float weight_decay, int32_t use_weight_decay, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/* =========================================================================
+ * A10 Restore: hash_indices[r] = unique_indices[unique_inverse[r] + unique_offset[t]]
+ * replaces Embcache::Restore (torchrec_embcache/csrc/ops/restore.cpp:15-51).
+ * offsets_per_table [n_tables+1] is a DEVICE array here.
+ * ========================================================================= */
+RECSDK_API int recsdk_restore(const int64_t* unique_indices, const int64_t* unique_inverse,
+                              const int64_t* unique_offset, const int64_t* offsets_per_table, int64_t n_tables,
+                              int64_t n, int64_t* hash_indices, void* stream);
+
+/* =========================================================================
+ * A2  IdsMapper: key -> slot in an HBM-resident open-addressing table, slots
+ * handed out in first-come (input position) order, then first-occurrence
+ * unique of the slots of one table segment.
+ * replaces hybrid::IdsMapper (hybrid_torchrec/src/ids_process/ids_mapper.h:30-102,
+ * ids_mapper.cpp:36-61 ids2indices_unique, :63-174 ids2indices_unique_out).
+ *
+ * The mapper's state lives in caller-allocated device memory described by
+ * recsdk_mapper_t (a plain struct the caller keeps on the host).
+ * ========================================================================= */
+typedef struct {
+    int64_t* table;       /* [hash_capacity*2] int64 {key,value} pairs          */
+    int64_t hash_capacity; /* power of two, >= 2*init_max_index recommended     */
+    int64_t* slot_key;    /* [init_max_index]  slot -> key  (indice2id)         */
+    int32_t* mark;        /* [init_max_index]  scratch, all 0x7fffffff between calls */
+    int64_t* counters;    /* [4] device: {max_index, -, -, -}                   */
+    int64_t init_max_index;
+    int32_t only_device_mem; /* 1: slot >= init_max_index is RECSDK_ERR_TABLE_FULL */
+} recsdk_mapper_t;
+RECSDK_API size_t recsdk_mapper_table_bytes(int64_t hash_capacity);
+/* initialises table / slot_key / mark / counters */
+RECSDK_API int recsdk_mapper_init(const recsdk_mapper_t* m, void* stream);
+RECSDK_API size_t recsdk_mapper_workspace_bytes(int64_t n);
+/* ids2indices_unique_out for one table segment [seg_start, seg_start+seg_len) of
+ * the batch arrays.  unique_offset is a device [T+1] array: entry table_id is
+ * read as this table's base (forced to 0 for table 0), entry table_id+1 written. */
+RECSDK_API int recsdk_mapper_unique_out(const recsdk_mapper_t* m, const int64_t* ids, int64_t* hash_indices,
+                                        int64_t seg_start, int64_t seg_len, int64_t* unique, int64_t* unique_ids,
+                                        int64_t* unique_inverse, int64_t* unique_offset, int64_t table_id,
+                                        int64_t* dev_status, void* workspace, size_t workspace_bytes,
+                                        void* stream);
+/* ids2indices_unique: slots for all ids (written to hash_indices), then SORTED
+ * unique of the slots + inverse.  Workspace: max(mapper, unique_sorted). */
+RECSDK_API int recsdk_mapper_ids2indices_unique(const recsdk_mapper_t* m, const int64_t* ids, int64_t n,
+                                                int64_t* hash_indices, int64_t* unique_out, int64_t* inverse_out,
+                                                int64_t* num_unique_out, int64_t* dev_status, void* workspace,
+                                                size_t workspace_bytes, void* stream);
+
+/* =========================================================================
+ * A4  SwapManager: slot policy of the HBM cache
+ * replaces Embcache::SwapManager (torchrec_embcache/csrc/embedding_cache/swap_manager.h:28-55,
+ * swap_manager.cpp:32-139 ComputeSwapInfo, :141-159 RemoveKeys).
+ * ========================================================================= */
+typedef struct {
+    int64_t* table;        /* [hash_capacity*2] {key,value}                      */
+    int64_t hash_capacity; /* power of two                                       */
+    int64_t* slot_key;     /* [cache_size]  cache_[off].key                      */
+    int64_t* slot_version; /* [cache_size]  cache_[off].version                  */
+    int64_t* counters;     /* [4] device: {occupied, now_version, swap_idx, -}   */
+    int64_t cache_size;
+    int64_t mem_start_offset; /* 1 when admission is enabled, else 0            */
+} recsdk_swap_t;
+RECSDK_API int recsdk_swap_init(const recsdk_swap_t* s, void* stream);
+RECSDK_API size_t recsdk_swap_workspace_bytes(int64_t n, int64_t cache_size);
+/* keys [n] (-1 = not admitted -> slot 0).  Outputs (device): batch_offs [n];
+ * swapin_keys/offs, swapout_keys/offs [n each]; counts_out [2] = {n_swapin, n_swapout}. */
+RECSDK_API int recsdk_swap_compute(const recsdk_swap_t* s, const int64_t* keys, int64_t n, int64_t* batch_offs,
+                                   int64_t* swapin_keys, int64_t* swapin_offs, int64_t* swapout_keys,
+                                   int64_t* swapout_offs, int64_t* counts_out, int64_t* dev_status,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+/* RemoveKeys; n_keys_dev (device int64) optional: when non-NULL only the first
+ * min(n, *n_keys_dev) keys are used (lets the evict list stay on the device). */
+RECSDK_API int recsdk_swap_remove(const recsdk_swap_t* s, const int64_t* keys, int64_t n,
+                                  const int64_t* n_keys_dev, void* stream);
+
+/* =========================================================================
+ * A5  FeatureFilter: count-based admission and timestamp eviction
+ * replaces Embcache::FeatureFilter (torchrec_embcache/csrc/feature_filter/feature_filter.h:26-60,
+ * feature_filter.cpp:112-138 StatisticsKeyCount, :140-160 CountFilter,
+ * :27-50 RecordTimestamp, :52-80 FeatureEvict).
+ * Entries are 32 bytes: {key, count, timestamp, tag}.
+ * ========================================================================= */
+typedef struct {
+    int64_t* table;        /* [hash_capacity*4]                                  */
+    int64_t hash_capacity; /* power of two                                       */
+    int64_t* counters;     /* [4] device: {latest_timestamp, record_batch_id, n_evict, -} */
+    int64_t admit_threshold; /* -1: admission disabled                           */
+    int64_t evict_threshold; /* 0: eviction disabled                             */
+    int64_t evict_step_interval;
+} recsdk_filter_t;
+RECSDK_API int recsdk_filter_init(const recsdk_filter_t* f, void* stream);
+RECSDK_API size_t recsdk_filter_workspace_bytes(int64_t n);
+/* counts may be NULL (every occurrence counts 1). */
+RECSDK_API int recsdk_filter_statistics(const recsdk_filter_t* f, const int64_t* keys, const int64_t* counts,
+                                        int64_t n, int64_t* dev_status, void* stream);
+/* keys_inout[i] = -1 where the key is in the count map with count < admit_threshold */
+RECSDK_API int recsdk_filter_count_filter(const recsdk_filter_t* f, int64_t* keys_inout, int64_t n, void* stream);
+/* insert_or_assign(key, ts) in input order (last occurrence wins), latest = max;
+ * runs the evict scan when (batch_id > 0 && (batch_id+1) % interval == 0), appending
+ * to evict_keys (device, capacity evict_capacity) and counters[2]. */
+RECSDK_API int recsdk_filter_record_timestamp(const recsdk_filter_t* f, const int64_t* keys, const int64_t* ts,
+                                              int64_t n, int64_t* evict_keys, int64_t evict_capacity,
+                                              int64_t* dev_status, void* workspace, size_t workspace_bytes,
+                                              void* stream);
+/* resets counters[2] (evictFeatureRecord_.ClearEvictInfo) */
+RECSDK_API int recsdk_filter_clear_evict(const recsdk_filter_t* f, void* stream);
+/* count of one key -> *count_out (device), -1 if absent from the count map */
+RECSDK_API int recsdk_filter_count_of(const recsdk_filter_t* f, const int64_t* keys, int64_t n, int64_t* count_out,
+                                      void* stream);
+
+/* =========================================================================
+ * A3  row-hash bucketize for row-wise sharding
+ * replaces hybrid::block_bucketize_sparse_features_cpu
+ * (hybrid_torchrec/src/ids_process/bucketize.cpp:214-282, kernel :133-211,
+ * ComputeNewLengths :35-51, FillNewIndices :54-76, Deduplicate :79-130).
+ * lengths [F*B]; bucket = id % world; new_lengths [world*F*B] bucket-major;
+ * new_indices grouped by (bucket, feature, sample) in input order;
+ * unbucketize_permute[i] = position of input i in new_indices (or, with
+ * do_unique, in the deduplicated list).  *num_out (device) = valid length of
+ * new_indices / ids_counts.
+ * ========================================================================= */
+RECSDK_API size_t recsdk_bucketize_workspace_bytes(int64_t n, int64_t lengths_size, int64_t world);
+RECSDK_API int recsdk_bucketize(const int64_t* lengths, int64_t lengths_size, const int64_t* indices, int64_t n,
+                                int64_t num_features, int64_t world, int32_t do_unique, int32_t return_count,
+                                int64_t* new_lengths, int64_t* new_indices, int64_t* unbucketize_permute,
+                                int64_t* ids_counts, int64_t* num_out, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RECSDK_B200_H */

@@ -701,7 +701,8 @@ int orc_tbe_backward(const float* grad_output, float* weights, float* momentum1,
                      const int64_t* indices, const int64_t* offsets, const int64_t* unique_ids,
                      const int64_t* unique_offsets, const int64_t* unique_inverse, int64_t T, int64_t B,
                      int32_t total_D, int32_t max_D, int pooling_mode, int optimizer, float lr, float eps,
-                     float beta1, float beta2, int64_t iter, int gradient_clipping, float max_gradient)
+                     float beta1, float beta2, int64_t iter, int gradient_clipping, float max_gradient,
+                     int reduce_chunk)
 {
     int64_t N = offsets[T * B];
     int64_t U, t, u, i;
@@ -724,26 +725,56 @@ int orc_tbe_backward(const float* grad_output, float* weights, float* momentum1,
         U = unique_offsets[T];
     }
     G = (float*)calloc((size_t)(U > 0 ? U : 1) * (size_t)max_D, sizeof(float));
-    /* (1) segment-sum in ascending index position */
-    for (t = 0; t < T; t++) {
-        int32_t D = D_offsets[t + 1] - D_offsets[t], d;
-        int64_t b;
-        int64_t uoff = unique_ids ? unique_offsets[t] : 0;
+    /* (1) segment-sum in ascending index position.  reduce_chunk == 0: one
+     * sequential sum.  reduce_chunk == C: a row with more than C contributions
+     * sums consecutive chunks of C contributions (each from 0.0f) and then the
+     * chunk sums (from 0.0f), both in order. */
+    {
         const int64_t* inv = unique_ids ? unique_inverse : own_inv;
-        for (b = 0; b < B; b++) {
-            int64_t s = offsets[t * B + b], e = offsets[t * B + b + 1];
-            float mean = 1.0f / (float)(e - s);
-            for (i = s; i < e; i++) {
-                const float* g = pooling_mode == 2 ? grad_output + i * max_D : grad_output + b * total_D + D_offsets[t];
-                float* acc = G + (inv[i] + uoff) * max_D;
-                for (d = 0; d < D; d++) {
-                    float v = g[d];
-                    if (gradient_clipping) v = v < -max_gradient ? -max_gradient : (v > max_gradient ? max_gradient : v);
-                    if (pooling_mode == 1) v = v * mean;
-                    acc[d] = acc[d] + v;
+        int64_t* cnt = (int64_t*)calloc((size_t)(U > 0 ? U : 1), sizeof(int64_t));
+        int64_t* seen = (int64_t*)calloc((size_t)(U > 0 ? U : 1), sizeof(int64_t));
+        float* P = (float*)calloc((size_t)(U > 0 ? U : 1) * (size_t)max_D, sizeof(float)); /* open chunk */
+        if (reduce_chunk > 0)
+            for (t = 0; t < T; t++) {
+                int64_t uoff = unique_ids ? unique_offsets[t] : 0;
+                for (i = offsets[t * B]; i < offsets[(t + 1) * B]; i++) cnt[inv[i] + uoff]++;
+            }
+        for (t = 0; t < T; t++) {
+            int32_t D = D_offsets[t + 1] - D_offsets[t], d;
+            int64_t b;
+            int64_t uoff = unique_ids ? unique_offsets[t] : 0;
+            for (b = 0; b < B; b++) {
+                int64_t s = offsets[t * B + b], e = offsets[t * B + b + 1];
+                float mean = 1.0f / (float)(e - s);
+                for (i = s; i < e; i++) {
+                    const float* g =
+                        pooling_mode == 2 ? grad_output + i * max_D : grad_output + b * total_D + D_offsets[t];
+                    int64_t u2 = inv[i] + uoff;
+                    int chunked = reduce_chunk > 0 && cnt[u2] > reduce_chunk;
+                    float* acc = chunked ? P + u2 * max_D : G + u2 * max_D;
+                    for (d = 0; d < D; d++) {
+                        float v = g[d];
+                        if (gradient_clipping)
+                            v = v < -max_gradient ? -max_gradient : (v > max_gradient ? max_gradient : v);
+                        if (pooling_mode == 1) v = v * mean;
+                        acc[d] = acc[d] + v;
+                    }
+                    if (chunked) {
+                        seen[u2]++;
+                        if (seen[u2] % reduce_chunk == 0 || seen[u2] == cnt[u2]) { /* chunk closed */
+                            float* tot = G + u2 * max_D;
+                            for (d = 0; d < D; d++) {
+                                tot[d] = tot[d] + acc[d];
+                                acc[d] = 0.0f;
+                            }
+                        }
+                    }
                 }
             }
         }
+        free(cnt);
+        free(seen);
+        free(P);
     }
     /* (2) one update per unique row */
     if (unique_ids) {

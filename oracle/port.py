@@ -215,7 +215,7 @@ def adam_beta2sqrt(beta1, beta2, it):
 def tbe_backward(grad_output, weights, momentum1, momentum2, weights_offsets, D_offsets, hash_size_cumsum, indices,
                  offsets, T, B, total_D, max_D, pooling_mode, optimizer, lr, eps=0.0, beta1=0.9, beta2=0.999, it=1,
                  unique_ids=None, unique_offsets=None, unique_inverse=None, gradient_clipping=False,
-                 max_gradient=0.0):
+                 max_gradient=0.0, reduce_chunk=0):
     """In place on ``weights`` / ``momentum1`` / ``momentum2`` (float32 numpy arrays)."""
     for a in (weights, momentum1, momentum2):
         assert a is None or (a.dtype == np.float32 and a.flags.c_contiguous)
@@ -229,7 +229,7 @@ def tbe_backward(grad_output, weights, momentum1, momentum2, weights_offsets, D_
                                 C.c_int64(T), C.c_int64(B), C.c_int32(total_D), C.c_int32(max_D),
                                 C.c_int(pooling_mode), C.c_int(optimizer), C.c_float(lr), C.c_float(eps),
                                 C.c_float(beta1), C.c_float(beta2), C.c_int64(it), C.c_int(int(gradient_clipping)),
-                                C.c_float(max_gradient))
+                                C.c_float(max_gradient), C.c_int(reduce_chunk))
     assert rc == 0
 
 

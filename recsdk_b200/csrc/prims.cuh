@@ -1,0 +1,272 @@
+// Device-wide building blocks written for this library: exclusive/inclusive
+// int32 scan and a stable LSD radix sort of (key, 32-bit value) pairs.
+// Both are multi-kernel, allocation-free (scratch comes from the caller) and
+// use no inter-block spin waits.
+#pragma once
+#include "common.cuh"
+
+namespace recsdk {
+
+// ----------------------------------------------------------------------------
+// Block-level helpers
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ int warp_inclusive_scan(int v)
+{
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(kFullMask, v, o);
+        if ((threadIdx.x & 31) >= o) v += n;
+    }
+    return v;
+}
+
+// Inclusive scan across a block of up to 1024 threads; `smem` needs 33 ints.
+// Returns the inclusive prefix of `v`; *total receives the block sum.
+__device__ __forceinline__ int block_inclusive_scan(int v, int* smem, int* total)
+{
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int nw = (blockDim.x + 31) >> 5;
+    int inc = warp_inclusive_scan(v);
+    if (lane == 31) smem[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+        int w = lane < nw ? smem[lane] : 0;
+        int winc = warp_inclusive_scan(w);
+        smem[lane] = winc - w;  // exclusive prefix of warp sums
+        if (lane == 31) smem[32] = winc;
+    }
+    __syncthreads();
+    inc += smem[wid];
+    *total = smem[32];
+    __syncthreads();
+    return inc;
+}
+
+// ----------------------------------------------------------------------------
+// Device-wide int32 scan: reduce per tile -> scan of tile sums (one block) ->
+// apply.  Tile = 256 threads x 8 items.
+// ----------------------------------------------------------------------------
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;
+
+static inline int64_t scan_num_tiles(int64_t n) { return ceil_div(n > 0 ? n : 1, kScanTile); }
+// scratch ints needed by device_scan
+static inline size_t scan_scratch_ints(int64_t n) { return static_cast<size_t>(scan_num_tiles(n)) + 8; }
+
+static __global__ void __launch_bounds__(kScanThreads) scan_reduce_kernel(const int* __restrict__ in, int64_t n,
+                                                                   int* __restrict__ tile_sums)
+{
+    __shared__ int sm[33];
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
+    int s = 0;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k)
+        if (base + k < n) s += in[base + k];
+    int total;
+    block_inclusive_scan(s, sm, &total);
+    if (threadIdx.x == 0) tile_sums[blockIdx.x] = total;
+}
+
+// In place exclusive scan of `m` tile sums by one block; total -> *total_out (int64, optional).
+static __global__ void __launch_bounds__(1024) scan_tile_sums_kernel(int* __restrict__ tile_sums, int64_t m,
+                                                              int64_t* __restrict__ total_out)
+{
+    __shared__ int sm[33];
+    int carry = 0;
+    for (int64_t base = 0; base < m; base += blockDim.x) {
+        int64_t i = base + threadIdx.x;
+        int v = i < m ? tile_sums[i] : 0;
+        int total;
+        int inc = block_inclusive_scan(v, sm, &total);
+        if (i < m) tile_sums[i] = carry + inc - v;
+        carry += total;
+    }
+    if (threadIdx.x == 0 && total_out != nullptr) *total_out = carry;
+}
+
+template <bool INCLUSIVE>
+__global__ void __launch_bounds__(kScanThreads) scan_apply_kernel(const int* __restrict__ in, int* __restrict__ out,
+                                                                  int64_t n, const int* __restrict__ tile_sums)
+{
+    __shared__ int sm[33];
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
+    int v[kScanItems];
+    int s = 0;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k) {
+        v[k] = (base + k < n) ? in[base + k] : 0;
+        s += v[k];
+    }
+    int total;
+    int inc = block_inclusive_scan(s, sm, &total);
+    int run = tile_sums[blockIdx.x] + inc - s;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k) {
+        if (base + k < n) out[base + k] = INCLUSIVE ? run + v[k] : run;
+        run += v[k];
+    }
+}
+
+// out may alias in.  scratch: scan_scratch_ints(n) ints.  total_out: device int64 or nullptr.
+template <bool INCLUSIVE>
+static inline void device_scan(const int* in, int* out, int64_t n, int* scratch, int64_t* total_out, cudaStream_t st)
+{
+    if (n <= 0) {
+        if (total_out) cudaMemsetAsync(total_out, 0, sizeof(int64_t), st);
+        return;
+    }
+    const int64_t tiles = scan_num_tiles(n);
+    scan_reduce_kernel<<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, n, scratch);
+    scan_tile_sums_kernel<<<1, 1024, 0, st>>>(scratch, tiles, total_out);
+    scan_apply_kernel<INCLUSIVE><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, out, n, scratch);
+}
+
+// ----------------------------------------------------------------------------
+// Stable LSD radix sort of (key, uint32 value) pairs, 8 bits per pass.
+// Per pass: tile histograms -> per-digit scan across tiles -> stable scatter
+// (warp match-any ranking).  Tile = 256 threads x 8 items; warp w owns the
+// contiguous 256 items [w*256, (w+1)*256) of the tile, taken 32 at a time, so
+// the order inside a digit is the input order.
+// ----------------------------------------------------------------------------
+constexpr int kSortThreads = 256;
+constexpr int kSortRounds = 8;
+constexpr int kSortTile = kSortThreads * kSortRounds;  // 2048
+constexpr int kRadix = 256;
+
+static inline int64_t sort_num_tiles(int64_t n) { return ceil_div(n > 0 ? n : 1, kSortTile); }
+// uint32 scratch needed: histogram [256][tiles] + digit totals [256]
+static inline size_t sort_scratch_u32(int64_t n) { return static_cast<size_t>(sort_num_tiles(n)) * kRadix + kRadix; }
+
+template <typename KeyT>
+__global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const KeyT* __restrict__ keys, int64_t n, int shift,
+                                                                 uint32_t* __restrict__ hist, int64_t tiles)
+{
+    __shared__ uint32_t h[kRadix];
+    h[threadIdx.x] = 0;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * kSortTile + warp * (kSortRounds * 32);
+#pragma unroll
+    for (int r = 0; r < kSortRounds; ++r) {
+        const int64_t i = tile0 + r * 32 + lane;
+        const bool valid = i < n;
+        const unsigned tag = valid ? static_cast<unsigned>((keys[i] >> shift) & 0xff) : (0x100u + lane);
+        // one shared-memory atomic per distinct digit in the warp, not per item
+        const unsigned peers = __match_any_sync(kFullMask, tag);
+        if (valid && (peers & lanemask_lt()) == 0) atomicAdd(&h[tag], static_cast<uint32_t>(__popc(peers)));
+    }
+    __syncthreads();
+    hist[static_cast<int64_t>(threadIdx.x) * tiles + blockIdx.x] = h[threadIdx.x];
+}
+
+// One block per digit: exclusive scan of hist[d][0..tiles) in place, total -> totals[d].
+static __global__ void __launch_bounds__(256) sort_scan_kernel(uint32_t* __restrict__ hist, int64_t tiles,
+                                                        uint32_t* __restrict__ totals)
+{
+    __shared__ int sm[33];
+    uint32_t* row = hist + static_cast<int64_t>(blockIdx.x) * tiles;
+    int carry = 0;
+    for (int64_t base = 0; base < tiles; base += blockDim.x) {
+        int64_t i = base + threadIdx.x;
+        int v = i < tiles ? static_cast<int>(row[i]) : 0;
+        int total;
+        int inc = block_inclusive_scan(v, sm, &total);
+        if (i < tiles) row[i] = static_cast<uint32_t>(carry + inc - v);
+        carry += total;
+    }
+    if (threadIdx.x == 0) totals[blockIdx.x] = static_cast<uint32_t>(carry);
+}
+
+template <typename KeyT>
+__global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* __restrict__ keys_in,
+                                                                    const uint32_t* __restrict__ vals_in,
+                                                                    KeyT* __restrict__ keys_out,
+                                                                    uint32_t* __restrict__ vals_out, int64_t n,
+                                                                    int shift, const uint32_t* __restrict__ hist,
+                                                                    const uint32_t* __restrict__ totals,
+                                                                    int64_t tiles)
+{
+    __shared__ uint32_t warp_cnt[kSortThreads / 32][kRadix];
+    __shared__ int sm[33];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int w = 0; w < kSortThreads / 32; ++w) warp_cnt[w][threadIdx.x] = 0;
+    __syncthreads();
+
+    const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * kSortTile + warp * (kSortRounds * 32);
+    KeyT key[kSortRounds];
+    uint32_t rank[kSortRounds];
+#pragma unroll
+    for (int r = 0; r < kSortRounds; ++r) {
+        const int64_t i = tile0 + r * 32 + lane;
+        const bool valid = i < n;
+        key[r] = valid ? keys_in[i] : KeyT(0);
+        // invalid lanes get a tag no valid lane can have, so they match nobody valid
+        const unsigned tag = valid ? static_cast<unsigned>((key[r] >> shift) & 0xff) : (0x100u + lane);
+        const unsigned peers = __match_any_sync(kFullMask, tag);
+        const unsigned before = __popc(peers & lanemask_lt());
+        uint32_t prev = 0;
+        if (valid) prev = warp_cnt[warp][tag];
+        __syncwarp();
+        if (valid && before == 0) warp_cnt[warp][tag] = prev + __popc(peers);
+        __syncwarp();
+        rank[r] = prev + before;
+    }
+    __syncthreads();
+
+    // digit base for this tile: exclusive scan of digit totals + this tile's prefix inside the digit
+    {
+        const int d = threadIdx.x;
+        int tot = static_cast<int>(totals[d]);
+        int total_all;
+        int inc = block_inclusive_scan(tot, sm, &total_all);
+        uint32_t run = static_cast<uint32_t>(inc - tot) + hist[static_cast<int64_t>(d) * tiles + blockIdx.x];
+#pragma unroll
+        for (int w = 0; w < kSortThreads / 32; ++w) {
+            uint32_t c = warp_cnt[w][d];
+            warp_cnt[w][d] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int r = 0; r < kSortRounds; ++r) {
+        const int64_t i = tile0 + r * 32 + lane;
+        if (i < n) {
+            const unsigned d = static_cast<unsigned>((key[r] >> shift) & 0xff);
+            const uint32_t pos = warp_cnt[warp][d] + rank[r];
+            keys_out[pos] = key[r];
+            vals_out[pos] = vals_in[i];
+        }
+    }
+}
+
+// Sorts n pairs by the key bits [0, key_bits).  Data ping-pongs between
+// (keys_a, vals_a) and (keys_b, vals_b); returns 0 when the result is in the
+// a-buffers, 1 when it is in the b-buffers.  n < 2^31.
+template <typename KeyT>
+static inline int radix_sort_pairs(KeyT* keys_a, uint32_t* vals_a, KeyT* keys_b, uint32_t* vals_b, int64_t n,
+                                   int key_bits, uint32_t* scratch, cudaStream_t st)
+{
+    if (n <= 1 || key_bits <= 0) return 0;
+    const int64_t tiles = sort_num_tiles(n);
+    uint32_t* hist = scratch;
+    uint32_t* totals = scratch + tiles * kRadix;
+    int cur = 0;
+    for (int shift = 0; shift < key_bits; shift += 8) {
+        KeyT* kin = cur ? keys_b : keys_a;
+        uint32_t* vin = cur ? vals_b : vals_a;
+        KeyT* kout = cur ? keys_a : keys_b;
+        uint32_t* vout = cur ? vals_a : vals_b;
+        sort_hist_kernel<KeyT><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, n, shift, hist, tiles);
+        sort_scan_kernel<<<kRadix, 256, 0, st>>>(hist, tiles, totals);
+        sort_scatter_kernel<KeyT><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, vin, kout, vout, n, shift,
+                                                                                        hist, totals, tiles);
+        cur ^= 1;
+    }
+    return cur;
+}
+
+}  // namespace recsdk

@@ -1,0 +1,631 @@
+// Fused backward of the table-batched embedding op: gradient segment-sum over
+// deduplicated rows + sparse Adagrad / Adam / SGD row update, in place.
+//
+// Plan (all on one stream, no host sync, no atomics on floats):
+//   1. expand   : every index position p -> (key, val); key identifies the row
+//                 (hash_size_cumsum[t] + idx, or inverse[p] + unique_offsets[t]),
+//                 val packs (feature, sample) of the bag whose gradient row p takes.
+//   2. sort     : stable LSD radix sort of the pairs by key (prims.cuh).  Equal
+//                 keys stay in ascending position order -> fixed reduction order.
+//   3. runs     : head flags -> inclusive scan -> run id per position, run starts, U.
+//   4. chunks   : runs longer than C are cut into chunks of C positions; chunk
+//                 sums go to a partial buffer (keeps Zipf-hot rows off one warp).
+//   5. update   : G lanes per unique row: sum its gradient rows (or its chunk
+//                 sums) in order, apply the optimizer, write w / m1 / m2 once.
+//                 128-bit accesses; w, m1, m2 of a row are read and written
+//                 exactly once per step.
+// The float arithmetic uses explicit round-to-nearest intrinsics in the operand
+// order of the reference kernels (ComputeAdagrad / ComputeAdam / ComputeSgd).
+#include <math.h>
+
+#include "prims.cuh"
+
+namespace recsdk {
+
+constexpr int kChunk = 64;  // the only non-zero reduce_chunk supported
+
+struct BwdParams {
+    const float* __restrict__ grad;
+    float* __restrict__ w;
+    float* __restrict__ m1;
+    float* __restrict__ m2;
+    const int64_t* __restrict__ wofs;
+    const int32_t* __restrict__ dofs;
+    const int64_t* __restrict__ cumsum;
+    const int64_t* __restrict__ idx;
+    const int64_t* __restrict__ offs;
+    const int64_t* __restrict__ uid;
+    const int64_t* __restrict__ uoff;
+    const int64_t* __restrict__ uinv;
+    int64_t T, B, N;
+    int32_t total_D, max_D, mode, opt;
+    int32_t bshift;  // val = (feature << bshift) | sample
+    int32_t chunk;   // 0 or kChunk
+    float lr, eps, beta1, beta2, beta2sqrt, max_grad;
+    int32_t clip;
+    int64_t w_numel;
+    int64_t* status;
+    int base_aligned;
+    // plan arrays
+    const uint32_t* __restrict__ vals;   // sorted
+    const int* __restrict__ rid;         // [N] run id of sorted position
+    const int* __restrict__ run_start;   // [U+1]
+    const int* __restrict__ chunk_base;  // [N] exclusive scan of chunks per run
+    const int* __restrict__ chunk_desc;  // [chunks] start position of each chunk
+    float* __restrict__ partial;         // [chunks, max_D]
+    const int64_t* __restrict__ counters;  // {U, total_chunks}
+};
+
+// ---------------------------------------------------------------------------- 1. expand
+// feature of index position p in NONE mode: last t with offsets[t*B] <= p
+__device__ __forceinline__ int64_t feature_of_position(const int64_t* offs, int64_t T, int64_t B, int64_t p)
+{
+    int64_t lo = 0, hi = T - 1;
+    while (lo < hi) {
+        int64_t mid = (lo + hi + 1) >> 1;
+        if (offs[mid * B] <= p) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+template <typename KeyT>
+__global__ void __launch_bounds__(256) expand_pooled_kernel(BwdParams p, KeyT* __restrict__ keys,
+                                                            uint32_t* __restrict__ vals)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t num_bags = p.T * p.B;
+    const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t bag0 = ((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * 32; bag0 < num_bags;
+         bag0 += warps_total * 32) {
+        const int64_t bag = bag0 + lane;
+        const int64_t start = bag < num_bags ? p.offs[bag] : INT64_MAX;  // lane l: first position of bag0+l
+        const int64_t last_bag = (bag0 + 32 < num_bags) ? bag0 + 32 : num_bags;
+        const int64_t p0 = p.offs[bag0], p1 = p.offs[last_bag];
+        const uint32_t f_l = bag < num_bags ? static_cast<uint32_t>(bag / p.B) : 0u;
+        const uint32_t b_l = bag < num_bags ? static_cast<uint32_t>(bag - static_cast<int64_t>(f_l) * p.B) : 0u;
+        for (int64_t base = p0; base < p1; base += 32) {
+            const int64_t pos = base + lane;
+            // largest j with start_j <= pos (bags with equal starts are empty; the last one owns pos)
+            int j = 0;
+#pragma unroll
+            for (int step = 16; step >= 1; step >>= 1) {
+                const int cand = j + step;
+                const int64_t sc = __shfl_sync(kFullMask, start, cand & 31);
+                if (cand < 32 && sc <= pos) j = cand;
+            }
+            const uint32_t f = __shfl_sync(kFullMask, f_l, j);
+            const uint32_t b = __shfl_sync(kFullMask, b_l, j);
+            if (pos < p1) {
+                int64_t key = p.uid != nullptr ? p.uinv[pos] + p.uoff[f] : p.cumsum[f] + p.idx[pos];
+                keys[pos] = static_cast<KeyT>(key);
+                vals[pos] = (f << p.bshift) | b;
+            }
+        }
+    }
+}
+
+template <typename KeyT>
+__global__ void __launch_bounds__(256) expand_nobag_kernel(BwdParams p, KeyT* __restrict__ keys,
+                                                           uint32_t* __restrict__ vals)
+{
+    for (int64_t pos = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; pos < p.N;
+         pos += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t f = feature_of_position(p.offs, p.T, p.B, pos);
+        int64_t key = p.uid != nullptr ? p.uinv[pos] + p.uoff[f] : p.cumsum[f] + p.idx[pos];
+        keys[pos] = static_cast<KeyT>(key);
+        vals[pos] = static_cast<uint32_t>(pos);
+    }
+}
+
+// ---------------------------------------------------------------------------- 3. runs
+template <typename KeyT>
+__global__ void __launch_bounds__(256) head_flag_kernel(const KeyT* __restrict__ keys, int64_t n, int* __restrict__ flag)
+{
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        flag[i] = (i == 0 || keys[i] != keys[i - 1]) ? 1 : 0;
+}
+
+// rid_incl: inclusive scan of the head flags.  Writes rid = incl-1 in place,
+// run_start[rid] at heads, run_start[U] = n and counters[0] = U.
+template <typename KeyT>
+__global__ void __launch_bounds__(256) run_start_kernel(const KeyT* __restrict__ keys, int64_t n, int* __restrict__ rid,
+                                                        int* __restrict__ run_start, int64_t* __restrict__ counters)
+{
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int r = rid[i] - 1;
+        rid[i] = r;
+        if (i == 0 || keys[i] != keys[i - 1]) run_start[r] = static_cast<int>(i);
+        if (i == n - 1) {
+            run_start[r + 1] = static_cast<int>(n);
+            counters[0] = r + 1;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------- 4. chunks
+__global__ void __launch_bounds__(256) chunk_count_kernel(const int* __restrict__ run_start,
+                                                          const int64_t* __restrict__ counters, int64_t n,
+                                                          int* __restrict__ nch)
+{
+    const int64_t U = counters[0];
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < n;
+         r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        int c = 0;
+        if (r < U) {
+            const int len = run_start[r + 1] - run_start[r];
+            if (len > kChunk) c = (len + kChunk - 1) / kChunk;
+        }
+        nch[r] = c;
+    }
+}
+
+__global__ void __launch_bounds__(256) chunk_desc_kernel(const int* __restrict__ rid, const int* __restrict__ run_start,
+                                                         const int* __restrict__ chunk_base, int64_t n,
+                                                         int* __restrict__ desc)
+{
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int r = rid[i];
+        const int rs = run_start[r];
+        const int len = run_start[r + 1] - rs;
+        const int d = static_cast<int>(i) - rs;
+        if (len > kChunk && (d % kChunk) == 0) desc[chunk_base[r] + d / kChunk] = static_cast<int>(i);
+    }
+}
+
+// ---------------------------------------------------------------------------- gradient rows
+struct GradRow {
+    const float* ptr;
+    float scale;  // MEAN: 1/len
+};
+
+__device__ __forceinline__ GradRow grad_row_of(const BwdParams& p, uint32_t v)
+{
+    GradRow g;
+    g.scale = 1.0f;
+    if (p.mode == RECSDK_POOL_NONE) {
+        g.ptr = p.grad + static_cast<int64_t>(v) * p.max_D;
+    } else {
+        const uint32_t f = v >> p.bshift;
+        const uint32_t b = v & ((1u << p.bshift) - 1u);
+        g.ptr = p.grad + static_cast<int64_t>(b) * p.total_D + p.dofs[f];
+        if (p.mode == RECSDK_POOL_MEAN) {
+            const int64_t bag = static_cast<int64_t>(f) * p.B + b;
+            g.scale = __fdiv_rn(1.0f, static_cast<float>(p.offs[bag + 1] - p.offs[bag]));
+        }
+    }
+    return g;
+}
+
+__device__ __forceinline__ float prep_grad(const BwdParams& p, float g, float scale)
+{
+    if (p.clip) g = g < -p.max_grad ? -p.max_grad : (g > p.max_grad ? p.max_grad : g);
+    if (p.mode == RECSDK_POOL_MEAN) g = __fmul_rn(g, scale);
+    return g;
+}
+
+// Sum of the gradient rows of sorted positions [s, e), columns (cb+lane+k*G) (in
+// V::W-element vectors), in position order starting from zero.
+template <typename V, int G, int K>
+__device__ __forceinline__ void sum_grad_rows(const BwdParams& p, int s, int e, int cb, int lane, int nvec,
+                                              typename V::T (&acc)[K])
+{
+    int i = s;
+    for (; i + 4 <= e; i += 4) {
+        GradRow g[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) g[j] = grad_row_of(p, p.vals[i + j]);
+        typename V::T v[4][K];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const int c = cb + lane + k * G;
+                v[j][k] = c < nvec ? V::ld_stream(g[j].ptr + V::W * c) : V::zero();
+            }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const float sc = g[j].scale;
+                acc[k] = add4(acc[k], map4(v[j][k], [&](float x) { return prep_grad(p, x, sc); }));
+            }
+    }
+    for (; i < e; ++i) {
+        const GradRow g = grad_row_of(p, p.vals[i]);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int c = cb + lane + k * G;
+            typename V::T v = c < nvec ? V::ld_stream(g.ptr + V::W * c) : V::zero();
+            const float sc = g.scale;
+            acc[k] = add4(acc[k], map4(v, [&](float x) { return prep_grad(p, x, sc); }));
+        }
+    }
+}
+
+__device__ __forceinline__ void run_geometry(const BwdParams& p, uint32_t v0, int32_t& D, int64_t& wofs, int64_t& f)
+{
+    f = p.mode == RECSDK_POOL_NONE ? feature_of_position(p.offs, p.T, p.B, static_cast<int64_t>(v0))
+                                   : static_cast<int64_t>(v0 >> p.bshift);
+    D = p.dofs[f + 1] - p.dofs[f];
+    wofs = p.wofs[f];
+}
+
+__device__ __forceinline__ bool vec_ok_for(const BwdParams& p, int64_t wofs, int32_t D, int64_t f)
+{
+    return p.base_aligned && (((wofs | D | p.dofs[f] | p.total_D | p.max_D) & 3) == 0);
+}
+
+// ---------------------------------------------------------------------------- 4b. chunk sums
+template <typename V, int G, int K>
+__device__ __forceinline__ void partial_body(const BwdParams& p, int c, int lane)
+{
+    const int p0 = p.chunk_desc[c];
+    const int r = p.rid[p0];
+    const int re = p.run_start[r + 1];
+    const int e = (p0 + kChunk < re) ? p0 + kChunk : re;
+    int32_t D;
+    int64_t wofs, f;
+    run_geometry(p, p.vals[p0], D, wofs, f);
+    const int nvec = D / V::W;
+    float* out = p.partial + static_cast<int64_t>(c) * p.max_D;
+    for (int cb = 0; cb < nvec; cb += G * K) {
+        typename V::T acc[K];
+#pragma unroll
+        for (int k = 0; k < K; ++k) acc[k] = V::zero();
+        sum_grad_rows<V, G, K>(p, p0, e, cb, lane, nvec, acc);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int col = cb + lane + k * G;
+            if (col < nvec) V::st(out + V::W * col, acc[k]);
+        }
+    }
+}
+
+template <int G, int K>
+__global__ void __launch_bounds__(256) partial_kernel(BwdParams p)
+{
+    const int groups_per_block = blockDim.x / G;
+    const int lane = threadIdx.x % G;
+    const int64_t total = p.counters[1];
+    for (int64_t c = static_cast<int64_t>(blockIdx.x) * groups_per_block + threadIdx.x / G; c < total;
+         c += static_cast<int64_t>(gridDim.x) * groups_per_block) {
+        int32_t D;
+        int64_t wofs, f;
+        run_geometry(p, p.vals[p.chunk_desc[c]], D, wofs, f);
+        if (vec_ok_for(p, wofs, D, f))
+            partial_body<V4, G, K>(p, static_cast<int>(c), lane);
+        else
+            partial_body<V1, G, K>(p, static_cast<int>(c), lane);
+    }
+}
+
+// ---------------------------------------------------------------------------- 5. optimizer math
+// Operand order follows the reference vector kernels, one rounding per operation.
+template <int OPT>
+__device__ __forceinline__ void opt_update(const BwdParams& p, float g, float& w, float& m1, float& m2)
+{
+    if (OPT == RECSDK_OPT_ADAGRAD) {
+        // ComputeAdagrad, backward_codegen_adagrad_unweighted_exact_kernel_unique.h:50-62
+        const float g2 = __fmul_rn(g, g);
+        const float s = __fadd_rn(m1, g2);
+        const float den = __fadd_rn(__fsqrt_rn(s), p.eps);
+        const float q = __fdiv_rn(p.lr, den);
+        const float delta = __fmul_rn(__fmul_rn(q, g), -1.0f);
+        w = __fadd_rn(w, delta);
+        m1 = __fadd_rn(m1, g2);
+    } else if (OPT == RECSDK_OPT_ADAM) {
+        // ComputeAdam, backward_codegen_adam_unweighted_exact_kernel_unique.h:70-96
+        const float omb1 = 1.0f - p.beta1, omb2 = 1.0f - p.beta2;
+        const float step = __fmul_rn(-p.lr, p.beta2sqrt);
+        const float nm1 = __fadd_rn(__fmul_rn(m1, p.beta1), __fmul_rn(g, omb1));
+        const float nm2 = __fadd_rn(__fmul_rn(m2, p.beta2), __fmul_rn(__fmul_rn(g, g), omb2));
+        const float den = __fadd_rn(__fsqrt_rn(nm2), p.eps);
+        const float delta = __fmul_rn(__fdiv_rn(nm1, den), step);
+        w = __fadd_rn(w, delta);
+        m1 = nm1;
+        m2 = nm2;
+    } else {
+        // ComputeSgd, backward_codegen_sgd_unweighted_exact_kernel.h:107-124
+        w = __fadd_rn(w, __fmul_rn(g, -p.lr));
+    }
+}
+
+template <int OPT>
+__device__ __forceinline__ void opt_update_vec(const BwdParams& p, float4 g, float4& w, float4& m1, float4& m2)
+{
+    opt_update<OPT>(p, g.x, w.x, m1.x, m2.x);
+    opt_update<OPT>(p, g.y, w.y, m1.y, m2.y);
+    opt_update<OPT>(p, g.z, w.z, m1.z, m2.z);
+    opt_update<OPT>(p, g.w, w.w, m1.w, m2.w);
+}
+template <int OPT>
+__device__ __forceinline__ void opt_update_vec(const BwdParams& p, float g, float& w, float& m1, float& m2)
+{
+    opt_update<OPT>(p, g, w, m1, m2);
+}
+
+template <typename V, int G, int K, int OPT>
+__device__ __forceinline__ void update_body(const BwdParams& p, int r, int lane, int64_t row_off, int32_t D)
+{
+    const int rs = p.run_start[r], re = p.run_start[r + 1];
+    const int nvec = D / V::W;
+    const bool chunked = p.chunk > 0 && (re - rs) > kChunk;
+    for (int cb = 0; cb < nvec; cb += G * K) {
+        typename V::T acc[K], w[K], m1[K], m2[K];
+        // issue the row loads first so they overlap the gradient reduction
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int col = cb + lane + k * G;
+            acc[k] = V::zero();
+            w[k] = m1[k] = m2[k] = V::zero();
+            if (col < nvec) {
+                w[k] = V::ld(p.w + row_off + V::W * col);
+                if (OPT != RECSDK_OPT_SGD) m1[k] = V::ld(p.m1 + row_off + V::W * col);
+                if (OPT == RECSDK_OPT_ADAM) m2[k] = V::ld(p.m2 + row_off + V::W * col);
+            }
+        }
+        if (chunked) {
+            const int c0 = p.chunk_base[r];
+            const int nc = (re - rs + kChunk - 1) / kChunk;
+            for (int c = 0; c < nc; ++c) {
+                const float* pr = p.partial + static_cast<int64_t>(c0 + c) * p.max_D;
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    const int col = cb + lane + k * G;
+                    if (col < nvec) acc[k] = add4(acc[k], V::ld(pr + V::W * col));
+                }
+            }
+        } else {
+            sum_grad_rows<V, G, K>(p, rs, re, cb, lane, nvec, acc);
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int col = cb + lane + k * G;
+            if (col < nvec) {
+                opt_update_vec<OPT>(p, acc[k], w[k], m1[k], m2[k]);
+                V::st(p.w + row_off + V::W * col, w[k]);
+                if (OPT != RECSDK_OPT_SGD) V::st(p.m1 + row_off + V::W * col, m1[k]);
+                if (OPT == RECSDK_OPT_ADAM) V::st(p.m2 + row_off + V::W * col, m2[k]);
+            }
+        }
+    }
+}
+
+template <typename KeyT, int G, int K, int OPT>
+__global__ void __launch_bounds__(256) update_kernel(BwdParams p, const KeyT* __restrict__ keys)
+{
+    const int groups_per_block = blockDim.x / G;
+    const int lane = threadIdx.x % G;
+    const int64_t U = p.counters[0];
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * groups_per_block + threadIdx.x / G; r < U;
+         r += static_cast<int64_t>(gridDim.x) * groups_per_block) {
+        const int rs = p.run_start[r];
+        const int64_t key = static_cast<int64_t>(keys[rs]);
+        int32_t D;
+        int64_t wofs, f;
+        run_geometry(p, p.vals[rs], D, wofs, f);
+        const int64_t row = p.uid != nullptr ? p.uid[key] : key - p.cumsum[f];
+        const int64_t row_off = wofs + row * D;
+        if (p.w_numel > 0 && (row < 0 || row_off + D > p.w_numel)) {
+            set_status(p.status, RECSDK_ERR_INDEX_RANGE, row, row_off);
+            continue;
+        }
+        if (vec_ok_for(p, wofs, D, f))
+            update_body<V4, G, K, OPT>(p, static_cast<int>(r), lane, row_off, D);
+        else
+            update_body<V1, G, K, OPT>(p, static_cast<int>(r), lane, row_off, D);
+    }
+}
+
+// ---------------------------------------------------------------------------- host side
+struct BwdWorkspace {
+    void *keys_a, *keys_b;
+    uint32_t *vals_a, *vals_b, *sort_scratch;
+    int *rid, *run_start, *nch, *desc, *scan_scratch;
+    float* partial;
+    int64_t* counters;
+    size_t bytes;
+};
+
+static BwdWorkspace carve_bwd(void* base, int64_t N, int32_t max_D)
+{
+    WorkspaceCarver c(base);
+    BwdWorkspace w;
+    const size_t n = static_cast<size_t>(N > 0 ? N : 1);
+    const size_t max_chunks = 2 * n / kChunk + 2;
+    w.counters = c.take<int64_t>(8);
+    w.keys_a = c.take<uint64_t>(n);
+    w.keys_b = c.take<uint64_t>(n);
+    w.vals_a = c.take<uint32_t>(n);
+    w.vals_b = c.take<uint32_t>(n);
+    w.sort_scratch = c.take<uint32_t>(sort_scratch_u32(N));
+    w.rid = c.take<int>(n);
+    w.run_start = c.take<int>(n + 1);
+    w.nch = c.take<int>(n + 1);
+    w.desc = c.take<int>(max_chunks);
+    w.scan_scratch = c.take<int>(scan_scratch_ints(N));
+    w.partial = c.take<float>(max_chunks * static_cast<size_t>(max_D));
+    w.bytes = c.used();
+    return w;
+}
+
+static int bits_for(int64_t x)
+{
+    int b = 0;
+    while (b < 63 && (int64_t(1) << b) <= x) ++b;
+    return b < 1 ? 1 : b;
+}
+
+template <typename KeyT, int G, int K>
+static void launch_update(const BwdParams& p, const KeyT* keys, int64_t N, cudaStream_t st)
+{
+    const int groups_per_block = 256 / G;
+    const int grid = grid_for(N, groups_per_block, 8);
+    switch (p.opt) {
+        case RECSDK_OPT_ADAGRAD: update_kernel<KeyT, G, K, RECSDK_OPT_ADAGRAD><<<grid, 256, 0, st>>>(p, keys); break;
+        case RECSDK_OPT_ADAM: update_kernel<KeyT, G, K, RECSDK_OPT_ADAM><<<grid, 256, 0, st>>>(p, keys); break;
+        default: update_kernel<KeyT, G, K, RECSDK_OPT_SGD><<<grid, 256, 0, st>>>(p, keys); break;
+    }
+}
+
+template <int G, int K>
+static void launch_partial(const BwdParams& p, int64_t N, cudaStream_t st)
+{
+    const int groups_per_block = 256 / G;
+    const int grid = grid_for(2 * N / kChunk + 2, groups_per_block, 8);
+    partial_kernel<G, K><<<grid, 256, 0, st>>>(p);
+}
+
+#define RECSDK_DISPATCH_GK(vec_per_row, CALL)                 \
+    do {                                                      \
+        const int G__ = group_lanes_for(vec_per_row);         \
+        switch (G__) {                                        \
+            case 1: CALL(1, 1); break;                        \
+            case 2: CALL(2, 1); break;                        \
+            case 4: CALL(4, 1); break;                        \
+            case 8: CALL(8, 1); break;                        \
+            case 16: CALL(16, 1); break;                      \
+            default:                                          \
+                if ((vec_per_row) <= 32) { CALL(32, 1); }     \
+                else if ((vec_per_row) <= 64) { CALL(32, 2); } \
+                else { CALL(32, 4); }                         \
+                break;                                        \
+        }                                                     \
+    } while (0)
+
+template <typename KeyT>
+static int run_backward(const recsdk_tbe_backward_args* a, BwdParams p, const BwdWorkspace& ws, int key_bits,
+                        cudaStream_t st)
+{
+    const int64_t N = a->N;
+    KeyT* ka = static_cast<KeyT*>(ws.keys_a);
+    KeyT* kb = static_cast<KeyT*>(ws.keys_b);
+    // 1. expand
+    if (a->pooling_mode == RECSDK_POOL_NONE)
+        expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, ka, ws.vals_a);
+    else
+        expand_pooled_kernel<KeyT><<<grid_for(a->T * a->B, 8 * 32), 256, 0, st>>>(p, ka, ws.vals_a);
+    // 2. sort
+    const int which = radix_sort_pairs<KeyT>(ka, ws.vals_a, kb, ws.vals_b, N, key_bits, ws.sort_scratch, st);
+    const KeyT* keys = which ? kb : ka;
+    p.vals = which ? ws.vals_b : ws.vals_a;
+    // 3. runs
+    head_flag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(keys, N, ws.rid);
+    device_scan<true>(ws.rid, ws.rid, N, ws.scan_scratch, nullptr, st);
+    run_start_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(keys, N, ws.rid, ws.run_start, ws.counters);
+    p.rid = ws.rid;
+    p.run_start = ws.run_start;
+    p.counters = ws.counters;
+    const int vec_per_row = (a->max_D + 3) / 4;
+    // 4. chunk sums of long runs
+    if (a->reduce_chunk > 0) {
+        chunk_count_kernel<<<grid_for(N, 256), 256, 0, st>>>(ws.run_start, ws.counters, N, ws.nch);
+        device_scan<false>(ws.nch, ws.nch, N, ws.scan_scratch, ws.counters + 1, st);
+        chunk_desc_kernel<<<grid_for(N, 256), 256, 0, st>>>(ws.rid, ws.run_start, ws.nch, N, ws.desc);
+        p.chunk_base = ws.nch;
+        p.chunk_desc = ws.desc;
+        p.partial = ws.partial;
+#define CALL_PARTIAL(G, K) launch_partial<G, K>(p, N, st)
+        RECSDK_DISPATCH_GK(vec_per_row, CALL_PARTIAL);
+#undef CALL_PARTIAL
+    }
+    // 5. update
+    if (a->ev_update_start) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_update_start), st);
+#define CALL_UPDATE(G, K) launch_update<KeyT, G, K>(p, keys, N, st)
+    RECSDK_DISPATCH_GK(vec_per_row, CALL_UPDATE);
+#undef CALL_UPDATE
+    if (a->ev_update_stop) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_update_stop), st);
+    RECSDK_CUDA_CHECK_LAUNCH();
+    return RECSDK_OK;
+}
+
+}  // namespace recsdk
+
+using namespace recsdk;
+
+extern "C" float recsdk_adam_beta2sqrt(float beta1, float beta2, int64_t iter)
+{
+    // op_host/backward_codegen_adagrad_unweighted_exact.cpp:98-102: pow in double,
+    // each intermediate stored in a float.
+    const float b1 = static_cast<float>(1 - pow(static_cast<double>(beta1), static_cast<double>(iter)));
+    const float b2 = static_cast<float>(1 - pow(static_cast<double>(beta2), static_cast<double>(iter)));
+    return static_cast<float>(sqrt(static_cast<double>(b2)) / static_cast<double>(b1));
+}
+
+extern "C" size_t recsdk_tbe_backward_workspace_bytes(int64_t N, int32_t max_D)
+{
+    return carve_bwd(nullptr, N, max_D > 0 ? max_D : 1).bytes;
+}
+
+extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stream)
+{
+    if (a == nullptr) return RECSDK_ERR_INVALID_ARG;
+    if (a->T < 0 || a->B < 0 || a->N < 0 || a->max_D <= 0 || a->total_D <= 0) return RECSDK_ERR_INVALID_ARG;
+    if (a->N >= (int64_t(1) << 31)) return RECSDK_ERR_TOO_LARGE;
+    if (a->pooling_mode < RECSDK_POOL_SUM || a->pooling_mode > RECSDK_POOL_NONE) return RECSDK_ERR_INVALID_ARG;
+    if (a->optimizer < RECSDK_OPT_ADAGRAD || a->optimizer > RECSDK_OPT_SGD) return RECSDK_ERR_INVALID_ARG;
+    if (a->reduce_chunk != 0 && a->reduce_chunk != kChunk) return RECSDK_ERR_INVALID_ARG;
+    if (a->T == 0 || a->B == 0 || a->N == 0) return RECSDK_OK;
+    if (!a->grad_output || !a->dev_weights || !a->weights_offsets || !a->D_offsets || !a->indices || !a->offsets)
+        return RECSDK_ERR_INVALID_ARG;
+    if (a->optimizer != RECSDK_OPT_SGD && !a->momentum1) return RECSDK_ERR_INVALID_ARG;
+    if (a->optimizer == RECSDK_OPT_ADAM && !a->momentum2) return RECSDK_ERR_INVALID_ARG;
+    const bool have_unique = a->unique_ids != nullptr;
+    if (have_unique && (!a->unique_offsets || !a->unique_inverse || a->num_unique_capacity <= 0))
+        return RECSDK_ERR_INVALID_ARG;
+    if (!have_unique && !a->hash_size_cumsum) return RECSDK_ERR_INVALID_ARG;
+    if (!a->workspace) return RECSDK_ERR_WORKSPACE;
+    const BwdWorkspace ws = carve_bwd(a->workspace, a->N, a->max_D);
+    if (ws.bytes > a->workspace_bytes) return RECSDK_ERR_WORKSPACE;
+
+    int bshift = bits_for(a->B - 1 > 0 ? a->B - 1 : 1);
+    if (a->pooling_mode != RECSDK_POOL_NONE && bshift + bits_for(a->T) > 32) return RECSDK_ERR_TOO_LARGE;
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    BwdParams p{};
+    p.grad = a->grad_output;
+    p.w = a->dev_weights;
+    p.m1 = a->momentum1;
+    p.m2 = a->momentum2;
+    p.wofs = a->weights_offsets;
+    p.dofs = a->D_offsets;
+    p.cumsum = a->hash_size_cumsum;
+    p.idx = a->indices;
+    p.offs = a->offsets;
+    p.uid = a->unique_ids;
+    p.uoff = a->unique_offsets;
+    p.uinv = a->unique_inverse;
+    p.T = a->T;
+    p.B = a->B;
+    p.N = a->N;
+    p.total_D = a->total_D;
+    p.max_D = a->max_D;
+    p.mode = a->pooling_mode;
+    p.opt = a->optimizer;
+    p.bshift = bshift;
+    p.chunk = a->reduce_chunk;
+    p.lr = a->learning_rate;
+    p.eps = a->eps;
+    p.beta1 = a->beta1;
+    p.beta2 = a->beta2;
+    p.beta2sqrt = a->optimizer == RECSDK_OPT_ADAM ? recsdk_adam_beta2sqrt(a->beta1, a->beta2, a->iter) : 0.f;
+    p.max_grad = a->max_gradient;
+    p.clip = a->gradient_clipping;
+    p.w_numel = a->weights_numel;
+    p.status = a->dev_status;
+    p.base_aligned = (aligned16(a->grad_output) && aligned16(a->dev_weights) && aligned16(a->momentum1) &&
+                      aligned16(a->momentum2) && aligned16(ws.partial))
+                         ? 1
+                         : 0;
+
+    int key_bits;
+    if (have_unique)
+        key_bits = bits_for(a->num_unique_capacity);
+    else
+        key_bits = (a->total_hash_size_bits > 0 && a->total_hash_size_bits <= 64) ? a->total_hash_size_bits : 64;
+    if (key_bits <= 32) return run_backward<uint32_t>(a, p, ws, key_bits, st);
+    return run_backward<uint64_t>(a, p, ws, key_bits, st);
+}

@@ -1,0 +1,298 @@
+"""Functional front end of the C ABI for torch CUDA tensors.
+
+torch is used only for device memory and streams: every function here checks
+its arguments, allocates outputs / workspace with torch, and calls one C-ABI
+entry point of ``librecsdk_b200.so`` on the current CUDA stream.  There is no
+CPU or pure-PyTorch path: CPU tensors are rejected.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import (OPT_ADAGRAD, OPT_ADAM, OPT_SGD, POOL_MEAN, POOL_NONE, POOL_SUM, RecsdkError, check)  # noqa: F401
+
+_STATUS_MESSAGES = {
+    _lib.ERR_NEGATIVE_KEY: "Invalid key value: {d0}",
+    _lib.ERR_TABLE_FULL: "Ids map reached maxIndex = {d0} please reallocate a larger buffer.",
+    _lib.ERR_CACHE_TOO_SMALL: "cacheSize_ too small",
+    _lib.ERR_INDEX_RANGE: "row index {d0} out of range (offset {d1})",
+    _lib.ERR_HASH_FULL: "key table has no free entry (key {d0})",
+    _lib.ERR_TOO_LARGE: "size {d0} beyond the maximum {d1}",
+}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def _chk(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (recsdk_b200 has no CPU path)")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} tensor type mismatch: expected {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    return t
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(_lib.STATUS_WORDS, dtype=torch.int64, device=device)
+
+
+def raise_on_status(status: torch.Tensor, where: str = "") -> None:
+    """Synchronises and raises RuntimeError with the reference's wording when a kernel recorded an error."""
+    code, d0, d1, _ = status.tolist()
+    if code != 0:
+        status.zero_()
+        msg = _STATUS_MESSAGES.get(code, _lib.error_string(code)).format(d0=d0, d1=d1)
+        err = RecsdkError(code, where)
+        err.args = (f"{where}: {msg}" if where else msg,)
+        raise err
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+# --------------------------------------------------------------------------- A6 forward
+def tbe_forward(dev_weights, weights_offsets, D_offsets, indices, offsets, total_D: int, max_D: int,
+                pooling_mode: int, status: Optional[torch.Tensor] = None, bounds_check: bool = True,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _lib.load()
+    _chk(dev_weights, torch.float32, "dev_weights")
+    _chk(weights_offsets, torch.int64, "weights_offsets")
+    _chk(D_offsets, torch.int32, "D_offsets")
+    _chk(indices, torch.int64, "indices")
+    _chk(offsets, torch.int64, "offsets")
+    T = weights_offsets.numel()
+    if T == 0 or (offsets.numel() - 1) % T != 0:
+        raise RuntimeError(f"offset size = {offsets.numel()} is incorrect for feature count = {T}")
+    B = (offsets.numel() - 1) // T
+    N = indices.numel()
+    shape = (N, max_D) if pooling_mode == POOL_NONE else (B, total_D)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32, device=dev_weights.device)
+    else:
+        _chk(out, torch.float32, "out")
+        assert tuple(out.shape) == shape
+    a = _lib.TbeForwardArgs(_ptr(dev_weights), _ptr(weights_offsets), _ptr(D_offsets), _ptr(indices), _ptr(offsets),
+                            _ptr(out), T, B, N, total_D, max_D, pooling_mode,
+                            dev_weights.numel() if bounds_check else 0, _ptr(status))
+    check(lib.recsdk_tbe_forward(C.byref(a), _stream()), "recsdk_tbe_forward")
+    return out
+
+
+# --------------------------------------------------------------------------- A1 sorted unique
+def unique_sorted(ids: torch.Tensor, key_bits: int = 64) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (unique_buffer[n], inverse[n], num_unique[1]); the first num_unique entries of the buffer are valid."""
+    lib = _lib.load()
+    _chk(ids, torch.int64, "ids")
+    n = ids.numel()
+    dev = ids.device
+    uniq = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
+    inv = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
+    cnt = torch.zeros(1, dtype=torch.int64, device=dev)
+    wsz = lib.recsdk_unique_sorted_workspace_bytes(n)
+    ws = _workspace(wsz, dev)
+    check(lib.recsdk_unique_sorted(_ptr(ids), n, key_bits, _ptr(uniq), _ptr(inv), _ptr(cnt), _ptr(ws), ws.numel(),
+                                   _stream()), "recsdk_unique_sorted")
+    return uniq, inv[:n], cnt
+
+
+# --------------------------------------------------------------------------- A7 backward
+def tbe_backward_workspace_bytes(N: int, max_D: int) -> int:
+    return _lib.load().recsdk_tbe_backward_workspace_bytes(N, max_D)
+
+
+def tbe_backward(grad_output, dev_weights, momentum1, momentum2, weights_offsets, D_offsets, hash_size_cumsum,
+                 indices, offsets, total_D: int, max_D: int, pooling_mode: int, optimizer: int,
+                 learning_rate: float, eps: float = 0.0, beta1: float = 0.9, beta2: float = 0.999, iter: int = 1,
+                 unique_ids=None, unique_offsets=None, unique_inverse=None, total_hash_size_bits: int = 0,
+                 reduce_chunk: int = 64, gradient_clipping: bool = False, max_gradient: float = 0.0,
+                 status: Optional[torch.Tensor] = None, bounds_check: bool = True,
+                 workspace: Optional[torch.Tensor] = None, update_events=None) -> None:
+    """``update_events``: optional (start, stop) torch.cuda.Event pair (created with enable_timing=True and
+    recorded at least once before) that the library records around the row-update kernel."""
+    lib = _lib.load()
+    _chk(grad_output, torch.float32, "grad_output")
+    _chk(dev_weights, torch.float32, "dev_weights")
+    if momentum1 is not None:
+        _chk(momentum1, torch.float32, "momentum1")
+    if momentum2 is not None:
+        _chk(momentum2, torch.float32, "momentum2")
+    _chk(weights_offsets, torch.int64, "weights_offsets")
+    _chk(D_offsets, torch.int32, "D_offsets")
+    _chk(indices, torch.int64, "indices")
+    _chk(offsets, torch.int64, "offsets")
+    have_unique = unique_ids is not None and unique_ids.numel() > 0
+    if have_unique:
+        _chk(unique_ids, torch.int64, "unique_ids")
+        _chk(unique_offsets, torch.int64, "unique_offsets")
+        _chk(unique_inverse, torch.int64, "unique_inverse")
+    else:
+        _chk(hash_size_cumsum, torch.int64, "hash_size_cumsum")
+    T = weights_offsets.numel()
+    B = (offsets.numel() - 1) // T
+    N = indices.numel()
+    wsz = lib.recsdk_tbe_backward_workspace_bytes(N, max_D)
+    if workspace is None or workspace.numel() < wsz:
+        workspace = _workspace(wsz, dev_weights.device)
+    a = _lib.TbeBackwardArgs()
+    a.grad_output = _ptr(grad_output)
+    a.dev_weights = _ptr(dev_weights)
+    a.momentum1 = _ptr(momentum1)
+    a.momentum2 = _ptr(momentum2)
+    a.weights_offsets = _ptr(weights_offsets)
+    a.D_offsets = _ptr(D_offsets)
+    a.hash_size_cumsum = _ptr(hash_size_cumsum) if hash_size_cumsum is not None else None
+    a.indices = _ptr(indices)
+    a.offsets = _ptr(offsets)
+    a.unique_ids = _ptr(unique_ids) if have_unique else None
+    a.unique_offsets = _ptr(unique_offsets) if have_unique else None
+    a.unique_inverse = _ptr(unique_inverse) if have_unique else None
+    a.T, a.B, a.N = T, B, N
+    a.num_unique_capacity = unique_ids.numel() if have_unique else 0
+    a.total_D, a.max_D = total_D, max_D
+    a.pooling_mode, a.optimizer = pooling_mode, optimizer
+    a.total_hash_size_bits = total_hash_size_bits
+    a.reduce_chunk = reduce_chunk
+    a.learning_rate, a.eps, a.beta1, a.beta2 = learning_rate, eps, beta1, beta2
+    a.iter = iter
+    a.gradient_clipping = int(gradient_clipping)
+    a.max_gradient = max_gradient
+    a.weights_numel = dev_weights.numel() if bounds_check else 0
+    a.dev_status = _ptr(status)
+    a.workspace = _ptr(workspace)
+    a.workspace_bytes = workspace.numel()
+    if update_events is not None:
+        a.ev_update_start = update_events[0].cuda_event
+        a.ev_update_stop = update_events[1].cuda_event
+    check(lib.recsdk_tbe_backward(C.byref(a), _stream()), "recsdk_tbe_backward")
+
+
+def adam_beta2sqrt(beta1: float, beta2: float, it: int) -> float:
+    return _lib.load().recsdk_adam_beta2sqrt(beta1, beta2, it)
+
+
+# --------------------------------------------------------------------------- A8 rows by slot
+def gather_rows(table: torch.Tensor, slots: torch.Tensor, D: int, status=None) -> torch.Tensor:
+    lib = _lib.load()
+    _chk(table, torch.float32, "table")
+    _chk(slots, torch.int64, "slots")
+    out = torch.empty((slots.numel(), D), dtype=torch.float32, device=table.device)
+    check(lib.recsdk_gather_rows(_ptr(table), _ptr(slots), slots.numel(), D, _ptr(out), table.numel() // D,
+                                 _ptr(status), _stream()), "recsdk_gather_rows")
+    return out
+
+
+def scatter_rows(table: torch.Tensor, slots: torch.Tensor, D: int, rows: torch.Tensor, status=None) -> None:
+    lib = _lib.load()
+    _chk(table, torch.float32, "table")
+    _chk(slots, torch.int64, "slots")
+    _chk(rows, torch.float32, "rows")
+    assert rows.numel() == slots.numel() * D
+    check(lib.recsdk_scatter_rows(_ptr(table), _ptr(slots), slots.numel(), D, _ptr(rows), table.numel() // D,
+                                  _ptr(status), _stream()), "recsdk_scatter_rows")
+
+
+# --------------------------------------------------------------------------- A9 TF-flavour ops
+def embedding_lookup_by_address(address: torch.Tensor, embedding_dim: int, embedding_type: int = 0) -> torch.Tensor:
+    lib = _lib.load()
+    _chk(address, torch.int64, "address")
+    if embedding_type != 0:
+        raise RuntimeError("only fp32 (embedding_type 0) is supported")
+    out = torch.empty((address.numel(), embedding_dim), dtype=torch.float32, device=address.device)
+    check(lib.recsdk_lookup_by_address(_ptr(address), address.numel(), embedding_dim, _ptr(out), _stream()),
+          "recsdk_lookup_by_address")
+    return out
+
+
+def embedding_update_by_address(address: torch.Tensor, embedding: torch.Tensor, update_type: int = 0) -> None:
+    lib = _lib.load()
+    _chk(address, torch.int64, "address")
+    _chk(embedding, torch.float32, "embedding")
+    dim = embedding.shape[-1]
+    check(lib.recsdk_update_by_address(_ptr(address), address.numel(), dim, _ptr(embedding), update_type,
+                                       _stream()), "recsdk_update_by_address")
+
+
+def lazy_adam(gradient, indices, m, v, var, lr: float, beta1: float, beta2: float, epsilon: float) -> None:
+    lib = _lib.load()
+    _chk(gradient, torch.float32, "gradient")
+    _chk(indices, torch.int32, "indices")
+    for t, nme in ((m, "inputM"), (v, "inputV"), (var, "inputVar")):
+        _chk(t, torch.float32, nme)
+    dim = gradient.shape[-1]
+    check(lib.recsdk_lazy_adam(_ptr(gradient), _ptr(indices), indices.numel(), dim, _ptr(m), _ptr(v), _ptr(var), lr,
+                               beta1, beta2, epsilon, _stream()), "recsdk_lazy_adam")
+
+
+def sgd(gradient, indices, var, lr: float, weight_decay: Optional[float] = None) -> None:
+    lib = _lib.load()
+    _chk(gradient, torch.float32, "gradient")
+    _chk(indices, torch.int64, "indices")
+    _chk(var, torch.float32, "inputVar")
+    dim = gradient.shape[-1]
+    ws = _workspace(gradient.numel() * 4, var.device) if weight_decay is not None else None
+    check(lib.recsdk_sgd(_ptr(gradient), _ptr(indices), indices.numel(), dim, _ptr(var), lr, weight_decay or 0.0,
+                         int(weight_decay is not None), _ptr(ws), ws.numel() if ws is not None else 0, _stream()),
+          "recsdk_sgd")
+
+
+# --------------------------------------------------------------------------- A10 restore
+def restore(unique_indices, unique_inverse, unique_offset, offsets_per_table, hash_indices=None) -> torch.Tensor:
+    lib = _lib.load()
+    _chk(unique_indices, torch.int64, "uniqueIndices")
+    _chk(unique_inverse, torch.int64, "uniqueInverse")
+    _chk(unique_offset, torch.int64, "uniqueOffset")
+    if not isinstance(offsets_per_table, torch.Tensor):
+        offsets_per_table = torch.tensor(list(offsets_per_table), dtype=torch.int64, device=unique_inverse.device)
+    _chk(offsets_per_table, torch.int64, "offsetsPerTable")
+    n = unique_inverse.numel()
+    if hash_indices is None:
+        hash_indices = torch.empty(n, dtype=torch.int64, device=unique_inverse.device)
+    elif hash_indices.numel() != n:
+        raise RuntimeError("hashIndices length must equal uniqueInverse length")
+    check(lib.recsdk_restore(_ptr(unique_indices), _ptr(unique_inverse), _ptr(unique_offset),
+                             _ptr(offsets_per_table), offsets_per_table.numel() - 1, n, _ptr(hash_indices),
+                             _stream()), "recsdk_restore")
+    return hash_indices
+
+
+# --------------------------------------------------------------------------- A3 bucketize
+def bucketize(lengths, indices, num_features: int, world: int, do_unique: bool = False, return_count: bool = False):
+    """Returns (new_lengths[W*F*B], new_indices_buffer[N], unbucketize_permute[N], ids_counts_buffer[N] or None,
+    num_out[1]); with do_unique only the first num_out entries of new_indices / ids_counts are valid."""
+    lib = _lib.load()
+    _chk(lengths, torch.int64, "lengths")
+    _chk(indices, torch.int64, "indices")
+    if lengths.numel() == 0:
+        raise RuntimeError("Lengths tensor is an empty tensor")
+    if indices.numel() == 0:
+        raise RuntimeError("Indices tensor is an empty tensor")
+    if world <= 0:
+        raise RuntimeError("Bucket size must be greater than 0")
+    dev = indices.device
+    n, L = indices.numel(), lengths.numel()
+    new_lengths = torch.empty(L * world, dtype=torch.int64, device=dev)
+    new_indices = torch.empty(n, dtype=torch.int64, device=dev)
+    perm = torch.empty(n, dtype=torch.int64, device=dev)
+    counts = torch.empty(n, dtype=torch.int64, device=dev) if (do_unique and return_count) else None
+    num_out = torch.zeros(1, dtype=torch.int64, device=dev)
+    ws = _workspace(lib.recsdk_bucketize_workspace_bytes(n, L, world), dev)
+    check(lib.recsdk_bucketize(_ptr(lengths), L, _ptr(indices), n, num_features, world, int(do_unique),
+                               int(return_count), _ptr(new_lengths), _ptr(new_indices), _ptr(perm), _ptr(counts),
+                               _ptr(num_out), _ptr(ws), ws.numel(), _stream()), "recsdk_bucketize")
+    return new_lengths, new_indices, perm, counts, num_out
