@@ -1,0 +1,448 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-embedding hot path: one step = pooled gather forward + fused backward
+(dedup, gradient segment-sum, sparse Adam) over one synthetic batch of the DLRM-style config
+(26 tables, rows log-uniform in [1e3, 4e7] from seed 2025, dim 128 fp32, batch 65536, one id per
+field ~ Zipf(1.1), Adam lr 1e-3 beta .9/.999 eps 1e-8).
+
+    python bench.py --gpus N --steps K --warmup W            our arm (CUDA kernels through the C ABI)
+    python bench.py --impl reference --gpus N ...            CPU arm: the reference path's CPU restatement
+                                                             on the host cores (bounded sample)
+
+Prints ONE JSON line.  `value` = embedding ids/s with inputs resident in HBM; `e2e` = the same metric through
+the module API with host index buffers (H2D of indices/offsets and a D2H read of the result inside the timed
+region); `roofline` = the row-update kernel's algorithmic bytes / its CUDA-event time against the measured copy
+peak; `cpu_baseline` = the CPU oracle on a bounded sample of the same workload.
+
+Multi-GPU (torchrun, one rank per GPU): tables are sharded table-wise by greedy byte balance; every rank runs
+the hot path on its own tables for the full batch; pooled outputs go back to the sample owners with one NCCL
+all-to-all and the gradients return the same way (weak scaling: per-GPU batch is fixed, the global batch grows).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SEED = 2025
+N_TABLES = 26
+DIM = 128
+BATCH = 65536
+ALPHA = 1.1
+LR, BETA1, BETA2, EPS = 1e-3, 0.9, 0.999, 1e-8
+# Adam state is 3 x rows x 512 B.  The 26 seeded tables hold 144.9 M rows = 222 GB, more than one
+# GPU's HBM, so single-GPU runs cap every table at this many rows (Zipf ids are drawn over the capped vocab).
+ROW_CAP_1GPU = 16_000_000
+HBM_BUDGET_BYTES = 150e9
+
+
+def seeded_rows():
+    from recsdk_b200.synthetic import table_rows_log_uniform
+
+    return table_rows_log_uniform(SEED, N_TABLES, 1e3, 4e7)
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ============================================================================ our arm
+def greedy_table_placement(rows, world):
+    """Table-wise sharding: biggest table first onto the least loaded rank (bytes)."""
+    load = [0] * world
+    owner = [0] * len(rows)
+    for t in sorted(range(len(rows)), key=lambda i: -rows[i]):
+        r = min(range(world), key=lambda k: load[k])
+        owner[t] = r
+        load[r] += rows[t]
+    return owner
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from recsdk_b200 import ops
+    from recsdk_b200.synthetic import make_layout, one_hot_batch
+    from recsdk_b200.tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    rows_all = seeded_rows()
+    row_cap = None
+    if world == 1:
+        row_cap = ROW_CAP_1GPU
+        rows_all = [min(r, row_cap) for r in rows_all]
+    owner = greedy_table_placement(rows_all, world)
+    my_tables = [t for t in range(N_TABLES) if owner[t] == rank]
+    rows = [rows_all[t] for t in my_tables]
+    state_bytes = sum(rows) * DIM * 4 * 3
+    assert state_bytes < HBM_BUDGET_BYTES + 20e9, f"rank {rank}: {state_bytes / 1e9:.1f} GB of table state"
+    T = len(rows)
+    B = BATCH * world  # a table owner sees the samples of every rank (weak scaling: BATCH per GPU)
+
+    module = HybridSplitTableBatchedEmbeddingBagsCodegen(
+        [(r, DIM) for r in rows], optimizer=EmbOptimType.ADAM, pooling_mode=PoolingMode.SUM, learning_rate=LR,
+        eps=EPS, beta1=BETA1, beta2=BETA2, device=dev, weights_init=(-0.01, 0.01), seed=SEED + rank)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 17 * rank)
+    n_batches = 4  # rotate distinct batches so consecutive steps touch different rows
+    batches = [one_hot_batch(gen, rows, B, ALPHA, dev) for _ in range(n_batches)]
+    ids_per_step_rank = T * B
+    grad = torch.randn((B, T * DIM), generator=gen, device=dev, dtype=torch.float32)
+    out = torch.empty((B, T * DIM), device=dev, dtype=torch.float32)
+    # output/gradient exchange buffers of the table-wise layout (multi-GPU only)
+    if world > 1:
+        a2a_out = torch.empty_like(out)
+        a2a_grad = torch.empty_like(grad)
+
+    ev_pairs = []
+
+    def step_resident(i, timed=False):
+        idx, offs = batches[i % n_batches]
+        module.forward_into(idx, offs, out)
+        if world > 1:
+            # pooled rows of my tables for every rank's samples -> sample owners; gradients come back
+            dist.all_to_all_single(a2a_out.view(world, -1), out.view(world, -1))
+            dist.all_to_all_single(a2a_grad.view(world, -1), grad.view(world, -1))
+            g = a2a_grad
+        else:
+            g = grad
+        evs = None
+        if timed:
+            evs = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            for e in evs:
+                e.record()  # torch creates the CUDA event on first record; the library re-records it
+            ev_pairs.append(evs)
+        module.backward_from(g, idx, offs, update_events=evs)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step_resident(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(args.steps):
+        step_resident(args.warmup + i, timed=True)
+    t1.record()
+    barrier()
+    ms_total = t0.elapsed_time(t1)
+    upd_ms = [a.elapsed_time(b) for a, b in ev_pairs]
+    U, n_chunks, n_long = module.last_plan_counters()
+
+    # ---- end to end through the module API with host index buffers.  The caller's pipeline double-buffers
+    # the H2D copy of the next batch on a copy stream (the reference pipeline's dedicated memcpy stream,
+    # torchrec_embcache/distributed/train_pipeline.py:115-119); every step's copy is inside the timed region.
+    host = [(idx.cpu().pin_memory(), offs.cpu().pin_memory()) for idx, offs in batches]
+    d_bufs = [(torch.empty_like(batches[0][0]), torch.empty_like(batches[0][1])) for _ in range(2)]
+    copy_stream = torch.cuda.Stream(device=dev)
+    copied = [torch.cuda.Event(), torch.cuda.Event()]
+    consumed = [torch.cuda.Event(), torch.cuda.Event()]
+    result_host = torch.empty(4096, dtype=torch.float32).pin_memory()
+    main_stream = torch.cuda.current_stream()
+
+    def prefetch(i):
+        h_idx, h_offs = host[i % n_batches]
+        d_idx, d_offs = d_bufs[i % 2]
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[i % 2])
+            d_idx.copy_(h_idx, non_blocking=True)
+            d_offs.copy_(h_offs, non_blocking=True)
+            copied[i % 2].record(copy_stream)
+
+    def step_e2e(i, last):
+        if not last:
+            prefetch(i + 1)
+        d_idx, d_offs = d_bufs[i % 2]
+        main_stream.wait_event(copied[i % 2])
+        o = module(d_idx, d_offs)  # autograd-tracked lookup; backward runs the fused optimizer
+        if world > 1:
+            dist.all_to_all_single(a2a_out.view(world, -1), o.detach().view(world, -1))
+            dist.all_to_all_single(a2a_grad.view(world, -1), grad.view(world, -1))
+            o.backward(a2a_grad)
+        else:
+            o.backward(grad)
+        consumed[i % 2].record(main_stream)
+        result_host.copy_(o.detach().view(-1)[:4096], non_blocking=True)
+
+    def run_e2e(n):
+        for e in consumed:
+            e.record(main_stream)
+        prefetch(0)
+        for i in range(n):
+            step_e2e(i, i == n - 1)
+
+    run_e2e(max(args.warmup, 3))
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run_e2e(args.steps)
+    e1.record()
+    barrier()
+    e2e_ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # max over ranks
+    if world > 1:
+        tt = torch.tensor([ms_total, e2e_ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms_total = tt.tolist()
+        ids_t = torch.tensor([ids_per_step_rank], device=dev, dtype=torch.float64)
+        dist.all_reduce(ids_t)
+        ids_per_step = int(ids_t.item())
+    else:
+        ids_per_step = ids_per_step_rank
+
+    if rank == 0:
+        ms_step = ms_total / args.steps
+        value = ids_per_step / (ms_step * 1e-3)
+        e2e_ms_step = e2e_ms_total / args.steps
+        peak, peak_kind = measured_peak_gbs()
+        S = 2  # Adam state slots
+        N = ids_per_step_rank
+        # algorithmic bytes of one row-update launch: per unique row read+write of w, m, v and three 4-byte
+        # plan entries; per index that it reduces itself (runs of <= 64) the gradient row and its 4-byte
+        # (feature, sample) tag; per chunk sum of a longer run one row of the partial buffer.  The gradient
+        # rows of chunked runs are read by partial_kernel and are not counted here.
+        upd_bytes = U * (4 * DIM * 2 * (1 + S) + 12) + (N - n_long) * (4 * DIM + 4) + n_chunks * 4 * DIM
+        upd_ms_avg = sum(upd_ms) / len(upd_ms)
+        achieved = upd_bytes / (upd_ms_avg * 1e-3) / 1e9
+        # whole step, SURVEY formula: dedup + fwd + bwd
+        step_bytes = (16 * N + 8 * U) + (N * (8 + 4 * DIM) + 8 * (N + 1) + 4 * DIM * N) + \
+                     (4 * DIM * N + 8 * N + 8 * U + U * 4 * DIM * 2 * (1 + S))
+        passes = math.ceil(module.total_hash_size_bits / 8)
+        launches_per_step = 1 + (1 + 3 * passes + 3 + 1 + 1 + 1)  # forward + expand, sort, run scan, plan, partial, update
+        line = {
+            "metric": "embedding ids/sec (fwd+bwd+sparse Adam)",
+            "value": value,
+            "unit": "ids/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": ms_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f32",
+            "data": "synthetic",
+            "config": {
+                "workload": "configs[1]: 26 tables dim 128 fp32, batch 65536 per GPU one-hot Zipf(1.1), sparse Adam, "
+                            "table-wise sharding",
+                "tables_this_rank": T, "rows_this_rank": sum(rows), "row_cap": row_cap,
+                "table_state_gb_this_rank": round(state_bytes / 1e9, 1),
+                "ids_per_step": ids_per_step, "unique_rows_per_step_rank0": U,
+                "indices_in_chunked_runs_rank0": n_long, "chunk_sums_rank0": n_chunks,
+                "l2": "inputs larger than L2: 872 MB output + 872 MB gradient + 2.6 GB of touched rows per step; "
+                      f"{n_batches} distinct batches rotate",
+                "reduce_chunk": 64,
+            },
+            "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+            "step_hbm_frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+            "roofline": {"kernel": "update_kernel<Adam>", "bound": "hbm", "achieved": achieved, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "bytes_per_launch": upd_bytes, "ms_per_launch": upd_ms_avg, "traffic": None},
+            "e2e": {"value": ids_per_step / (e2e_ms_step * 1e-3), "unit": "ids/s", "ms_per_step": e2e_ms_step,
+                    "h2d_bytes_per_step": int(d_bufs[0][0].numel() * 8 + d_bufs[0][1].numel() * 8),
+                    "d2h_bytes_per_step": int(result_host.numel() * 4)},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_sample(budget_s=args.cpu_budget)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ============================================================================ CPU arms (oracle)
+CPU_SAMPLE_ROW_CAP = 262_144
+CPU_SAMPLE_BATCH = 8192
+
+
+def _cpu_sample_setup():
+    """Bounded sample of the workload for the CPU legs: all 26 tables with rows capped at 262144
+    (4.4 GB of fp32 Adam state) and 8192 of the 65536 samples per step."""
+    import numpy as np
+
+    from oracle import port
+
+    rows = [min(r, CPU_SAMPLE_ROW_CAP) for r in seeded_rows()]
+    T, B = len(rows), CPU_SAMPLE_BATCH
+    rng = np.random.default_rng(SEED)
+    wo = np.concatenate([[0], np.cumsum([r * DIM for r in rows])]).astype(np.int64)
+    do = (np.arange(T + 1) * DIM).astype(np.int32)
+    hs = np.concatenate([[0], np.cumsum(rows)]).astype(np.int64)
+    w = rng.uniform(-0.01, 0.01, int(wo[-1])).astype(np.float32)
+    m1 = np.zeros_like(w)
+    m2 = np.zeros_like(w)
+    idx = []
+    for r in rows:
+        p = np.arange(1, r + 1, dtype=np.float64) ** (-ALPHA)
+        cdf = np.cumsum(p)
+        u = rng.random(B) * cdf[-1]
+        idx.append(np.minimum(np.searchsorted(cdf, u), r - 1))
+    idx = np.concatenate(idx).astype(np.int64)
+    offs = np.arange(T * B + 1, dtype=np.int64)
+    grad = rng.standard_normal((B, T * DIM)).astype(np.float32)
+    return port, dict(T=T, B=B, wo=wo[:-1].copy(), do=do, hs=hs, w=w, m1=m1, m2=m2, idx=idx, offs=offs, grad=grad)
+
+
+def _cpu_step(port, c, it):
+    out = port.tbe_forward(c["w"], c["wo"], c["do"], c["idx"], c["offs"], c["T"], c["B"], c["T"] * DIM, DIM, 0)
+    port.tbe_backward(c["grad"], c["w"], c["m1"], c["m2"], c["wo"], c["do"], c["hs"], c["idx"], c["offs"], c["T"],
+                      c["B"], c["T"] * DIM, DIM, 0, 2, LR, EPS, BETA1, BETA2, it)
+    return out
+
+
+def cpu_baseline_sample(budget_s: float = 15.0):
+    port, c = _cpu_sample_setup()
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    _cpu_step(port, c, 1)
+    t0 = time.perf_counter()
+    n = 0
+    while time.perf_counter() - t0 < budget_s and n < 50:
+        _cpu_step(port, c, n + 2)
+        n += 1
+    dt = time.perf_counter() - t0
+    ids = c["T"] * c["B"] * n
+    return {"value": ids / dt, "unit": "ids/s", "cores": cores, "kind": "port",
+            "sample": f"{n} steps of 26 tables (rows capped at {CPU_SAMPLE_ROW_CAP}) x {CPU_SAMPLE_BATCH} samples, "
+                      "oracle C restatement with OpenMP (forward + fused backward + Adam)"}
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path: its Ascend kernels have no CPU build, so this arm times
+    the CPU restatement of those kernels (oracle/oracle.c, OpenMP over all host cores) on a bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    port, c = _cpu_sample_setup()
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    for i in range(args.warmup):
+        _cpu_step(port, c, i + 1)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        _cpu_step(port, c, args.warmup + i + 1)
+    dt = time.perf_counter() - t0
+    ids = c["T"] * c["B"]
+    value = ids * args.steps / dt
+    sample = (f"each step = 26 tables (rows capped at {CPU_SAMPLE_ROW_CAP}) x {CPU_SAMPLE_BATCH} of the 65536 samples; "
+              "oracle C restatement, OpenMP")
+    line = {
+        "impl": "reference",
+        "metric": "embedding ids/sec (fwd+bwd+sparse Adam)", "value": value, "unit": "ids/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: 26 tables dim 128 fp32, one-hot Zipf(1.1), sparse Adam (bounded CPU sample)",
+                   "ids_per_step": ids},
+        "cpu_baseline": {"value": value, "unit": "ids/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "ids/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if args.warmup < 3:
+            args.warmup = 3
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

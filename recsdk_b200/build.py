@@ -50,7 +50,8 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> str:
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if _stale(obj, [src] + headers) or ptxas_info:
-            cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
+            # RECSDK_NVCC_EXTRA: extra flags, e.g. "-DRECSDK_SELFCHECK" for the bounds-checking debug build
+            cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("RECSDK_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
             if ptxas_info:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

@@ -1,6 +1,8 @@
 // Shared device/host helpers for the recsdk_b200 kernels (sm_100a).
 #pragma once
+#ifndef RECSDK_EMULATE  // host-side SIMT emulation builds provide their own shim
 #include <cuda_runtime.h>
+#endif
 #include <stdint.h>
 
 #include "recsdk_b200.h"
@@ -62,9 +64,13 @@ __device__ __forceinline__ void set_status(int64_t* st, int code, int64_t d0 = 0
 
 __device__ __forceinline__ unsigned lanemask_lt()
 {
+#ifdef RECSDK_EMULATE
+    return (1u << (threadIdx.x & 31)) - 1u;
+#else
     unsigned m;
     asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
     return m;
+#endif
 }
 
 // 128-bit global accesses.  Table rows are read through the normal (L2
@@ -129,6 +135,6 @@ static inline int group_lanes_for(int vec_per_row)
     return g;
 }
 
-static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+__host__ __device__ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace recsdk

@@ -122,6 +122,59 @@ static inline void device_scan(const int* in, int* out, int64_t n, int* scratch,
     scan_apply_kernel<INCLUSIVE><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, out, n, scratch);
 }
 
+// Functor form of the scan: the input is computed on the fly (`in(i)` -> int) and
+// the result is consumed on the fly (`out(i, item, prefix)`), so flag arrays and
+// the kernels that would write/read them disappear.
+template <typename InFn>
+__global__ void __launch_bounds__(kScanThreads) scan_reduce_fn_kernel(InFn in, int64_t n, int* __restrict__ tile_sums)
+{
+    __shared__ int sm[33];
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
+    int s = 0;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k)
+        if (base + k < n) s += in(base + k);
+    int total;
+    block_inclusive_scan(s, sm, &total);
+    if (threadIdx.x == 0) tile_sums[blockIdx.x] = total;
+}
+
+template <bool INCLUSIVE, typename InFn, typename OutFn>
+__global__ void __launch_bounds__(kScanThreads) scan_apply_fn_kernel(InFn in, OutFn out, int64_t n,
+                                                                     const int* __restrict__ tile_sums)
+{
+    __shared__ int sm[33];
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
+    int v[kScanItems];
+    int s = 0;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k) {
+        v[k] = (base + k < n) ? in(base + k) : 0;
+        s += v[k];
+    }
+    int total;
+    int inc = block_inclusive_scan(s, sm, &total);
+    int run = tile_sums[blockIdx.x] + inc - s;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k) {
+        if (base + k < n) out(base + k, v[k], INCLUSIVE ? run + v[k] : run);
+        run += v[k];
+    }
+}
+
+template <bool INCLUSIVE, typename InFn, typename OutFn>
+static inline void device_scan_fn(InFn in, OutFn out, int64_t n, int* scratch, int64_t* total_out, cudaStream_t st)
+{
+    if (n <= 0) {
+        if (total_out) cudaMemsetAsync(total_out, 0, sizeof(int64_t), st);
+        return;
+    }
+    const int64_t tiles = scan_num_tiles(n);
+    scan_reduce_fn_kernel<InFn><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, n, scratch);
+    scan_tile_sums_kernel<<<1, 1024, 0, st>>>(scratch, tiles, total_out);
+    scan_apply_fn_kernel<INCLUSIVE, InFn, OutFn><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, out, n, scratch);
+}
+
 // ----------------------------------------------------------------------------
 // Stable LSD radix sort of (key, uint32 value) pairs, 8 bits per pass.
 // Per pass: tile histograms -> per-digit scan across tiles -> stable scatter

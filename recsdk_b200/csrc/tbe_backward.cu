@@ -16,9 +16,14 @@
 //                 exactly once per step.
 // The float arithmetic uses explicit round-to-nearest intrinsics in the operand
 // order of the reference kernels (ComputeAdagrad / ComputeAdam / ComputeSgd).
+#include <limits.h>
 #include <math.h>
 
+#ifdef RECSDK_EMULATE
+#include "common.cuh"
+#else
 #include "prims.cuh"
+#endif
 
 namespace recsdk {
 
@@ -46,12 +51,11 @@ struct BwdParams {
     int64_t w_numel;
     int64_t* status;
     int base_aligned;
+    int64_t grad_numel;  // self-check builds only
     // plan arrays
     const uint32_t* __restrict__ vals;   // sorted
-    const int* __restrict__ rid;         // [N] run id of sorted position
     const int* __restrict__ run_start;   // [U+1]
-    const int* __restrict__ chunk_base;  // [N] exclusive scan of chunks per run
-    const int* __restrict__ chunk_desc;  // [chunks] start position of each chunk
+    const int2* __restrict__ chunk_desc;  // [chunks] {begin, end} sorted positions of each chunk
     float* __restrict__ partial;         // [chunks, max_D]
     const int64_t* __restrict__ counters;  // {U, total_chunks}
 };
@@ -118,62 +122,26 @@ __global__ void __launch_bounds__(256) expand_nobag_kernel(BwdParams p, KeyT* __
 }
 
 // ---------------------------------------------------------------------------- 3. runs
+// Head flags are computed on the fly inside the scan; the scan's consumer writes
+// run_start[] directly (no flag array, no run-id array).
 template <typename KeyT>
-__global__ void __launch_bounds__(256) head_flag_kernel(const KeyT* __restrict__ keys, int64_t n, int* __restrict__ flag)
-{
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
-        flag[i] = (i == 0 || keys[i] != keys[i - 1]) ? 1 : 0;
-}
-
-// rid_incl: inclusive scan of the head flags.  Writes rid = incl-1 in place,
-// run_start[rid] at heads, run_start[U] = n and counters[0] = U.
-template <typename KeyT>
-__global__ void __launch_bounds__(256) run_start_kernel(const KeyT* __restrict__ keys, int64_t n, int* __restrict__ rid,
-                                                        int* __restrict__ run_start, int64_t* __restrict__ counters)
-{
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int r = rid[i] - 1;
-        rid[i] = r;
-        if (i == 0 || keys[i] != keys[i - 1]) run_start[r] = static_cast<int>(i);
+struct HeadFlagIn {
+    const KeyT* __restrict__ keys;
+    __device__ __forceinline__ int operator()(int64_t i) const { return (i == 0 || keys[i] != keys[i - 1]) ? 1 : 0; }
+};
+struct RunStartOut {
+    int* __restrict__ run_start;
+    int64_t* __restrict__ counters;
+    int64_t n;
+    __device__ __forceinline__ void operator()(int64_t i, int flag, int incl) const
+    {
+        if (flag) run_start[incl - 1] = static_cast<int>(i);
         if (i == n - 1) {
-            run_start[r + 1] = static_cast<int>(n);
-            counters[0] = r + 1;
+            run_start[incl] = static_cast<int>(n);
+            counters[0] = incl;  // U
         }
     }
-}
-
-// ---------------------------------------------------------------------------- 4. chunks
-__global__ void __launch_bounds__(256) chunk_count_kernel(const int* __restrict__ run_start,
-                                                          const int64_t* __restrict__ counters, int64_t n,
-                                                          int* __restrict__ nch)
-{
-    const int64_t U = counters[0];
-    for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < n;
-         r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        int c = 0;
-        if (r < U) {
-            const int len = run_start[r + 1] - run_start[r];
-            if (len > kChunk) c = (len + kChunk - 1) / kChunk;
-        }
-        nch[r] = c;
-    }
-}
-
-__global__ void __launch_bounds__(256) chunk_desc_kernel(const int* __restrict__ rid, const int* __restrict__ run_start,
-                                                         const int* __restrict__ chunk_base, int64_t n,
-                                                         int* __restrict__ desc)
-{
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int r = rid[i];
-        const int rs = run_start[r];
-        const int len = run_start[r + 1] - rs;
-        const int d = static_cast<int>(i) - rs;
-        if (len > kChunk && (d % kChunk) == 0) desc[chunk_base[r] + d / kChunk] = static_cast<int>(i);
-    }
-}
+};
 
 // ---------------------------------------------------------------------------- gradient rows
 struct GradRow {
@@ -262,10 +230,8 @@ __device__ __forceinline__ bool vec_ok_for(const BwdParams& p, int64_t wofs, int
 template <typename V, int G, int K>
 __device__ __forceinline__ void partial_body(const BwdParams& p, int c, int lane)
 {
-    const int p0 = p.chunk_desc[c];
-    const int r = p.rid[p0];
-    const int re = p.run_start[r + 1];
-    const int e = (p0 + kChunk < re) ? p0 + kChunk : re;
+    const int2 be = p.chunk_desc[c];
+    const int p0 = be.x, e = be.y;
     int32_t D;
     int64_t wofs, f;
     run_geometry(p, p.vals[p0], D, wofs, f);
@@ -284,20 +250,74 @@ __device__ __forceinline__ void partial_body(const BwdParams& p, int c, int lane
     }
 }
 
+template <int G>
+__device__ __forceinline__ unsigned group_mask();
+
+// Chunk sums.  One group per chunk (<= kChunk sorted positions of one long run):
+// lanes resolve G gradient tags at a time to addresses in parallel, then the group
+// walks them in order with several independent 128-bit loads in flight.
 template <int G, int K>
 __global__ void __launch_bounds__(256) partial_kernel(BwdParams p)
 {
     const int groups_per_block = blockDim.x / G;
     const int lane = threadIdx.x % G;
+    const unsigned gmask = group_mask<G>();
     const int64_t total = p.counters[1];
+    constexpr int kUnroll = 8 / K;
     for (int64_t c = static_cast<int64_t>(blockIdx.x) * groups_per_block + threadIdx.x / G; c < total;
          c += static_cast<int64_t>(gridDim.x) * groups_per_block) {
         int32_t D;
         int64_t wofs, f;
-        run_geometry(p, p.vals[p.chunk_desc[c]], D, wofs, f);
-        if (vec_ok_for(p, wofs, D, f))
-            partial_body<V4, G, K>(p, static_cast<int>(c), lane);
-        else
+        const int2 be = p.chunk_desc[c];
+        run_geometry(p, p.vals[be.x], D, wofs, f);
+        if (vec_ok_for(p, wofs, D, f)) {
+            const int nvec = D >> 2;
+            float* out = p.partial + c * p.max_D;
+            for (int cb = 0; cb < nvec; cb += G * K) {
+                float4 acc[K];
+#pragma unroll
+                for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int base = be.x; base < be.y; base += G) {
+                    const int pos = base + lane;
+                    GradRow g_l;
+                    g_l.ptr = nullptr;
+                    g_l.scale = 1.0f;
+                    if (pos < be.y) g_l = grad_row_of(p, p.vals[pos]);
+                    const int cnt = (be.y - base) < G ? (be.y - base) : G;
+                    for (int jj0 = 0; jj0 < cnt; jj0 += kUnroll) {
+                        float4 v[kUnroll][K];
+                        float sc[kUnroll];
+#pragma unroll
+                        for (int u = 0; u < kUnroll; ++u) {
+                            const int jj = jj0 + u;
+                            const int src = jj < cnt ? jj : 0;
+                            const float* gp = reinterpret_cast<const float*>(
+                                __shfl_sync(gmask, reinterpret_cast<unsigned long long>(g_l.ptr), src, G));
+                            sc[u] = __shfl_sync(gmask, g_l.scale, src, G);
+#pragma unroll
+                            for (int k = 0; k < K; ++k) {
+                                const int col = cb + lane + k * G;
+                                v[u][k] = (jj < cnt && col < nvec) ? ld_f4_stream(gp + 4 * col)
+                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < kUnroll; ++u)
+                            if (jj0 + u < cnt) {
+                                const float s = sc[u];
+#pragma unroll
+                                for (int k = 0; k < K; ++k)
+                                    acc[k] = add4(acc[k], map4(v[u][k], [&](float x) { return prep_grad(p, x, s); }));
+                            }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    const int col = cb + lane + k * G;
+                    if (col < nvec) st_f4(out + 4 * col, acc[k]);
+                }
+            }
+        } else
             partial_body<V1, G, K>(p, static_cast<int>(c), lane);
     }
 }
@@ -347,37 +367,120 @@ __device__ __forceinline__ void opt_update_vec(const BwdParams& p, float g, floa
     opt_update<OPT>(p, g, w, m1, m2);
 }
 
-template <typename V, int G, int K, int OPT>
-__device__ __forceinline__ void update_body(const BwdParams& p, int r, int lane, int64_t row_off, int32_t D)
+// ---------------------------------------------------------------------------- 4. per-run records
+// Everything the row update needs to know about one unique row, resolved once by one
+// thread per run (fully parallel), so that the update kernel starts its row loads after
+// a single 32-byte read instead of a chain of five dependent loads.
+struct __align__(16) RunMeta {
+    int64_t row_off;     // element offset of the row in dev_weights; -1: out of range, skip
+    int64_t g0_off;      // element offset in grad_output of the run's first gradient row
+    int32_t rs, len;     // sorted positions [rs, rs + len)
+    int32_t D;           // row width in elements; kMetaVecBit set when the 128-bit path applies
+    int32_t chunk_base;  // first slot of the run in the partial buffer (len > kChunk), else -1
+};
+constexpr int32_t kMetaVecBit = 1 << 30;
+
+// A run longer than kChunk also reserves ceil(len/kChunk) slots of the partial buffer (atomic
+// counter; slot numbers differ from launch to launch but a slot's content and the order in which
+// a run's slots are summed do not) and describes each chunk as [begin, end) in sorted positions.
+// counters[2] collects how many indices live in chunked runs (bandwidth accounting only).
+template <typename KeyT>
+__global__ void __launch_bounds__(256) run_meta_kernel(BwdParams p, const KeyT* __restrict__ keys,
+                                                       int64_t* __restrict__ counters, RunMeta* __restrict__ meta,
+                                                       int2* __restrict__ desc)
 {
-    const int rs = p.run_start[r], re = p.run_start[r + 1];
+    const int64_t U = counters[0];
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < U;
+         r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int rs = p.run_start[r], re = p.run_start[r + 1];
+        const int len = re - rs;
+        const int64_t key = static_cast<int64_t>(keys[rs]);
+        const uint32_t v0 = p.vals[rs];
+        int32_t D;
+        int64_t wofs, f;
+        run_geometry(p, v0, D, wofs, f);
+        const int64_t row = p.uid != nullptr ? p.uid[key] : key - p.cumsum[f];
+        RunMeta m;
+        m.row_off = wofs + row * D;
+        if (p.w_numel > 0 && (row < 0 || m.row_off + D > p.w_numel)) {
+            set_status(p.status, RECSDK_ERR_INDEX_RANGE, row, m.row_off);
+            m.row_off = -1;
+        }
+        m.g0_off = grad_row_of(p, v0).ptr - p.grad;
+        m.rs = rs;
+        m.len = len;
+        m.D = D | (vec_ok_for(p, wofs, D, f) ? kMetaVecBit : 0);
+        m.chunk_base = -1;
+        if (p.chunk > 0 && len > kChunk) {
+            const int c = (len + kChunk - 1) / kChunk;
+            const int base = static_cast<int>(atomicAdd(reinterpret_cast<unsigned long long*>(counters + 1),
+                                                        static_cast<unsigned long long>(c)));
+            atomicAdd(reinterpret_cast<unsigned long long*>(counters + 2), static_cast<unsigned long long>(len));
+            m.chunk_base = base;
+            for (int k = 0; k < c; ++k) {
+                const int b0 = rs + k * kChunk;
+                desc[base + k] = make_int2(b0, b0 + kChunk < re ? b0 + kChunk : re);
+            }
+        }
+        meta[r] = m;
+    }
+}
+
+// ---------------------------------------------------------------------------- 5b. row update
+template <typename V, int G, int K, int OPT>
+__device__ __forceinline__ void update_body(const BwdParams& p, const RunMeta& m, int lane, int32_t D)
+{
+    const int rs = m.rs, re = m.rs + m.len;
     const int nvec = D / V::W;
-    const bool chunked = p.chunk > 0 && (re - rs) > kChunk;
+    const bool chunked = m.chunk_base >= 0;
+    const int64_t row_off = m.row_off;
+    // MEAN pooling scales every gradient row by its bag length: take the general path for all rows
+    const bool first_direct = !chunked && p.mode != RECSDK_POOL_MEAN;
     for (int cb = 0; cb < nvec; cb += G * K) {
-        typename V::T acc[K], w[K], m1[K], m2[K];
-        // issue the row loads first so they overlap the gradient reduction
+        typename V::T acc[K], w[K], m1[K], m2[K], g0[K];
+        // all row loads of a short run are independent: issue them together
 #pragma unroll
         for (int k = 0; k < K; ++k) {
             const int col = cb + lane + k * G;
             acc[k] = V::zero();
-            w[k] = m1[k] = m2[k] = V::zero();
+            w[k] = m1[k] = m2[k] = g0[k] = V::zero();
             if (col < nvec) {
                 w[k] = V::ld(p.w + row_off + V::W * col);
                 if (OPT != RECSDK_OPT_SGD) m1[k] = V::ld(p.m1 + row_off + V::W * col);
                 if (OPT == RECSDK_OPT_ADAM) m2[k] = V::ld(p.m2 + row_off + V::W * col);
+                if (first_direct) g0[k] = V::ld_stream(p.grad + m.g0_off + V::W * col);
             }
         }
         if (chunked) {
-            const int c0 = p.chunk_base[r];
-            const int nc = (re - rs + kChunk - 1) / kChunk;
-            for (int c = 0; c < nc; ++c) {
-                const float* pr = p.partial + static_cast<int64_t>(c0 + c) * p.max_D;
+            const int nc = (m.len + kChunk - 1) / kChunk;
+            int c = 0;
+            for (; c + 4 <= nc; c += 4) {
+                typename V::T v[4][K];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int k = 0; k < K; ++k) {
+                        const int col = cb + lane + k * G;
+                        v[u][k] = col < nvec ? V::ld(p.partial + static_cast<int64_t>(m.chunk_base + c + u) * p.max_D + V::W * col)
+                                             : V::zero();
+                    }
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int k = 0; k < K; ++k) acc[k] = add4(acc[k], v[u][k]);
+            }
+            for (; c < nc; ++c) {
 #pragma unroll
                 for (int k = 0; k < K; ++k) {
                     const int col = cb + lane + k * G;
-                    if (col < nvec) acc[k] = add4(acc[k], V::ld(pr + V::W * col));
+                    if (col < nvec)
+                        acc[k] = add4(acc[k], V::ld(p.partial + static_cast<int64_t>(m.chunk_base + c) * p.max_D + V::W * col));
                 }
             }
+        } else if (first_direct) {
+#pragma unroll
+            for (int k = 0; k < K; ++k) acc[k] = add4(acc[k], map4(g0[k], [&](float x) { return prep_grad(p, x, 1.0f); }));
+            if (re > rs + 1) sum_grad_rows<V, G, K>(p, rs + 1, re, cb, lane, nvec, acc);
         } else {
             sum_grad_rows<V, G, K>(p, rs, re, cb, lane, nvec, acc);
         }
@@ -394,37 +497,48 @@ __device__ __forceinline__ void update_body(const BwdParams& p, int r, int lane,
     }
 }
 
-template <typename KeyT, int G, int K, int OPT>
-__global__ void __launch_bounds__(256) update_kernel(BwdParams p, const KeyT* __restrict__ keys)
+// G lanes per unique row; the row's record tells where everything is.
+template <int G, int K, int OPT>
+__global__ void __launch_bounds__(256) update_kernel(BwdParams p, const RunMeta* __restrict__ meta)
 {
     const int groups_per_block = blockDim.x / G;
     const int lane = threadIdx.x % G;
     const int64_t U = p.counters[0];
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * groups_per_block + threadIdx.x / G; r < U;
          r += static_cast<int64_t>(gridDim.x) * groups_per_block) {
-        const int rs = p.run_start[r];
-        const int64_t key = static_cast<int64_t>(keys[rs]);
-        int32_t D;
-        int64_t wofs, f;
-        run_geometry(p, p.vals[rs], D, wofs, f);
-        const int64_t row = p.uid != nullptr ? p.uid[key] : key - p.cumsum[f];
-        const int64_t row_off = wofs + row * D;
-        if (p.w_numel > 0 && (row < 0 || row_off + D > p.w_numel)) {
-            set_status(p.status, RECSDK_ERR_INDEX_RANGE, row, row_off);
-            continue;
-        }
-        if (vec_ok_for(p, wofs, D, f))
-            update_body<V4, G, K, OPT>(p, static_cast<int>(r), lane, row_off, D);
+        const int4 lo = *reinterpret_cast<const int4*>(meta + r);
+        const int4 hi = *(reinterpret_cast<const int4*>(meta + r) + 1);
+        RunMeta m;
+        m.row_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.y)) << 32) | static_cast<uint32_t>(lo.x);
+        m.g0_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
+        m.rs = hi.x;
+        m.len = hi.y;
+        m.D = hi.z;
+        m.chunk_base = hi.w;
+        if (m.row_off < 0) continue;
+        const int32_t D = m.D & (kMetaVecBit - 1);
+        if (m.D & kMetaVecBit)
+            update_body<V4, G, K, OPT>(p, m, lane, D);
         else
-            update_body<V1, G, K, OPT>(p, static_cast<int>(r), lane, row_off, D);
+            update_body<V1, G, K, OPT>(p, m, lane, D);
     }
 }
 
+template <int G>
+__device__ __forceinline__ unsigned group_mask()
+{
+    if (G == 32) return kFullMask;
+    return ((1u << G) - 1u) << ((threadIdx.x & 31) / G * G);
+}
+
+#ifndef RECSDK_EMULATE
 // ---------------------------------------------------------------------------- host side
 struct BwdWorkspace {
     void *keys_a, *keys_b;
     uint32_t *vals_a, *vals_b, *sort_scratch;
-    int *rid, *run_start, *nch, *desc, *scan_scratch;
+    int *run_start, *scan_scratch;
+    RunMeta* meta;
+    int2* desc;
     float* partial;
     int64_t* counters;
     size_t bytes;
@@ -442,10 +556,9 @@ static BwdWorkspace carve_bwd(void* base, int64_t N, int32_t max_D)
     w.vals_a = c.take<uint32_t>(n);
     w.vals_b = c.take<uint32_t>(n);
     w.sort_scratch = c.take<uint32_t>(sort_scratch_u32(N));
-    w.rid = c.take<int>(n);
     w.run_start = c.take<int>(n + 1);
-    w.nch = c.take<int>(n + 1);
-    w.desc = c.take<int>(max_chunks);
+    w.meta = c.take<RunMeta>(n);
+    w.desc = c.take<int2>(max_chunks);
     w.scan_scratch = c.take<int>(scan_scratch_ints(N));
     w.partial = c.take<float>(max_chunks * static_cast<size_t>(max_D));
     w.bytes = c.used();
@@ -459,15 +572,15 @@ static int bits_for(int64_t x)
     return b < 1 ? 1 : b;
 }
 
-template <typename KeyT, int G, int K>
-static void launch_update(const BwdParams& p, const KeyT* keys, int64_t N, cudaStream_t st)
+template <int G, int K>
+static void launch_update(const BwdParams& p, const RunMeta* meta, int64_t N, cudaStream_t st)
 {
     const int groups_per_block = 256 / G;
     const int grid = grid_for(N, groups_per_block, 8);
     switch (p.opt) {
-        case RECSDK_OPT_ADAGRAD: update_kernel<KeyT, G, K, RECSDK_OPT_ADAGRAD><<<grid, 256, 0, st>>>(p, keys); break;
-        case RECSDK_OPT_ADAM: update_kernel<KeyT, G, K, RECSDK_OPT_ADAM><<<grid, 256, 0, st>>>(p, keys); break;
-        default: update_kernel<KeyT, G, K, RECSDK_OPT_SGD><<<grid, 256, 0, st>>>(p, keys); break;
+        case RECSDK_OPT_ADAGRAD: update_kernel<G, K, RECSDK_OPT_ADAGRAD><<<grid, 256, 0, st>>>(p, meta); break;
+        case RECSDK_OPT_ADAM: update_kernel<G, K, RECSDK_OPT_ADAM><<<grid, 256, 0, st>>>(p, meta); break;
+        default: update_kernel<G, K, RECSDK_OPT_SGD><<<grid, 256, 0, st>>>(p, meta); break;
     }
 }
 
@@ -503,6 +616,7 @@ static int run_backward(const recsdk_tbe_backward_args* a, BwdParams p, const Bw
     const int64_t N = a->N;
     KeyT* ka = static_cast<KeyT*>(ws.keys_a);
     KeyT* kb = static_cast<KeyT*>(ws.keys_b);
+    cudaMemsetAsync(ws.counters, 0, 8 * sizeof(int64_t), st);  // {U, chunks, indices in chunked runs, ...}
     // 1. expand
     if (a->pooling_mode == RECSDK_POOL_NONE)
         expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, ka, ws.vals_a);
@@ -513,30 +627,27 @@ static int run_backward(const recsdk_tbe_backward_args* a, BwdParams p, const Bw
     const KeyT* keys = which ? kb : ka;
     p.vals = which ? ws.vals_b : ws.vals_a;
     // 3. runs
-    head_flag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(keys, N, ws.rid);
-    device_scan<true>(ws.rid, ws.rid, N, ws.scan_scratch, nullptr, st);
-    run_start_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(keys, N, ws.rid, ws.run_start, ws.counters);
-    p.rid = ws.rid;
+    device_scan_fn<true>(HeadFlagIn<KeyT>{keys}, RunStartOut{ws.run_start, ws.counters, N}, N, ws.scan_scratch, nullptr,
+                         st);
     p.run_start = ws.run_start;
     p.counters = ws.counters;
     const int vec_per_row = (a->max_D + 3) / 4;
-    // 4. chunk sums of long runs
+    // 4. per-run records (+ chunk descriptors of long runs), chunk sums
+    p.chunk_desc = ws.desc;
+    p.partial = ws.partial;
+    run_meta_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, keys, ws.counters, ws.meta, ws.desc);
     if (a->reduce_chunk > 0) {
-        chunk_count_kernel<<<grid_for(N, 256), 256, 0, st>>>(ws.run_start, ws.counters, N, ws.nch);
-        device_scan<false>(ws.nch, ws.nch, N, ws.scan_scratch, ws.counters + 1, st);
-        chunk_desc_kernel<<<grid_for(N, 256), 256, 0, st>>>(ws.rid, ws.run_start, ws.nch, N, ws.desc);
-        p.chunk_base = ws.nch;
-        p.chunk_desc = ws.desc;
-        p.partial = ws.partial;
 #define CALL_PARTIAL(G, K) launch_partial<G, K>(p, N, st)
         RECSDK_DISPATCH_GK(vec_per_row, CALL_PARTIAL);
 #undef CALL_PARTIAL
     }
     // 5. update
     if (a->ev_update_start) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_update_start), st);
-#define CALL_UPDATE(G, K) launch_update<KeyT, G, K>(p, keys, N, st)
+#ifndef RECSDK_SKIP_UPDATE
+#define CALL_UPDATE(G, K) launch_update<G, K>(p, ws.meta, N, st)
     RECSDK_DISPATCH_GK(vec_per_row, CALL_UPDATE);
 #undef CALL_UPDATE
+#endif
     if (a->ev_update_stop) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_update_stop), st);
     RECSDK_CUDA_CHECK_LAUNCH();
     return RECSDK_OK;
@@ -615,6 +726,7 @@ extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stre
     p.max_grad = a->max_gradient;
     p.clip = a->gradient_clipping;
     p.w_numel = a->weights_numel;
+    p.grad_numel = a->pooling_mode == RECSDK_POOL_NONE ? a->N * a->max_D : a->B * static_cast<int64_t>(a->total_D);
     p.status = a->dev_status;
     p.base_aligned = (aligned16(a->grad_output) && aligned16(a->dev_weights) && aligned16(a->momentum1) &&
                       aligned16(a->momentum2) && aligned16(ws.partial))
@@ -629,3 +741,4 @@ extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stre
     if (key_bits <= 32) return run_backward<uint32_t>(a, p, ws, key_bits, st);
     return run_backward<uint64_t>(a, p, ws, key_bits, st);
 }
+#endif  // RECSDK_EMULATE

@@ -1,11 +1,20 @@
 // Pooled embedding gather over ragged bags (forward of the table-batched
-// embedding op).  HBM-bound: G lanes cooperate on one bag, every lane moves
-// 128-bit pieces of a row, rows of one bag are fetched four at a time so that
-// several 128-bit loads per lane are in flight, and the pooled row is written
-// once with a streaming store.  Rows are added in index order starting from
-// 0.0f, which is the order of the reference kernel (Pooling(),
-// split_embedding_codegen_forward_unweighted_kernel.h:226-241) for bags that
-// fit one of its blocks, so the result is bit-exact against a sequential loop.
+// embedding op).
+//
+// The op is HBM-bound, but a naive "one warp per bag" mapping is latency-bound:
+// offsets -> index -> row is a chain of three dependent global loads per bag.
+// Here G lanes (G*16 bytes = one row, at most a warp) own G consecutive bags:
+//   * each lane fetches the metadata of ONE of the G bags (offsets, feature
+//     geometry) and, 32 positions at a time, ONE index of the contiguous index
+//     range those bags cover, and resolves it to a row address -- all in parallel;
+//   * the group then walks the resolved rows in order, broadcasting the row
+//     address with shuffles and issuing eight independent 128-bit row loads per
+//     lane before consuming them, so many rows are in flight per warp;
+//   * rows are accumulated in index order from 0.0f and the pooled row is
+//     written once with a streaming store when the walk crosses a bag boundary.
+// The addition order is the order of the reference kernel (Pooling(),
+// split_embedding_codegen_forward_unweighted_kernel.h:226-241) for bags that fit
+// one of its blocks: bit-exact against a sequential loop.
 #include "common.cuh"
 
 namespace recsdk {
@@ -21,7 +30,7 @@ struct FwdParams {
     int32_t total_D, max_D, mode;
     int64_t w_numel;
     int64_t* status;
-    int base_aligned;  // dev_weights and out are 16-byte aligned
+    int base_aligned;  // dev_weights and out are 16-byte aligned and total_D % 4 == 0
 };
 
 __device__ __forceinline__ bool row_ok(const FwdParams& p, int64_t idx, int64_t row_off, int32_t D)
@@ -34,11 +43,18 @@ __device__ __forceinline__ bool row_ok(const FwdParams& p, int64_t idx, int64_t 
     return true;
 }
 
-// Scalar path for bags whose offsets/dims are not multiples of 4 elements.
+// Generic per-bag path (any dim / offset alignment), G lanes striding over the columns.
 template <int G>
-__device__ void forward_bag_scalar(const FwdParams& p, int lane, int64_t s, int64_t e, int64_t wofs, int32_t D,
-                                   float* out_row, float mean)
+__device__ void forward_bag_scalar(const FwdParams& p, int lane, int64_t bag)
 {
+    const int64_t t = bag / p.B;
+    const int64_t b = bag - t * p.B;
+    const int64_t s = p.offs[bag], e = p.offs[bag + 1];
+    const int32_t d0 = p.dofs[t];
+    const int32_t D = p.dofs[t + 1] - d0;
+    const int64_t wofs = p.wofs[t];
+    float* out_row = p.out + b * p.total_D + d0;
+    const float mean = __fdiv_rn(1.0f, static_cast<float>(e - s));
     for (int c = lane; c < D; c += G) {
         float acc = 0.f;
         for (int64_t i = s; i < e; ++i) {
@@ -52,75 +68,130 @@ __device__ void forward_bag_scalar(const FwdParams& p, int lane, int64_t s, int6
     }
 }
 
+template <int G>
+__device__ __forceinline__ unsigned group_mask()
+{
+    if (G == 32) return kFullMask;
+    return ((1u << G) - 1u) << ((threadIdx.x & 31) / G * G);
+}
+
+constexpr int kFwdUnroll = 8;
+
 template <int G, int K>
 __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
 {
-    const int groups_per_block = blockDim.x / G;
-    const int lane = threadIdx.x % G;
+    const int gl = threadIdx.x % G;
+    const unsigned gmask = group_mask<G>();
     const int64_t num_bags = p.T * p.B;
-    for (int64_t bag = static_cast<int64_t>(blockIdx.x) * groups_per_block + threadIdx.x / G; bag < num_bags;
-         bag += static_cast<int64_t>(gridDim.x) * groups_per_block) {
-        const int64_t t = bag / p.B;
-        const int64_t b = bag - t * p.B;
-        const int64_t s = p.offs[bag], e = p.offs[bag + 1];
-        const int32_t d0 = p.dofs[t];
-        const int32_t D = p.dofs[t + 1] - d0;
-        const int64_t wofs = p.wofs[t];
-        float* out_row = p.out + b * p.total_D + d0;
-        const float mean = __fdiv_rn(1.0f, static_cast<float>(e - s));
-        const bool vec_ok = p.base_aligned && (((wofs | D | d0 | p.total_D) & 3) == 0);
-        if (!vec_ok) {
-            forward_bag_scalar<G>(p, lane, s, e, wofs, D, out_row, mean);
+    const int64_t groups_total = static_cast<int64_t>(gridDim.x) * blockDim.x / G;
+    const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / G;
+    const int max_nvec = p.max_D >> 2;
+
+    for (int64_t bag0 = gid * G; bag0 < num_bags; bag0 += groups_total * G) {
+        const int nb = static_cast<int>((num_bags - bag0) < G ? (num_bags - bag0) : G);
+        const bool valid = gl < nb;
+        const int64_t my_bag = bag0 + gl;
+        const int64_t start_l = valid ? p.offs[my_bag] : INT64_MAX;
+        const int64_t end_all = p.offs[bag0 + nb];
+        const int64_t t_l = valid ? my_bag / p.B : 0;
+        const int64_t b_l = my_bag - t_l * p.B;
+        const int32_t d0_l = p.dofs[t_l];
+        const int32_t D_l = p.dofs[t_l + 1] - d0_l;
+        const int64_t wofs_l = p.wofs[t_l];
+        const int64_t oofs_l = b_l * p.total_D + d0_l;
+        const bool ok_l = !valid || (((wofs_l | D_l | d0_l) & 3) == 0);
+        const bool all_ok = __all_sync(gmask, ok_l) != 0;  // executed by every lane of the group
+        if (!(p.base_aligned && all_ok)) {
+            for (int j = 0; j < nb; ++j) forward_bag_scalar<G>(p, gl, bag0 + j);
             continue;
         }
-        const int nvec = D >> 2;
-        for (int cb = 0; cb < nvec; cb += G * K) {
+        const int64_t p0 = __shfl_sync(gmask, start_l, 0, G);
+
+        // flush bag j: write `acc` (scaled for MEAN) or zeros
+        auto flush = [&](int j, const float4 (&acc)[K], bool has_rows, int cb) {
+            const int64_t oofs = __shfl_sync(gmask, oofs_l, j, G);
+            const int nvec = __shfl_sync(gmask, D_l, j, G) >> 2;
+            const int64_t sj = __shfl_sync(gmask, start_l, j, G);
+            const int64_t nx = __shfl_sync(gmask, start_l, (j + 1) & (G - 1), G);
+            const int64_t ej = (j + 1 < nb) ? nx : end_all;
+            const float mean = __fdiv_rn(1.0f, static_cast<float>(ej - sj));
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const int c = cb + gl + k * G;
+                if (c < nvec) {
+                    float4 r = has_rows ? acc[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (has_rows && p.mode == RECSDK_POOL_MEAN) r = mul4s(r, mean);
+                    st_f4_stream(p.out + oofs + 4 * c, r);
+                }
+            }
+        };
+
+        for (int cb = 0; cb < max_nvec; cb += G * K) {
+            int cur = 0;           // bag (0..nb) whose rows are being accumulated
+            bool cur_has = false;  // accumulator holds at least one row
             float4 acc[K];
 #pragma unroll
             for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-            int64_t i = s;
-            for (; i + 4 <= e; i += 4) {
-                int64_t id[4];
-                const float* rp[4];
+
+            for (int64_t base = p0; base < end_all; base += G) {
+                const int64_t pos = base + gl;
+                const bool have = pos < end_all;
+                const int64_t id = have ? p.idx[pos] : 0;
+                // bag of `pos`: the largest j with start_j <= pos (empty bags share a start; the last owns it)
+                int j_l = 0;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) id[j] = p.idx[i + j];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    int64_t ro = wofs + id[j] * D;
-                    rp[j] = row_ok(p, id[j], ro, D) ? p.w + ro : nullptr;
+                for (int step = G >> 1; step >= 1; step >>= 1) {
+                    const int cand = j_l + step;
+                    const int64_t sc = __shfl_sync(gmask, start_l, cand & (G - 1), G);
+                    if (cand < G && sc <= pos) j_l = cand;
                 }
-                float4 v[4][K];
+                const int64_t wofs_j = __shfl_sync(gmask, wofs_l, j_l, G);
+                const int32_t D_j = __shfl_sync(gmask, D_l, j_l, G);
+                int64_t ro_l = wofs_j + id * D_j;
+                if (have && !row_ok(p, id, ro_l, D_j)) ro_l = -1;
+                const int cnt = static_cast<int>((end_all - base) < G ? (end_all - base) : G);
+
+                constexpr int kUnroll = kFwdUnroll / K;  // independent row loads in flight per lane
+                for (int jj0 = 0; jj0 < cnt; jj0 += kUnroll) {
+                    float4 v[kUnroll][K];
+                    int bj[kUnroll];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                    for (int u = 0; u < kUnroll; ++u) {
+                        const int jj = jj0 + u;
+                        const int src = jj < cnt ? jj : 0;
+                        const int64_t ro = __shfl_sync(gmask, ro_l, src, G);
+                        bj[u] = __shfl_sync(gmask, j_l, src, G);
+                        const int nvec = __shfl_sync(gmask, D_l, bj[u], G) >> 2;
 #pragma unroll
-                    for (int k = 0; k < K; ++k) {
-                        int c = cb + lane + k * G;
-                        v[j][k] = (rp[j] != nullptr && c < nvec) ? ld_f4(rp[j] + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int k = 0; k < K; ++k) {
+                            const int c = cb + gl + k * G;
+                            v[u][k] = (jj < cnt && ro >= 0 && c < nvec) ? ld_f4(p.w + ro + 4 * c)
+                                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
                     }
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                    for (int u = 0; u < kUnroll; ++u) {
+                        if (jj0 + u < cnt) {
+                            while (cur < bj[u]) {  // group-uniform: finished (or empty) bags
+                                flush(cur, acc, cur_has, cb);
 #pragma unroll
-                    for (int k = 0; k < K; ++k) acc[k] = add4(acc[k], v[j][k]);
-            }
-            for (; i < e; ++i) {
-                int64_t id = p.idx[i];
-                int64_t ro = wofs + id * D;
-                const float* rp = row_ok(p, id, ro, D) ? p.w + ro : nullptr;
+                                for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                cur_has = false;
+                                ++cur;
+                            }
 #pragma unroll
-                for (int k = 0; k < K; ++k) {
-                    int c = cb + lane + k * G;
-                    float4 v = (rp != nullptr && c < nvec) ? ld_f4(rp + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    acc[k] = add4(acc[k], v);
+                            for (int k = 0; k < K; ++k) acc[k] = add4(acc[k], v[u][k]);
+                            cur_has = true;
+                        }
+                    }
                 }
             }
+            while (cur < nb) {
+                flush(cur, acc, cur_has, cb);
 #pragma unroll
-            for (int k = 0; k < K; ++k) {
-                int c = cb + lane + k * G;
-                if (c < nvec) {
-                    float4 r = acc[k];
-                    if (p.mode == RECSDK_POOL_MEAN && e > s) r = mul4s(r, mean);
-                    st_f4_stream(out_row + 4 * c, r);
-                }
+                for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                cur_has = false;
+                ++cur;
             }
         }
     }
@@ -147,7 +218,7 @@ __global__ void __launch_bounds__(256) tbe_forward_nobag_kernel(FwdParams p)
         const int64_t ro = wofs + id * D;
         const bool ok = row_ok(p, id, ro, D);
         float* out_row = p.out + i * p.max_D;
-        const bool vec_ok = p.base_aligned && (((wofs | D | p.max_D) & 3) == 0);
+        const bool vec_ok = aligned16(p.w) && aligned16(p.out) && (((wofs | D | p.max_D) & 3) == 0);
         if (vec_ok) {
             const int nvec = D >> 2, nvec_out = p.max_D >> 2;
             for (int c = lane; c < nvec_out; c += G) {
@@ -164,7 +235,7 @@ template <int G, int K>
 static void launch_pooled(const FwdParams& p, cudaStream_t st)
 {
     const int groups_per_block = 256 / G;
-    int grid = grid_for(p.T * p.B, groups_per_block, 8);
+    int grid = grid_for(ceil_div(p.T * p.B, G), groups_per_block, 8);
     tbe_forward_pooled_kernel<G, K><<<grid, 256, 0, st>>>(p);
 }
 
@@ -191,7 +262,7 @@ extern "C" int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     FwdParams p{a->dev_weights, a->weights_offsets, a->D_offsets, a->indices, a->offsets, a->out, a->T, a->B, a->N,
                 a->total_D, a->max_D, a->pooling_mode, a->weights_numel, a->dev_status,
-                (aligned16(a->dev_weights) && aligned16(a->out)) ? 1 : 0};
+                (aligned16(a->dev_weights) && aligned16(a->out) && (a->total_D & 3) == 0) ? 1 : 0};
     const int vec_per_row = (a->max_D + 3) / 4;
     const int G = group_lanes_for(vec_per_row);
     if (a->pooling_mode == RECSDK_POOL_NONE) {
