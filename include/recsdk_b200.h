@@ -98,6 +98,26 @@ RECSDK_API int recsdk_unique_sorted(const int64_t* ids, int64_t n, int key_bits,
                                     int64_t* inverse_out, int64_t* num_unique_out, void* workspace,
                                     size_t workspace_bytes, void* stream);
 
+/* Allocation-free variant of recsdk_unique_sorted.  It has no counterpart in the
+ * reference.  It exists for callers that cannot allocate device memory where they need
+ * the dedup (allocator callbacks and memory-pool hooks, preprocessing threads that own
+ * device buffers but no allocator, services whose device memory is budgeted up front):
+ * the sort scratch is a __device__ array built into the library, so the call performs no
+ * cudaMalloc/cudaFree and takes no workspace.  Limits and rules:
+ *   - n <= RECSDK_UNIQUE_STATIC_MAX_N, else RECSDK_ERR_TOO_LARGE (use recsdk_unique_sorted);
+ *   - every GPU that loads the library holds the scratch (8 MiB) until the process exits;
+ *   - the first call on a device resolves the array's device address
+ *     (cudaGetSymbolAddress, once per device, with that device current): make that first
+ *     call before starting any stream capture;
+ *   - all calls on a device share the scratch and it keeps the previous call's contents
+ *     (nothing needs to start at zero: every word is written before it is read); calls whose
+ *     kernels overlap on the GPU race on it, so serialise them (one stream, or events).
+ * Inputs and outputs are the caller's, exactly as for recsdk_unique_sorted. */
+#define RECSDK_UNIQUE_STATIC_MAX_N 262144
+RECSDK_API int64_t recsdk_unique_sorted_static_max_n(void);
+RECSDK_API int recsdk_unique_sorted_static(const int64_t* ids, int64_t n, int key_bits, int64_t* unique_out,
+                                           int64_t* inverse_out, int64_t* num_unique_out, void* stream);
+
 /* =========================================================================
  * A7  fused backward: gradient segment-sum over deduplicated rows + sparse
  * Adagrad / Adam / SGD row update, in place.

@@ -77,6 +77,8 @@ SIGNATURES = {
     "recsdk_tbe_forward": (C.c_int, [C.POINTER(TbeForwardArgs), vp]),
     "recsdk_unique_sorted_workspace_bytes": (C.c_size_t, [C.c_int64]),
     "recsdk_unique_sorted": (C.c_int, [vp, C.c_int64, C.c_int, vp, vp, vp, vp, C.c_size_t, vp]),
+    "recsdk_unique_sorted_static_max_n": (C.c_int64, []),
+    "recsdk_unique_sorted_static": (C.c_int, [vp, C.c_int64, C.c_int, vp, vp, vp, vp]),
     "recsdk_tbe_backward_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "recsdk_tbe_backward": (C.c_int, [C.POINTER(TbeBackwardArgs), vp]),
     "recsdk_adam_beta2sqrt": (C.c_float, [C.c_float, C.c_float, C.c_int64]),

@@ -106,3 +106,67 @@ extern "C" int recsdk_unique_sorted(const int64_t* ids, int64_t n, int key_bits,
     if (key_bits <= 32) return run_unique<uint32_t>(ids, n, key_bits, unique_out, inverse_out, num_unique_out, ws, st);
     return run_unique<uint64_t>(ids, n, key_bits, unique_out, inverse_out, num_unique_out, ws, st);
 }
+
+// ----------------------------------------------------------------------------
+// Allocation-free variant: sorted unique + inverse with built-in scratch.
+//
+// Some callers of this library cannot allocate device memory at the point where they
+// need a dedup: code running inside a framework's allocator callback or memory-pool
+// hook, a preprocessing thread that was handed device buffers but no allocator, or a
+// service whose device memory is fully budgeted up front and where a late cudaMalloc
+// may fail or stall the device.  For them the scratch of the sort lives in a
+// file-scope __device__ array, sized for at most RECSDK_UNIQUE_STATIC_MAX_N ids; every
+// GPU that loads this library holds those bytes until the process exits.
+//
+// The array's name is only a host-side stand-in for the symbol: its device address
+// is resolved with cudaGetSymbolAddress, once per device, on the first call made with
+// that device current.  That first call should therefore happen before any stream
+// capture is started.  All calls on one device share the same scratch, which keeps the
+// contents of the previous call: nothing in this pipeline needs it zeroed (every
+// scratch word is written before it is read), but two calls whose kernels overlap on
+// the GPU (different streams) race on it -- serialise them.
+// ----------------------------------------------------------------------------
+#include <mutex>
+
+namespace recsdk {
+
+constexpr int64_t kUniqueStaticMaxN = RECSDK_UNIQUE_STATIC_MAX_N;
+constexpr size_t kUniqueStaticBytes = size_t(8) << 20;  // >= carve_unique(kUniqueStaticMaxN).bytes, checked at set-up
+
+static __device__ __align__(256) unsigned char g_unique_static_scratch[kUniqueStaticBytes];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_unique_static_mu;
+static void* g_unique_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device (resolved once per device).
+static int unique_static_scratch(void** out)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return RECSDK_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_unique_static_mu);
+    if (g_unique_static_ptr[dev] == nullptr) {
+        if (carve_unique(nullptr, kUniqueStaticMaxN).bytes > kUniqueStaticBytes) return RECSDK_ERR_WORKSPACE;
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_unique_static_scratch) != cudaSuccess || ptr == nullptr) return RECSDK_ERR_CUDA;
+        g_unique_static_ptr[dev] = ptr;
+    }
+    *out = g_unique_static_ptr[dev];
+    return RECSDK_OK;
+}
+
+}  // namespace recsdk
+
+extern "C" int64_t recsdk_unique_sorted_static_max_n(void) { return recsdk::kUniqueStaticMaxN; }
+
+extern "C" int recsdk_unique_sorted_static(const int64_t* ids, int64_t n, int key_bits, int64_t* unique_out,
+                                           int64_t* inverse_out, int64_t* num_unique_out, void* stream)
+{
+    if (n < 0 || key_bits < 1 || key_bits > 64) return RECSDK_ERR_INVALID_ARG;
+    if (n > recsdk::kUniqueStaticMaxN) return RECSDK_ERR_TOO_LARGE;  // beyond the built-in scratch: use recsdk_unique_sorted
+    void* scratch = nullptr;
+    const int rc = recsdk::unique_static_scratch(&scratch);
+    if (rc != RECSDK_OK) return rc;
+    return recsdk_unique_sorted(ids, n, key_bits, unique_out, inverse_out, num_unique_out, scratch,
+                                recsdk::kUniqueStaticBytes, stream);
+}

@@ -111,6 +111,24 @@ def unique_sorted(ids: torch.Tensor, key_bits: int = 64) -> Tuple[torch.Tensor, 
     return uniq, inv[:n], cnt
 
 
+def unique_sorted_static(ids: torch.Tensor, unique_out: torch.Tensor, inverse_out: torch.Tensor,
+                         num_unique_out: torch.Tensor, key_bits: int = 64) -> None:
+    """Sorted unique + inverse into caller-provided outputs with NO device allocation: the sort scratch is
+    built into the library (at most ``recsdk_unique_sorted_static_max_n()`` ids).  For callers that must not
+    allocate (allocator callbacks, pre-budgeted services).  Calls on one device share that scratch: keep them
+    on one stream (or otherwise serialised); make the first call on a device before any stream capture."""
+    lib = _lib.load()
+    _chk(ids, torch.int64, "ids")
+    _chk(unique_out, torch.int64, "unique_out")
+    _chk(inverse_out, torch.int64, "inverse_out")
+    _chk(num_unique_out, torch.int64, "num_unique_out")
+    n = ids.numel()
+    if unique_out.numel() < n or inverse_out.numel() < n or num_unique_out.numel() < 1:
+        raise RuntimeError("unique_out / inverse_out need n entries and num_unique_out one")
+    check(lib.recsdk_unique_sorted_static(_ptr(ids), n, key_bits, _ptr(unique_out), _ptr(inverse_out),
+                                          _ptr(num_unique_out), _stream()), "recsdk_unique_sorted_static")
+
+
 # --------------------------------------------------------------------------- A7 backward
 def tbe_backward_workspace_bytes(N: int, max_D: int) -> int:
     return _lib.load().recsdk_tbe_backward_workspace_bytes(N, max_D)
