@@ -113,17 +113,6 @@ class ClockSampler:
 
 
 # ============================================================================ our arm
-def greedy_table_placement(rows, world):
-    """Table-wise sharding: biggest table first onto the least loaded rank (bytes)."""
-    load = [0] * world
-    owner = [0] * len(rows)
-    for t in sorted(range(len(rows)), key=lambda i: -rows[i]):
-        r = min(range(world), key=lambda k: load[k])
-        owner[t] = r
-        load[r] += rows[t]
-    return owner
-
-
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -145,8 +134,10 @@ def run_ours(args):
     if world == 1:
         row_cap = ROW_CAP_1GPU
         rows_all = [min(r, row_cap) for r in rows_all]
-    owner = greedy_table_placement(rows_all, world)
-    my_tables = [t for t in range(N_TABLES) if owner[t] == rank]
+    from recsdk_b200.sharding import TableWiseSharding
+
+    sh = TableWiseSharding(rows_all, [DIM] * N_TABLES, world, rank)
+    my_tables = sh.local_tables
     rows = [rows_all[t] for t in my_tables]
     state_bytes = sum(rows) * DIM * 4 * 3
     assert state_bytes < HBM_BUDGET_BYTES + 20e9, f"rank {rank}: {state_bytes / 1e9:.1f} GB of table state"
@@ -159,27 +150,38 @@ def run_ours(args):
     gen = torch.Generator(device=dev)
     gen.manual_seed(SEED + 17 * rank)
     n_batches = 4  # rotate distinct batches so consecutive steps touch different rows
-    batches = [one_hot_batch(gen, rows, B, ALPHA, dev) for _ in range(n_batches)]
     ids_per_step_rank = T * B
-    grad = torch.randn((B, T * DIM), generator=gen, device=dev, dtype=torch.float32)
     out = torch.empty((B, T * DIM), device=dev, dtype=torch.float32)
-    # output/gradient exchange buffers of the table-wise layout (multi-GPU only)
-    if world > 1:
-        a2a_out = torch.empty_like(out)
-        a2a_grad = torch.empty_like(grad)
+    if world == 1:
+        batches = [one_hot_batch(gen, rows, B, ALPHA, dev) for _ in range(n_batches)]
+        grad = torch.randn((B, T * DIM), generator=gen, device=dev, dtype=torch.float32)
+    else:
+        # every rank holds the ids of ITS 65536 samples for all 26 fields and the upstream gradient of its
+        # samples; ids travel to the table owners, pooled rows come back, gradients go out again
+        from recsdk_b200.synthetic import zipf_ids
+
+        batches = [torch.stack([zipf_ids(gen, BATCH, r, ALPHA, dev) for r in rows_all]).view(N_TABLES, BATCH, 1)
+                   for _ in range(n_batches)]
+        grad = torch.randn((BATCH, N_TABLES * DIM), generator=gen, device=dev, dtype=torch.float32)
+        owner_offsets = torch.arange(T * B + 1, dtype=torch.int64, device=dev)
 
     ev_pairs = []
 
+    def owner_view(i, ids_local=None):
+        """(indices, offsets, upstream gradient) as the table owner sees them for step i."""
+        if world == 1:
+            idx, offs = batches[i % n_batches]
+            return idx, offs, grad
+        ids = sh.exchange_ids(batches[i % n_batches] if ids_local is None else ids_local)
+        return ids.view(-1), owner_offsets, None
+
     def step_resident(i, timed=False):
-        idx, offs = batches[i % n_batches]
+        idx, offs, g = owner_view(i)
         module.forward_into(idx, offs, out)
         if world > 1:
-            # pooled rows of my tables for every rank's samples -> sample owners; gradients come back
-            dist.all_to_all_single(a2a_out.view(world, -1), out.view(world, -1))
-            dist.all_to_all_single(a2a_grad.view(world, -1), grad.view(world, -1))
-            g = a2a_grad
-        else:
-            g = grad
+            pooled = sh.exchange_outputs(out, BATCH)  # [BATCH, 26*DIM] on the sample owner (consumed by the dense part)
+            g = sh.exchange_gradients(grad)
+            del pooled
         evs = None
         if timed:
             evs = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
@@ -214,13 +216,18 @@ def run_ours(args):
     # ---- end to end through the module API with host index buffers.  The caller's pipeline double-buffers
     # the H2D copy of the next batch on a copy stream (the reference pipeline's dedicated memcpy stream,
     # torchrec_embcache/distributed/train_pipeline.py:115-119); every step's copy is inside the timed region.
-    host = [(idx.cpu().pin_memory(), offs.cpu().pin_memory()) for idx, offs in batches]
-    d_bufs = [(torch.empty_like(batches[0][0]), torch.empty_like(batches[0][1])) for _ in range(2)]
+    if world == 1:
+        host = [(idx.cpu().pin_memory(), offs.cpu().pin_memory()) for idx, offs in batches]
+        d_bufs = [(torch.empty_like(batches[0][0]), torch.empty_like(batches[0][1])) for _ in range(2)]
+    else:
+        host = [(ids.cpu().pin_memory(), None) for ids in batches]
+        d_bufs = [(torch.empty_like(batches[0]), None) for _ in range(2)]
     copy_stream = torch.cuda.Stream(device=dev)
     copied = [torch.cuda.Event(), torch.cuda.Event()]
     consumed = [torch.cuda.Event(), torch.cuda.Event()]
     result_host = torch.empty(4096, dtype=torch.float32).pin_memory()
     main_stream = torch.cuda.current_stream()
+    h2d_bytes = sum(t.numel() * 8 for t in host[0] if t is not None)
 
     def prefetch(i):
         h_idx, h_offs = host[i % n_batches]
@@ -228,7 +235,8 @@ def run_ours(args):
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(consumed[i % 2])
             d_idx.copy_(h_idx, non_blocking=True)
-            d_offs.copy_(h_offs, non_blocking=True)
+            if h_offs is not None:
+                d_offs.copy_(h_offs, non_blocking=True)
             copied[i % 2].record(copy_stream)
 
     def step_e2e(i, last):
@@ -236,15 +244,17 @@ def run_ours(args):
             prefetch(i + 1)
         d_idx, d_offs = d_bufs[i % 2]
         main_stream.wait_event(copied[i % 2])
-        o = module(d_idx, d_offs)  # autograd-tracked lookup; backward runs the fused optimizer
-        if world > 1:
-            dist.all_to_all_single(a2a_out.view(world, -1), o.detach().view(world, -1))
-            dist.all_to_all_single(a2a_grad.view(world, -1), grad.view(world, -1))
-            o.backward(a2a_grad)
-        else:
+        if world == 1:
+            o = module(d_idx, d_offs)  # autograd-tracked lookup; backward runs the fused optimizer
             o.backward(grad)
+            res = o
+        else:
+            idx, offs, _ = owner_view(i, ids_local=d_idx)
+            o = module(idx, offs)
+            res = sh.exchange_outputs(o.detach(), BATCH)
+            o.backward(sh.exchange_gradients(grad))
         consumed[i % 2].record(main_stream)
-        result_host.copy_(o.detach().view(-1)[:4096], non_blocking=True)
+        result_host.copy_(res.detach().reshape(-1)[:4096], non_blocking=True)
 
     def run_e2e(n):
         for e in consumed:
@@ -292,7 +302,8 @@ def run_ours(args):
         # whole step, SURVEY formula: dedup + fwd + bwd
         step_bytes = (16 * N + 8 * U) + (N * (8 + 4 * DIM) + 8 * (N + 1) + 4 * DIM * N) + \
                      (4 * DIM * N + 8 * N + 8 * U + U * 4 * DIM * 2 * (1 + S))
-        passes = math.ceil(module.total_hash_size_bits / 8)
+        bits = module.total_hash_size_bits
+        passes = min(math.ceil(bits / 8), math.ceil(bits / 9))  # the sort takes 9-bit digits when that saves a pass
         launches_per_step = 1 + (1 + 3 * passes + 3 + 1 + 1 + 1)  # forward + expand, sort, run scan, plan, partial, update
         line = {
             "metric": "embedding ids/sec (fwd+bwd+sparse Adam)",
@@ -324,7 +335,7 @@ def run_ours(args):
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                          "bytes_per_launch": upd_bytes, "ms_per_launch": upd_ms_avg, "traffic": None},
             "e2e": {"value": ids_per_step / (e2e_ms_step * 1e-3), "unit": "ids/s", "ms_per_step": e2e_ms_step,
-                    "h2d_bytes_per_step": int(d_bufs[0][0].numel() * 8 + d_bufs[0][1].numel() * 8),
+                    "h2d_bytes_per_step": int(h2d_bytes),
                     "d2h_bytes_per_step": int(result_host.numel() * 4)},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,

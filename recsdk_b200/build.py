@@ -73,5 +73,31 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> str:
     return LIB
 
 
+def build_torch_ops(verbose: bool = False) -> str:
+    """Compiles csrc_torch/torch_ops.cpp (torch custom-op registration over the C ABI) against the installed
+    libtorch and links it to librecsdk_b200.so (found at run time next to it through $ORIGIN)."""
+    import torch
+
+    src = os.path.join(PKG, "csrc_torch", "torch_ops.cpp")
+    hdr = os.path.join(ROOT, "include", "recsdk_b200.h")
+    if not _stale(TORCH_LIB, [src, hdr]) and os.path.exists(LIB):
+        return TORCH_LIB
+    build()
+    tdir = os.path.dirname(torch.__file__)
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+           f"-I{os.path.join(ROOT, 'include')}", f"-I{tdir}/include", f"-I{tdir}/include/torch/csrc/api/include",
+           f"-I{cuda_inc}", src, "-o", TORCH_LIB, f"-L{PKG}", "-lrecsdk_b200", f"-L{tdir}/lib", "-ltorch", "-ltorch_cpu",
+           "-ltorch_cuda", "-lc10", "-lc10_cuda", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tdir}/lib"]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return TORCH_LIB
+
+
 if __name__ == "__main__":
+    if "--torch" in sys.argv:
+        print(build_torch_ops(verbose=True))
+        sys.exit(0)
     print(build(verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv))

@@ -176,7 +176,8 @@ static inline void device_scan_fn(InFn in, OutFn out, int64_t n, int* scratch, i
 }
 
 // ----------------------------------------------------------------------------
-// Stable LSD radix sort of (key, uint32 value) pairs, 8 bits per pass.
+// Stable LSD radix sort of (key, uint32 value) pairs, 8 or 9 bits per pass
+// (9 when that saves a pass, e.g. 27-bit keys: 3 passes instead of 4).
 // Per pass: tile histograms -> per-digit scan across tiles -> stable scatter
 // (warp match-any ranking).  Tile = 256 threads x 8 items; warp w owns the
 // contiguous 256 items [w*256, (w+1)*256) of the tile, taken 32 at a time, so
@@ -185,18 +186,19 @@ static inline void device_scan_fn(InFn in, OutFn out, int64_t n, int* scratch, i
 constexpr int kSortThreads = 256;
 constexpr int kSortRounds = 8;
 constexpr int kSortTile = kSortThreads * kSortRounds;  // 2048
-constexpr int kRadix = 256;
+constexpr int kMaxRadix = 512;
 
 static inline int64_t sort_num_tiles(int64_t n) { return ceil_div(n > 0 ? n : 1, kSortTile); }
-// uint32 scratch needed: histogram [256][tiles] + digit totals [256]
-static inline size_t sort_scratch_u32(int64_t n) { return static_cast<size_t>(sort_num_tiles(n)) * kRadix + kRadix; }
+// uint32 scratch needed: histogram [radix][tiles] + digit totals [radix]
+static inline size_t sort_scratch_u32(int64_t n) { return static_cast<size_t>(sort_num_tiles(n)) * kMaxRadix + kMaxRadix; }
 
-template <typename KeyT>
+template <typename KeyT, int BITS>
 __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const KeyT* __restrict__ keys, int64_t n, int shift,
                                                                  uint32_t* __restrict__ hist, int64_t tiles)
 {
-    __shared__ uint32_t h[kRadix];
-    h[threadIdx.x] = 0;
+    constexpr int RADIX = 1 << BITS;
+    __shared__ uint32_t h[RADIX];
+    for (int d = threadIdx.x; d < RADIX; d += kSortThreads) h[d] = 0;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * kSortTile + warp * (kSortRounds * 32);
@@ -204,13 +206,13 @@ __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const KeyT* __r
     for (int r = 0; r < kSortRounds; ++r) {
         const int64_t i = tile0 + r * 32 + lane;
         const bool valid = i < n;
-        const unsigned tag = valid ? static_cast<unsigned>((keys[i] >> shift) & 0xff) : (0x100u + lane);
+        const unsigned tag = valid ? static_cast<unsigned>((keys[i] >> shift) & (RADIX - 1)) : (RADIX + lane);
         // one shared-memory atomic per distinct digit in the warp, not per item
         const unsigned peers = __match_any_sync(kFullMask, tag);
         if (valid && (peers & lanemask_lt()) == 0) atomicAdd(&h[tag], static_cast<uint32_t>(__popc(peers)));
     }
     __syncthreads();
-    hist[static_cast<int64_t>(threadIdx.x) * tiles + blockIdx.x] = h[threadIdx.x];
+    for (int d = threadIdx.x; d < RADIX; d += kSortThreads) hist[static_cast<int64_t>(d) * tiles + blockIdx.x] = h[d];
 }
 
 // One block per digit: exclusive scan of hist[d][0..tiles) in place, total -> totals[d].
@@ -231,7 +233,7 @@ static __global__ void __launch_bounds__(256) sort_scan_kernel(uint32_t* __restr
     if (threadIdx.x == 0) totals[blockIdx.x] = static_cast<uint32_t>(carry);
 }
 
-template <typename KeyT>
+template <typename KeyT, int BITS>
 __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* __restrict__ keys_in,
                                                                     const uint32_t* __restrict__ vals_in,
                                                                     KeyT* __restrict__ keys_out,
@@ -240,11 +242,13 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
                                                                     const uint32_t* __restrict__ totals,
                                                                     int64_t tiles)
 {
-    __shared__ uint32_t warp_cnt[kSortThreads / 32][kRadix];
+    constexpr int RADIX = 1 << BITS;
+    constexpr int PER = RADIX / kSortThreads;  // digits per thread in the block-wide steps
+    __shared__ uint32_t warp_cnt[kSortThreads / 32][RADIX];
     __shared__ int sm[33];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#pragma unroll
-    for (int w = 0; w < kSortThreads / 32; ++w) warp_cnt[w][threadIdx.x] = 0;
+    for (int w = 0; w < kSortThreads / 32; ++w)
+        for (int d = threadIdx.x; d < RADIX; d += kSortThreads) warp_cnt[w][d] = 0;
     __syncthreads();
 
     const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * kSortTile + warp * (kSortRounds * 32);
@@ -256,7 +260,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
         const bool valid = i < n;
         key[r] = valid ? keys_in[i] : KeyT(0);
         // invalid lanes get a tag no valid lane can have, so they match nobody valid
-        const unsigned tag = valid ? static_cast<unsigned>((key[r] >> shift) & 0xff) : (0x100u + lane);
+        const unsigned tag = valid ? static_cast<unsigned>((key[r] >> shift) & (RADIX - 1)) : (RADIX + lane);
         const unsigned peers = __match_any_sync(kFullMask, tag);
         const unsigned before = __popc(peers & lanemask_lt());
         uint32_t prev = 0;
@@ -268,18 +272,30 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
     }
     __syncthreads();
 
-    // digit base for this tile: exclusive scan of digit totals + this tile's prefix inside the digit
+    // digit base for this tile: exclusive scan of digit totals + this tile's prefix inside the digit;
+    // thread t owns the PER consecutive digits [t*PER, t*PER+PER)
     {
-        const int d = threadIdx.x;
-        int tot = static_cast<int>(totals[d]);
-        int total_all;
-        int inc = block_inclusive_scan(tot, sm, &total_all);
-        uint32_t run = static_cast<uint32_t>(inc - tot) + hist[static_cast<int64_t>(d) * tiles + blockIdx.x];
+        int tot[PER];
+        int mine = 0;
 #pragma unroll
-        for (int w = 0; w < kSortThreads / 32; ++w) {
-            uint32_t c = warp_cnt[w][d];
-            warp_cnt[w][d] = run;
-            run += c;
+        for (int q = 0; q < PER; ++q) {
+            tot[q] = static_cast<int>(totals[threadIdx.x * PER + q]);
+            mine += tot[q];
+        }
+        int total_all;
+        const int inc = block_inclusive_scan(mine, sm, &total_all);
+        uint32_t digit_base = static_cast<uint32_t>(inc - mine);
+#pragma unroll
+        for (int q = 0; q < PER; ++q) {
+            const int d = threadIdx.x * PER + q;
+            uint32_t run = digit_base + hist[static_cast<int64_t>(d) * tiles + blockIdx.x];
+#pragma unroll
+            for (int w = 0; w < kSortThreads / 32; ++w) {
+                const uint32_t c = warp_cnt[w][d];
+                warp_cnt[w][d] = run;
+                run += c;
+            }
+            digit_base += static_cast<uint32_t>(tot[q]);
         }
     }
     __syncthreads();
@@ -288,12 +304,34 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
     for (int r = 0; r < kSortRounds; ++r) {
         const int64_t i = tile0 + r * 32 + lane;
         if (i < n) {
-            const unsigned d = static_cast<unsigned>((key[r] >> shift) & 0xff);
+            const unsigned d = static_cast<unsigned>((key[r] >> shift) & (RADIX - 1));
             const uint32_t pos = warp_cnt[warp][d] + rank[r];
             keys_out[pos] = key[r];
             vals_out[pos] = vals_in[i];
         }
     }
+}
+
+template <typename KeyT, int BITS>
+static inline void radix_sort_pass(const KeyT* kin, const uint32_t* vin, KeyT* kout, uint32_t* vout, int64_t n, int shift,
+                                   uint32_t* scratch, cudaStream_t st)
+{
+    constexpr int RADIX = 1 << BITS;
+    const int64_t tiles = sort_num_tiles(n);
+    uint32_t* hist = scratch;
+    uint32_t* totals = scratch + tiles * RADIX;
+    sort_hist_kernel<KeyT, BITS><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, n, shift, hist, tiles);
+    sort_scan_kernel<<<RADIX, 256, 0, st>>>(hist, tiles, totals);
+    sort_scatter_kernel<KeyT, BITS><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, vin, kout, vout, n, shift,
+                                                                                          hist, totals, tiles);
+}
+
+// Number of passes and bits per pass for keys of `key_bits` significant bits.
+static inline void radix_plan(int key_bits, int* passes, int* bits)
+{
+    const int p8 = (key_bits + 7) / 8, p9 = (key_bits + 8) / 9;
+    *bits = p9 < p8 ? 9 : 8;
+    *passes = p9 < p8 ? p9 : p8;
 }
 
 // Sorts n pairs by the key bits [0, key_bits).  Data ping-pongs between
@@ -304,19 +342,18 @@ static inline int radix_sort_pairs(KeyT* keys_a, uint32_t* vals_a, KeyT* keys_b,
                                    int key_bits, uint32_t* scratch, cudaStream_t st)
 {
     if (n <= 1 || key_bits <= 0) return 0;
-    const int64_t tiles = sort_num_tiles(n);
-    uint32_t* hist = scratch;
-    uint32_t* totals = scratch + tiles * kRadix;
+    int passes, bits;
+    radix_plan(key_bits, &passes, &bits);
     int cur = 0;
-    for (int shift = 0; shift < key_bits; shift += 8) {
+    for (int p = 0; p < passes; ++p) {
         KeyT* kin = cur ? keys_b : keys_a;
         uint32_t* vin = cur ? vals_b : vals_a;
         KeyT* kout = cur ? keys_a : keys_b;
         uint32_t* vout = cur ? vals_a : vals_b;
-        sort_hist_kernel<KeyT><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, n, shift, hist, tiles);
-        sort_scan_kernel<<<kRadix, 256, 0, st>>>(hist, tiles, totals);
-        sort_scatter_kernel<KeyT><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, vin, kout, vout, n, shift,
-                                                                                        hist, totals, tiles);
+        if (bits == 9)
+            radix_sort_pass<KeyT, 9>(kin, vin, kout, vout, n, p * 9, scratch, st);
+        else
+            radix_sort_pass<KeyT, 8>(kin, vin, kout, vout, n, p * 8, scratch, st);
         cur ^= 1;
     }
     return cur;

@@ -1,0 +1,544 @@
+// Torch custom-op registration over the C ABI of include/recsdk_b200.h.
+//
+// Same schema strings as the reference's registration
+// (cust_op/framework/torch_plugin/torch_library/2.6.0/split_embedding_codegen_forward_unweighted/
+//  split_embedding_codegen_forward_unweighted.cpp:77-95, backward_codegen_adagrad_unweighted_exact.cpp:282-365,
+//  backward_codegen_adam_unweighted_exact.cpp:418-505, backward_codegen_sgd_unweighted_exact.cpp:336-417),
+// registered under `fbgemm::` (what the reference's invokers call) and, identically, under `recsdk::`
+// (usable when a real fbgemm_gpu owns the fbgemm namespace; build with -DRECSDK_NO_FBGEMM_NS then).
+// The implementations enqueue the CUDA kernels of librecsdk_b200.so on the current stream; uvm / lxu cache /
+// placements / vbe arguments are accepted and ignored, as in the reference.
+// Also: class `recsdk::IdsMapper` with the methods of `hybrid::IdsMapper`
+// (hybrid_torchrec/src/bind_torch_lib.cpp:9-19) and `recsdk::block_bucketize_sparse_features`.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/csrc/autograd/custom_function.h>
+#include <torch/custom_class.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+
+#include "recsdk_b200.h"
+
+namespace recsdk_torch {
+
+using at::Tensor;
+using torch::autograd::AutogradContext;
+using torch::autograd::variable_list;
+
+static void* cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+static void check_rc(int rc, const char* where) { TORCH_CHECK(rc == RECSDK_OK, where, ": ", recsdk_error_string(rc)); }
+
+static const Tensor& pick(const Tensor& indices, const Tensor& hash_indices)
+{
+    return (hash_indices.defined() && hash_indices.numel() > 0) ? hash_indices : indices;
+}
+
+static void check_i64(const Tensor& t, const char* name)
+{
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(t.scalar_type() == at::kLong, name, " must be int64");
+    TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+// ---------------------------------------------------------------------------- forward
+Tensor forward_unweighted_cuda(const Tensor& dev_weights, const Tensor& uvm_weights, const Tensor& lxu_cache_weights,
+                               const Tensor& weights_placements, const Tensor& weights_offsets, const Tensor& D_offsets,
+                               c10::SymInt total_D, c10::SymInt max_D, const Tensor& indices, const Tensor& offsets,
+                               int64_t pooling_mode, const Tensor& lxu_cache_locations, const Tensor& uvm_cache_stats,
+                               int64_t output_dtype, bool is_experimental, const Tensor& hash_indices,
+                               const Tensor& offset_per_key)
+{
+    const int64_t totalD = total_D.guard_int(__FILE__, __LINE__);
+    const int64_t maxD = max_D.guard_int(__FILE__, __LINE__);
+    TORCH_CHECK(dev_weights.is_cuda(), "dev_weights must be a CUDA tensor (recsdk_b200 has no CPU path)");
+    const c10::cuda::OptionalCUDAGuard guard(device_of(dev_weights));
+    const int64_t T = weights_offsets.size(0);
+    const Tensor& idx = pick(indices, hash_indices);
+    if (T == 0 || idx.numel() == 0) return Tensor();  // forward.cpp:49-55
+    TORCH_CHECK((offsets.size(0) - 1) % T == 0, "offset size = ", offsets.size(0),
+                " is incorrect for feature count = ", T);
+    TORCH_CHECK(dev_weights.scalar_type() == at::kFloat && dev_weights.is_contiguous(), "dev_weights must be contiguous fp32");
+    TORCH_CHECK(D_offsets.scalar_type() == at::kInt, "D_offsets must be int32");
+    check_i64(idx, "indices");
+    check_i64(offsets, "offsets");
+    check_i64(weights_offsets, "weights_offsets");
+    const int64_t B = (offsets.size(0) - 1) / T;
+    Tensor out = pooling_mode == RECSDK_POOL_NONE ? at::empty({idx.numel(), maxD}, dev_weights.options())
+                                                  : at::empty({B, totalD}, dev_weights.options());
+    recsdk_tbe_forward_args a{};
+    a.dev_weights = dev_weights.data_ptr<float>();
+    a.weights_offsets = weights_offsets.data_ptr<int64_t>();
+    a.D_offsets = D_offsets.data_ptr<int32_t>();
+    a.indices = idx.data_ptr<int64_t>();
+    a.offsets = offsets.data_ptr<int64_t>();
+    a.out = out.data_ptr<float>();
+    a.T = T;
+    a.B = B;
+    a.N = idx.numel();
+    a.total_D = static_cast<int32_t>(totalD);
+    a.max_D = static_cast<int32_t>(maxD);
+    a.pooling_mode = static_cast<int32_t>(pooling_mode);
+    check_rc(recsdk_tbe_forward(&a, cur_stream()), "split_embedding_codegen_forward_unweighted_cuda");
+    return out;
+}
+
+// ---------------------------------------------------------------------------- fused backward
+struct OptArgs {
+    int optimizer;
+    double eps = 0, lr = 0, beta1 = 0.9, beta2 = 0.999;
+    int64_t iter = 1;
+};
+
+static Tensor backward_exact(const Tensor& grad_output_in, const Tensor& dev_weights, const Tensor& weights_offsets,
+                             const Tensor& D_offsets, int64_t max_D, const Tensor& hash_size_cumsum,
+                             int64_t total_hash_size_bits, const Tensor& indices, const Tensor& offsets,
+                             int64_t pooling_mode, const Tensor& momentum1, const Tensor& momentum2,
+                             const Tensor& hash_indices, const Tensor& unique_ids, const Tensor& unique_offsets,
+                             const Tensor& unique_inverse, const OptArgs& o)
+{
+    TORCH_CHECK(dev_weights.is_cuda(), "dev_weights must be a CUDA tensor (recsdk_b200 has no CPU path)");
+    const c10::cuda::OptionalCUDAGuard guard(device_of(dev_weights));
+    const int64_t T = weights_offsets.size(0);
+    const Tensor& idx = pick(indices, hash_indices);
+    if (T == 0 || idx.numel() == 0) return Tensor();
+    Tensor grad_output = grad_output_in.contiguous();
+    TORCH_CHECK(grad_output.scalar_type() == at::kFloat, "grad_output must be fp32");
+    check_i64(idx, "indices");
+    check_i64(offsets, "offsets");
+    const int64_t B = (offsets.size(0) - 1) / T;
+    recsdk_tbe_backward_args b{};
+    b.grad_output = grad_output.data_ptr<float>();
+    b.dev_weights = dev_weights.data_ptr<float>();
+    if (o.optimizer != RECSDK_OPT_SGD) b.momentum1 = momentum1.data_ptr<float>();
+    if (o.optimizer == RECSDK_OPT_ADAM) b.momentum2 = momentum2.data_ptr<float>();
+    b.weights_offsets = weights_offsets.data_ptr<int64_t>();
+    b.D_offsets = D_offsets.data_ptr<int32_t>();
+    b.hash_size_cumsum = hash_size_cumsum.defined() && hash_size_cumsum.numel() ? hash_size_cumsum.data_ptr<int64_t>() : nullptr;
+    b.indices = idx.data_ptr<int64_t>();
+    b.offsets = offsets.data_ptr<int64_t>();
+    const bool have_unique = unique_ids.defined() && unique_ids.numel() > 0;
+    if (have_unique) {
+        check_i64(unique_ids, "unique_ids");
+        check_i64(unique_offsets, "unique_offsets");
+        check_i64(unique_inverse, "unique_inverse");
+        b.unique_ids = unique_ids.data_ptr<int64_t>();
+        b.unique_offsets = unique_offsets.data_ptr<int64_t>();
+        b.unique_inverse = unique_inverse.data_ptr<int64_t>();
+        b.num_unique_capacity = unique_ids.numel();
+    }
+    b.T = T;
+    b.B = B;
+    b.N = idx.numel();
+    b.total_D = static_cast<int32_t>(pooling_mode == RECSDK_POOL_NONE ? max_D : grad_output.size(1));
+    b.max_D = static_cast<int32_t>(max_D);
+    b.pooling_mode = static_cast<int32_t>(pooling_mode);
+    b.optimizer = o.optimizer;
+    b.total_hash_size_bits = static_cast<int32_t>(total_hash_size_bits);
+    b.reduce_chunk = 64;
+    b.learning_rate = static_cast<float>(o.lr);
+    b.eps = static_cast<float>(o.eps);
+    b.beta1 = static_cast<float>(o.beta1);
+    b.beta2 = static_cast<float>(o.beta2);
+    b.iter = o.iter;
+    Tensor ws = at::empty({static_cast<int64_t>(recsdk_tbe_backward_workspace_bytes(b.N, b.max_D))},
+                          dev_weights.options().dtype(at::kByte));
+    b.workspace = ws.data_ptr();
+    b.workspace_bytes = static_cast<size_t>(ws.numel());
+    check_rc(recsdk_tbe_backward(&b, cur_stream()), "split_embedding_backward_codegen_unweighted_exact_cuda");
+    return Tensor();  // like the reference: state is updated in place, no weight gradient is returned
+}
+
+Tensor backward_adagrad_cuda(const Tensor& grad_output, const Tensor& dev_weights, const Tensor&, const Tensor&,
+                             const Tensor&, const Tensor& weights_offsets, const Tensor& D_offsets, c10::SymInt max_D,
+                             const Tensor& hash_size_cumsum, int64_t total_hash_size_bits, const Tensor& indices,
+                             const Tensor& offsets, int64_t pooling_mode, const Tensor&, int64_t, int64_t, bool, int64_t,
+                             int64_t, bool, bool, Tensor momentum1_dev, Tensor, Tensor, Tensor, const Tensor& hash_indices,
+                             const Tensor& unique_ids, const Tensor& unique_offsets, const Tensor& unique_inverse,
+                             const Tensor&, double eps, double learning_rate)
+{
+    OptArgs o{RECSDK_OPT_ADAGRAD, eps, learning_rate};
+    return backward_exact(grad_output, dev_weights, weights_offsets, D_offsets, max_D.guard_int(__FILE__, __LINE__),
+                          hash_size_cumsum, total_hash_size_bits, indices, offsets, pooling_mode, momentum1_dev, Tensor(),
+                          hash_indices, unique_ids, unique_offsets, unique_inverse, o);
+}
+
+Tensor backward_adam_cuda(const Tensor& grad_output, const Tensor& dev_weights, const Tensor&, const Tensor&, const Tensor&,
+                          const Tensor& weights_offsets, const Tensor& D_offsets, c10::SymInt max_D,
+                          const Tensor& hash_size_cumsum, int64_t total_hash_size_bits, const Tensor& indices,
+                          const Tensor& offsets, int64_t pooling_mode, const Tensor&, int64_t, int64_t, bool, int64_t, int64_t,
+                          bool, bool, Tensor momentum1_dev, Tensor, Tensor, Tensor, Tensor momentum2_dev, Tensor, Tensor, Tensor,
+                          const Tensor& hash_indices, const Tensor& unique_ids, const Tensor& unique_offsets,
+                          const Tensor& unique_inverse, const Tensor&, double eps, double learning_rate, double beta1,
+                          double beta2, int64_t iter)
+{
+    OptArgs o{RECSDK_OPT_ADAM, eps, learning_rate, beta1, beta2, iter};
+    return backward_exact(grad_output, dev_weights, weights_offsets, D_offsets, max_D.guard_int(__FILE__, __LINE__),
+                          hash_size_cumsum, total_hash_size_bits, indices, offsets, pooling_mode, momentum1_dev,
+                          momentum2_dev, hash_indices, unique_ids, unique_offsets, unique_inverse, o);
+}
+
+Tensor backward_sgd_cuda(const Tensor& grad_output, const Tensor& dev_weights, const Tensor&, const Tensor&, const Tensor&,
+                         const Tensor& weights_offsets, const Tensor& D_offsets, c10::SymInt max_D,
+                         const Tensor& hash_size_cumsum, int64_t total_hash_size_bits, const Tensor& indices,
+                         const Tensor& offsets, int64_t pooling_mode, const Tensor&, int64_t, int64_t, bool, int64_t, int64_t,
+                         bool, bool, const Tensor& hash_indices, const Tensor& unique_ids, const Tensor& unique_offsets,
+                         const Tensor& unique_inverse, const Tensor&, double learning_rate)
+{
+    OptArgs o{RECSDK_OPT_SGD, 0.0, learning_rate};
+    return backward_exact(grad_output, dev_weights, weights_offsets, D_offsets, max_D.guard_int(__FILE__, __LINE__),
+                          hash_size_cumsum, total_hash_size_bits, indices, offsets, pooling_mode, Tensor(), Tensor(),
+                          hash_indices, unique_ids, unique_offsets, unique_inverse, o);
+}
+
+// ---------------------------------------------------------------------------- autograd lookup functions
+// One Function for the three optimizers (the reference has SplitLookupAdagrad / SplitLookupAdam / SplitLookupSgd,
+// e.g. backward_codegen_adam_unweighted_exact.cpp:65-284): forward = pooled gather, backward = optional clamp of
+// the incoming gradient + fused segment-sum / optimizer, no gradient for any input.
+class SplitLookup : public torch::autograd::Function<SplitLookup> {
+public:
+    static variable_list forward(AutogradContext* ctx, const Tensor& placeholder_autograd_tensor, int64_t optimizer,
+                                 const Tensor& dev_weights, const Tensor& weights_offsets, const Tensor& D_offsets,
+                                 int64_t total_D, int64_t max_D, const Tensor& hash_size_cumsum,
+                                 int64_t total_hash_size_bits, const Tensor& indices,
+                                 const std::optional<Tensor>& hash_indices_, const std::optional<Tensor>& unique_ids_,
+                                 const std::optional<Tensor>& unique_offsets_, const std::optional<Tensor>& unique_inverse_,
+                                 const Tensor& offsets, int64_t pooling_mode, bool gradient_clipping, double max_gradient,
+                                 const std::optional<Tensor>& momentum1_, const std::optional<Tensor>& momentum2_, double eps,
+                                 double lr, double beta1, double beta2, int64_t iter)
+    {
+        if (weights_offsets.size(0) == 0) return {Tensor()};
+        // optional tensors travel through apply() as std::optional (an undefined Tensor argument is rejected there)
+        const Tensor hash_indices = hash_indices_.value_or(Tensor()), unique_ids = unique_ids_.value_or(Tensor()),
+                     unique_offsets = unique_offsets_.value_or(Tensor()), unique_inverse = unique_inverse_.value_or(Tensor()),
+                     momentum1 = momentum1_.value_or(Tensor()), momentum2 = momentum2_.value_or(Tensor());
+        ctx->save_for_backward({dev_weights, weights_offsets, D_offsets, hash_size_cumsum, indices, offsets, momentum1,
+                                momentum2, hash_indices, unique_ids, unique_offsets, unique_inverse});
+        ctx->saved_data["optimizer"] = optimizer;
+        ctx->saved_data["max_D"] = max_D;
+        ctx->saved_data["bits"] = total_hash_size_bits;
+        ctx->saved_data["pooling_mode"] = pooling_mode;
+        ctx->saved_data["gradient_clipping"] = gradient_clipping;
+        ctx->saved_data["max_gradient"] = max_gradient;
+        ctx->saved_data["eps"] = eps;
+        ctx->saved_data["lr"] = lr;
+        ctx->saved_data["beta1"] = beta1;
+        ctx->saved_data["beta2"] = beta2;
+        ctx->saved_data["iter"] = iter;
+        const Tensor none;
+        return {forward_unweighted_cuda(dev_weights, none, none, none, weights_offsets, D_offsets, total_D, max_D, indices,
+                                        offsets, pooling_mode, none, none, 0, false, hash_indices, none)};
+    }
+
+    static variable_list backward(AutogradContext* ctx, variable_list grad_outputs)
+    {
+        const auto s = ctx->get_saved_variables();
+        TORCH_CHECK_EQ(grad_outputs.size(), 1);
+        Tensor g = grad_outputs[0];
+        if (ctx->saved_data["gradient_clipping"].toBool()) {
+            const double mg = ctx->saved_data["max_gradient"].toDouble();
+            g = at::clamp(g, -mg, mg);  // backward_codegen_adagrad_unweighted_exact.cpp:153
+        }
+        OptArgs o{static_cast<int>(ctx->saved_data["optimizer"].toInt()), ctx->saved_data["eps"].toDouble(),
+                  ctx->saved_data["lr"].toDouble(), ctx->saved_data["beta1"].toDouble(),
+                  ctx->saved_data["beta2"].toDouble(), ctx->saved_data["iter"].toInt()};
+        backward_exact(g, s[0], s[1], s[2], ctx->saved_data["max_D"].toInt(), s[3], ctx->saved_data["bits"].toInt(), s[4],
+                       s[5], ctx->saved_data["pooling_mode"].toInt(), s[6], s[7], s[8], s[9], s[10], s[11], o);
+        return variable_list(25);  // no gradient for any of the 25 forward inputs
+    }
+};
+
+static std::optional<Tensor> opt_or_empty(const std::optional<Tensor>& t)
+{
+    return (t.has_value() && t->defined()) ? t : std::nullopt;
+}
+
+Tensor lookup_adagrad_function(
+    const Tensor& placeholder_autograd_tensor, const Tensor& dev_weights, const Tensor&, const Tensor&, const Tensor&,
+    const Tensor& weights_offsets, const Tensor& D_offsets, c10::SymInt total_D, c10::SymInt max_D,
+    const Tensor& hash_size_cumsum, int64_t total_hash_size_bits, const Tensor& indices, const Tensor& offsets,
+    int64_t pooling_mode, const std::optional<Tensor>& indice_weights, const std::optional<Tensor>&, const Tensor&,
+    bool gradient_clipping, double max_gradient, bool, Tensor momentum1_dev, Tensor, Tensor, Tensor,
+    const std::optional<Tensor>& hash_indices, const std::optional<Tensor>& unique_ids,
+    const std::optional<Tensor>& unique_offsets, const std::optional<Tensor>& unique_inverse, double eps,
+    double learning_rate, int64_t, const std::optional<Tensor>&, const std::optional<Tensor>&,
+    const std::optional<Tensor>&, c10::SymInt, c10::SymInt, c10::SymInt, bool, bool, bool, const std::optional<Tensor>&,
+    const std::optional<Tensor>&, int64_t, bool, double)
+{
+    TORCH_CHECK(!indice_weights.has_value(), "weighted lookups are not supported");
+    return SplitLookup::apply(placeholder_autograd_tensor, RECSDK_OPT_ADAGRAD, dev_weights, weights_offsets, D_offsets,
+                              total_D.guard_int(__FILE__, __LINE__), max_D.guard_int(__FILE__, __LINE__), hash_size_cumsum,
+                              total_hash_size_bits, indices, opt_or_empty(hash_indices), opt_or_empty(unique_ids),
+                              opt_or_empty(unique_offsets), opt_or_empty(unique_inverse), offsets, pooling_mode,
+                              gradient_clipping, max_gradient, std::optional<Tensor>(momentum1_dev), std::nullopt, eps,
+                              learning_rate, 0.0, 0.0, 0)[0];
+}
+
+Tensor lookup_adam_function(
+    const Tensor& placeholder_autograd_tensor, const Tensor& dev_weights, const Tensor&, const Tensor&, const Tensor&,
+    const Tensor& weights_offsets, const Tensor& D_offsets, c10::SymInt total_D, c10::SymInt max_D,
+    const Tensor& hash_size_cumsum, int64_t total_hash_size_bits, const Tensor& indices, const Tensor& offsets,
+    int64_t pooling_mode, const std::optional<Tensor>& indice_weights, const std::optional<Tensor>&, const Tensor&,
+    bool gradient_clipping, double max_gradient, bool, Tensor momentum1_dev, Tensor, Tensor, Tensor, Tensor momentum2_dev,
+    Tensor, Tensor, Tensor, const std::optional<Tensor>& hash_indices, const std::optional<Tensor>& unique_ids,
+    const std::optional<Tensor>& unique_offsets, const std::optional<Tensor>& unique_inverse, double eps,
+    double learning_rate, double beta1, double beta2, double, int64_t iter, int64_t, const std::optional<Tensor>&,
+    const std::optional<Tensor>&, const std::optional<Tensor>&, c10::SymInt, c10::SymInt, c10::SymInt, bool, bool, bool,
+    const std::optional<Tensor>&, const std::optional<Tensor>&, bool, double)
+{
+    TORCH_CHECK(!indice_weights.has_value(), "weighted lookups are not supported");
+    return SplitLookup::apply(placeholder_autograd_tensor, RECSDK_OPT_ADAM, dev_weights, weights_offsets, D_offsets,
+                              total_D.guard_int(__FILE__, __LINE__), max_D.guard_int(__FILE__, __LINE__), hash_size_cumsum,
+                              total_hash_size_bits, indices, opt_or_empty(hash_indices), opt_or_empty(unique_ids),
+                              opt_or_empty(unique_offsets), opt_or_empty(unique_inverse), offsets, pooling_mode,
+                              gradient_clipping, max_gradient, std::optional<Tensor>(momentum1_dev),
+                              std::optional<Tensor>(momentum2_dev), eps, learning_rate, beta1, beta2, iter)[0];
+}
+
+Tensor lookup_sgd_function(
+    const Tensor& placeholder_autograd_tensor, const Tensor& dev_weights, const Tensor&, const Tensor&, const Tensor&,
+    const Tensor& weights_offsets, const Tensor& D_offsets, c10::SymInt total_D, c10::SymInt max_D,
+    const Tensor& hash_size_cumsum, int64_t total_hash_size_bits, const Tensor& indices, const Tensor& offsets,
+    int64_t pooling_mode, const std::optional<Tensor>& indice_weights, const std::optional<Tensor>&, const Tensor&,
+    bool gradient_clipping, double max_gradient, bool, const std::optional<Tensor>& hash_indices,
+    const std::optional<Tensor>& unique_ids, const std::optional<Tensor>& unique_offsets,
+    const std::optional<Tensor>& unique_inverse, double learning_rate, int64_t, const std::optional<Tensor>&,
+    const std::optional<Tensor>&, const std::optional<Tensor>&, c10::SymInt, c10::SymInt, c10::SymInt, bool, bool, bool,
+    const std::optional<Tensor>&, const std::optional<Tensor>&, int64_t, bool, double)
+{
+    TORCH_CHECK(!indice_weights.has_value(), "weighted lookups are not supported");
+    return SplitLookup::apply(placeholder_autograd_tensor, RECSDK_OPT_SGD, dev_weights, weights_offsets, D_offsets,
+                              total_D.guard_int(__FILE__, __LINE__), max_D.guard_int(__FILE__, __LINE__), hash_size_cumsum,
+                              total_hash_size_bits, indices, opt_or_empty(hash_indices), opt_or_empty(unique_ids),
+                              opt_or_empty(unique_offsets), opt_or_empty(unique_inverse), offsets, pooling_mode,
+                              gradient_clipping, max_gradient, std::nullopt, std::nullopt, 0.0, learning_rate, 0.0, 0.0, 0)[0];
+}
+
+// ---------------------------------------------------------------------------- schemas
+static const char* kFwdSchema =
+    "split_embedding_codegen_forward_unweighted_cuda(Tensor dev_weights, Tensor uvm_weights, Tensor lxu_cache_weights, "
+    "Tensor weights_placements, Tensor weights_offsets, Tensor D_offsets, SymInt total_D, SymInt max_D, Tensor indices, "
+    "Tensor offsets, int pooling_mode, Tensor lxu_cache_locations, Tensor uvm_cache_stats, int output_dtype, "
+    "bool is_experimental, Tensor hash_indices = None, Tensor offset_per_key = None) -> Tensor";
+
+#define RECSDK_LOOKUP_HEAD                                                                                             \
+    "Tensor placeholder_autograd_tensor, Tensor(a!) dev_weights, Tensor(b!) uvm_weights, Tensor lxu_cache_weights, "   \
+    "Tensor weights_placements, Tensor weights_offsets, Tensor D_offsets, SymInt total_D, SymInt max_D, "              \
+    "Tensor hash_size_cumsum, int total_hash_size_bits, Tensor indices, Tensor offsets, int pooling_mode, "            \
+    "Tensor? indice_weights, Tensor? feature_requires_grad, Tensor lxu_cache_locations, bool gradient_clipping, "      \
+    "float max_gradient, bool stochastic_rounding, "
+#define RECSDK_LOOKUP_UNIQ \
+    "Tensor? hash_indices = None, Tensor? unique_ids = None, Tensor? unique_offsets = None, Tensor? unique_inverse = None, "
+#define RECSDK_LOOKUP_VBE                                                                                              \
+    "int output_dtype=0, Tensor? B_offsets=None, Tensor? vbe_output_offsets_feature_rank=None, "                       \
+    "Tensor? vbe_B_offsets_rank_per_feature=None, SymInt max_B=-1, SymInt max_B_feature_rank=-1, "                     \
+    "SymInt vbe_output_size=-1, bool is_experimental=False, bool use_uniq_cache_locations_bwd=False, "                 \
+    "bool use_homogeneous_placements=False, Tensor? uvm_cache_stats=None, Tensor? prev_iter_dev=None, "
+#define RECSDK_MOM1 "Tensor momentum1_dev, Tensor momentum1_uvm, Tensor momentum1_placements, Tensor momentum1_offsets, "
+#define RECSDK_MOM2 "Tensor momentum2_dev, Tensor momentum2_uvm, Tensor momentum2_placements, Tensor momentum2_offsets, "
+#define RECSDK_BWD_HEAD                                                                                                \
+    "Tensor grad_output, Tensor(a!) dev_weights, Tensor(b!) uvm_weights, Tensor lxu_cache_weights, "                   \
+    "Tensor weights_placements, Tensor weights_offsets, Tensor D_offsets, SymInt max_D, Tensor hash_size_cumsum, "     \
+    "int total_hash_size_bits, Tensor indices, Tensor offsets, int pooling_mode, Tensor lxu_cache_locations, "         \
+    "int unused_, int max_segment_length_per_warp, bool stochastic_rounding, int info_B_num_bits, "                    \
+    "int info_B_mask_int64, bool use_uniq_cache_locations, bool use_homogeneous_placements, "
+#define RECSDK_BWD_UNIQ                                                                                                \
+    "Tensor hash_indices = None, Tensor unique_ids = None, Tensor unique_offsets = None, Tensor unique_inverse = None, " \
+    "Tensor offset_per_key = None, "
+
+static void define_and_implement(torch::Library& m)
+{
+    m.def(kFwdSchema);
+    m.def("split_embedding_codegen_lookup_adagrad_function(" RECSDK_LOOKUP_HEAD RECSDK_MOM1 RECSDK_LOOKUP_UNIQ
+          "float eps = 0, float learning_rate = 0, " RECSDK_LOOKUP_VBE
+          "int iter=0, bool apply_global_weight_decay=False, float gwd_lower_bound=0) -> Tensor");
+    m.def("split_embedding_codegen_lookup_adam_function(" RECSDK_LOOKUP_HEAD RECSDK_MOM1 RECSDK_MOM2 RECSDK_LOOKUP_UNIQ
+          "float eps = 0, float learning_rate = 0, float beta1 = 0, float beta2 = 0, float weight_decay = 0, int iter = 0, "
+          RECSDK_LOOKUP_VBE "bool apply_global_weight_decay=False, float gwd_lower_bound=0) -> Tensor");
+    m.def("split_embedding_codegen_lookup_sgd_function(" RECSDK_LOOKUP_HEAD RECSDK_LOOKUP_UNIQ "float learning_rate = 0, "
+          RECSDK_LOOKUP_VBE "int iter=0, bool apply_global_weight_decay=False, float gwd_lower_bound=0) -> Tensor");
+    m.def("split_embedding_backward_codegen_adagrad_unweighted_exact_cuda(" RECSDK_BWD_HEAD RECSDK_MOM1 RECSDK_BWD_UNIQ
+          "float eps = 0, float learning_rate = 0) -> Tensor");
+    m.def("split_embedding_backward_codegen_adam_unweighted_exact_cuda(" RECSDK_BWD_HEAD RECSDK_MOM1 RECSDK_MOM2 RECSDK_BWD_UNIQ
+          "float eps = 0, float learning_rate = 0, float beta1 = 0, float beta2 = 0, int iter = 0) -> Tensor");
+    m.def("split_embedding_backward_codegen_sgd_unweighted_exact_cuda(" RECSDK_BWD_HEAD RECSDK_BWD_UNIQ
+          "float learning_rate = 0) -> Tensor");
+
+    const auto cuda = c10::DispatchKey::CUDA;
+    const auto autograd = c10::DispatchKey::Autograd;
+    m.impl("split_embedding_codegen_forward_unweighted_cuda", torch::dispatch(cuda, TORCH_FN(forward_unweighted_cuda)));
+    m.impl("split_embedding_backward_codegen_adagrad_unweighted_exact_cuda", torch::dispatch(cuda, TORCH_FN(backward_adagrad_cuda)));
+    m.impl("split_embedding_backward_codegen_adam_unweighted_exact_cuda", torch::dispatch(cuda, TORCH_FN(backward_adam_cuda)));
+    m.impl("split_embedding_backward_codegen_sgd_unweighted_exact_cuda", torch::dispatch(cuda, TORCH_FN(backward_sgd_cuda)));
+    m.impl("split_embedding_codegen_lookup_adagrad_function", torch::dispatch(autograd, TORCH_FN(lookup_adagrad_function)));
+    m.impl("split_embedding_codegen_lookup_adam_function", torch::dispatch(autograd, TORCH_FN(lookup_adam_function)));
+    m.impl("split_embedding_codegen_lookup_sgd_function", torch::dispatch(autograd, TORCH_FN(lookup_sgd_function)));
+}
+
+// ---------------------------------------------------------------------------- IdsMapper / bucketize
+static void raise_on_status(const Tensor& status, const char* where)
+{
+    const Tensor h = status.cpu();  // synchronises, like the reference's TORCH_CHECK inside its host loop
+    const int64_t* s = h.data_ptr<int64_t>();
+    if (s[0] == 0) return;
+    const int code = static_cast<int>(s[0]);
+    const int64_t d0 = s[1];
+    status.zero_();
+    if (code == RECSDK_ERR_NEGATIVE_KEY) TORCH_CHECK(false, where, ":  Invalid key value: ", d0);
+    if (code == RECSDK_ERR_TABLE_FULL)
+        TORCH_CHECK(false, where, ": Ids map reached maxIndex = ", d0, " please reallocate a larger buffer.");
+    TORCH_CHECK(false, where, ": ", recsdk_error_string(code));
+}
+
+class IdsMapper : public torch::CustomClassHolder {
+public:
+    IdsMapper(int64_t initMaxIndex, bool onlyDeviceMem) : initMaxIndex_(initMaxIndex)
+    {
+        TORCH_CHECK(initMaxIndex > 0, "initMaxIndex must be positive");
+        const auto dev = at::Device(at::kCUDA, at::cuda::current_device());
+        const auto i64 = at::TensorOptions().dtype(at::kLong).device(dev);
+        int64_t cap = 16;
+        while (cap < 2 * initMaxIndex + 1) cap <<= 1;
+        table_ = at::empty({cap * 2}, i64);
+        slot_key_ = at::empty({initMaxIndex}, i64);
+        mark_ = at::empty({initMaxIndex}, i64.dtype(at::kInt));
+        counters_ = at::zeros({4}, i64);
+        status_ = at::zeros({RECSDK_STATUS_WORDS}, i64);
+        m_ = recsdk_mapper_t{table_.data_ptr<int64_t>(), cap, slot_key_.data_ptr<int64_t>(), mark_.data_ptr<int32_t>(),
+                             counters_.data_ptr<int64_t>(), initMaxIndex, onlyDeviceMem ? 1 : 0};
+        check_rc(recsdk_mapper_init(&m_, cur_stream()), "IdsMapper");
+    }
+
+    std::tuple<Tensor, Tensor, Tensor> UniqueAndLookup(const Tensor& globalIds)
+    {
+        TORCH_CHECK(globalIds.is_cuda(), "globalIds must be on the GPU but on ", globalIds.device());
+        TORCH_CHECK(globalIds.scalar_type() == at::kLong,
+                    "globalIds must be int64_t tensor expected but got a tensor with dtype: ", globalIds.scalar_type());
+        const Tensor ids = globalIds.contiguous();
+        const int64_t n = ids.numel();
+        Tensor hi = at::empty_like(ids), uq = at::empty({std::max<int64_t>(n, 1)}, ids.options()),
+               inv = at::empty({std::max<int64_t>(n, 1)}, ids.options()), cnt = at::zeros({1}, ids.options());
+        Tensor ws = workspace(n);
+        check_rc(recsdk_mapper_ids2indices_unique(&m_, ids.data_ptr<int64_t>(), n, hi.data_ptr<int64_t>(),
+                                                  uq.data_ptr<int64_t>(), inv.data_ptr<int64_t>(), cnt.data_ptr<int64_t>(),
+                                                  status_.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), cur_stream()),
+                 "ids2indices_unique");
+        raise_on_status(status_, "ids2indices_unique");
+        const int64_t u = cnt.item<int64_t>();
+        return {hi, uq.narrow(0, 0, u), inv.narrow(0, 0, n)};
+    }
+
+    void UniqueAndLookupOut(const Tensor& globalIds, const Tensor& hashIndices, const Tensor& offset, const Tensor& unique,
+                            const Tensor& uniqueIds, const Tensor& uniqueInverse, const Tensor& uniqueOffset, int64_t tableId)
+    {
+        enqueue_out(globalIds, hashIndices, offset, unique, uniqueIds, uniqueInverse, uniqueOffset, tableId);
+        raise_on_status(status_, "ids2indices_unique_out");
+    }
+
+    static void ParallelUniqueHashOut(const c10::List<c10::intrusive_ptr<IdsMapper>>& mappers, const Tensor& globalIds,
+                                      const Tensor& hashIndices, const Tensor& offsets, const Tensor& unique,
+                                      const Tensor& uniqueIds, const Tensor& uniqueInverse, const Tensor& uniqueOffset)
+    {
+        for (size_t t = 0; t < mappers.size(); ++t) {
+            const c10::intrusive_ptr<IdsMapper> m = mappers.get(t);
+            m->enqueue_out(globalIds, hashIndices, offsets, unique, uniqueIds, uniqueInverse, uniqueOffset,
+                           static_cast<int64_t>(t));
+        }
+        for (size_t t = 0; t < mappers.size(); ++t) {
+            const c10::intrusive_ptr<IdsMapper> m = mappers.get(t);
+            raise_on_status(m->status_, "parallel_ids2indices_unique_out");
+        }
+    }
+
+    int64_t size() { return counters_.cpu().data_ptr<int64_t>()[0]; }
+
+private:
+    Tensor workspace(int64_t n)
+    {
+        const int64_t need = static_cast<int64_t>(recsdk_mapper_workspace_bytes(n));
+        if (!ws_.defined() || ws_.numel() < need) ws_ = at::empty({need}, table_.options().dtype(at::kByte));
+        return ws_;
+    }
+    void enqueue_out(const Tensor& globalIds, const Tensor& hashIndices, const Tensor& offset, const Tensor& unique,
+                     const Tensor& uniqueIds, const Tensor& uniqueInverse, const Tensor& uniqueOffset, int64_t tableId)
+    {
+        check_i64(globalIds, "globalIds");
+        check_i64(hashIndices, "hashIndices");
+        check_i64(unique, "unique");
+        check_i64(uniqueIds, "uniqueIds");
+        check_i64(uniqueInverse, "uniqueInverse");
+        check_i64(uniqueOffset, "uniqueOffset");
+        TORCH_CHECK(offset.numel() - 1 > tableId, "offset must be equal to table size + 1");
+        const Tensor off = offset.cpu();  // segment bounds are host scalars for the launch
+        const int64_t start = off.data_ptr<int64_t>()[tableId], end = off.data_ptr<int64_t>()[tableId + 1];
+        Tensor ws = workspace(end - start);
+        check_rc(recsdk_mapper_unique_out(&m_, globalIds.data_ptr<int64_t>(), hashIndices.data_ptr<int64_t>(), start,
+                                          end - start, unique.data_ptr<int64_t>(), uniqueIds.data_ptr<int64_t>(),
+                                          uniqueInverse.data_ptr<int64_t>(), uniqueOffset.data_ptr<int64_t>(), tableId,
+                                          status_.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), cur_stream()),
+                 "ids2indices_unique_out");
+    }
+
+    int64_t initMaxIndex_;
+    Tensor table_, slot_key_, mark_, counters_, status_, ws_;
+    recsdk_mapper_t m_;
+};
+
+// (new_lengths, new_indices, None, None, unbucketize_permute, None, ids_counts), bucketize.cpp:214-282
+std::tuple<Tensor, Tensor, std::optional<Tensor>, std::optional<Tensor>, std::optional<Tensor>, std::optional<Tensor>, Tensor>
+block_bucketize_sparse_features(const Tensor& lengths, const Tensor& indices, bool bucketize_pos, bool sequence,
+                                const Tensor& block_sizes, int64_t bucket_size, const std::optional<Tensor>& total_num_blocks,
+                                const std::optional<Tensor>& weights, const std::optional<Tensor>& batch_size_per_feature,
+                                int64_t max_B, const std::optional<std::vector<Tensor>>& block_bucketize_pos,
+                                bool return_bucket_mapping, bool keep_orig_idx, bool do_unique, bool return_count)
+{
+    TORCH_CHECK(lengths.defined() && lengths.numel() > 0, "Lengths tensor is an empty tensor");
+    TORCH_CHECK(indices.defined() && indices.numel() > 0, "Indices tensor is an empty tensor");
+    TORCH_CHECK(!weights.has_value(), "Weighted KJT is currently not supported");
+    TORCH_CHECK(!bucketize_pos, "Bucket position tracking is not implemented");
+    TORCH_CHECK(!return_bucket_mapping, "Bucket mapping return is not supported");
+    TORCH_CHECK(!batch_size_per_feature, "batchSize PerFeature return is not supported");
+    TORCH_CHECK(!block_bucketize_pos, "block BucketizePos return is not supported");
+    TORCH_CHECK(bucket_size > 0, "Bucket size must be greater than 0");
+    check_i64(lengths, "lengths");
+    check_i64(indices, "indices");
+    const c10::cuda::OptionalCUDAGuard guard(device_of(indices));
+    const int64_t n = indices.numel(), L = lengths.numel(), F = block_sizes.numel();
+    TORCH_CHECK(F > 0, "blockSizes must have at least one element");
+    const bool uniq = sequence && do_unique;
+    Tensor new_lengths = at::empty({L * bucket_size}, lengths.options());
+    Tensor new_indices = at::empty_like(indices), perm = at::empty_like(indices);
+    Tensor counts = (uniq && return_count) ? at::empty_like(indices) : at::empty({0}, indices.options());
+    Tensor num_out = at::zeros({1}, indices.options());
+    Tensor ws = at::empty({static_cast<int64_t>(recsdk_bucketize_workspace_bytes(n, L, bucket_size))},
+                          indices.options().dtype(at::kByte));
+    check_rc(recsdk_bucketize(lengths.data_ptr<int64_t>(), L, indices.data_ptr<int64_t>(), n, F, bucket_size, uniq ? 1 : 0,
+                              (uniq && return_count) ? 1 : 0, new_lengths.data_ptr<int64_t>(), new_indices.data_ptr<int64_t>(),
+                              perm.data_ptr<int64_t>(), counts.numel() ? counts.data_ptr<int64_t>() : nullptr,
+                              num_out.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), cur_stream()),
+             "block_bucketize_sparse_features");
+    if (uniq) {
+        const int64_t k = num_out.item<int64_t>();  // the reference resize_()s to the unique count
+        new_indices = new_indices.narrow(0, 0, k);
+        if (return_count) counts = counts.narrow(0, 0, k);
+    }
+    return {new_lengths, new_indices, std::nullopt, std::nullopt, perm, std::nullopt, counts};
+}
+
+}  // namespace recsdk_torch
+
+#ifndef RECSDK_NO_FBGEMM_NS
+TORCH_LIBRARY_FRAGMENT(fbgemm, m) { recsdk_torch::define_and_implement(m); }
+#endif
+
+TORCH_LIBRARY(recsdk, m)
+{
+    recsdk_torch::define_and_implement(m);
+    m.class_<recsdk_torch::IdsMapper>("IdsMapper")
+        .def(torch::init<int64_t, bool>())
+        .def("ids2indices_unique", &recsdk_torch::IdsMapper::UniqueAndLookup)
+        .def("ids2indices_unique_out", &recsdk_torch::IdsMapper::UniqueAndLookupOut)
+        .def("size", &recsdk_torch::IdsMapper::size)
+        .def_static("parallel_ids2indices_unique_out", &recsdk_torch::IdsMapper::ParallelUniqueHashOut);
+    m.def("block_bucketize_sparse_features", &recsdk_torch::block_bucketize_sparse_features);
+}

@@ -124,6 +124,7 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         seed: int = 0,
         reduce_chunk: int = 64,
         bounds_check: bool = False,
+        use_torch_ops: Optional[bool] = None,
         **_ignored,
     ) -> None:
         super().__init__()
@@ -168,6 +169,15 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         self.output_dtype = int(output_dtype)
         self.reduce_chunk = reduce_chunk
         self.bounds_check = bounds_check
+        # forward() goes through torch.ops.fbgemm.* (C++ registration) when that library is built; the
+        # registered ops use reduce_chunk 64 and no bounds checking, so other settings keep the Python Function
+        from . import torch_ops
+
+        if use_torch_ops is None:
+            use_torch_ops = torch_ops.available() and reduce_chunk == 64 and not bounds_check
+        if use_torch_ops:
+            torch_ops.load()
+        self.use_torch_ops = bool(use_torch_ops)
 
         total = table_wo[-1]
         self.weights_dev = nn.Parameter(torch.empty(total, dtype=torch.float32, device=dev), requires_grad=False)
@@ -240,8 +250,40 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         self.step += 1
         self.iter[0] += 1  # create_momentum(), batched_embedding_kernel.py:159-176
         iteration = int(self.iter.item())
+        if self.use_torch_ops:
+            return self._invoke_registered_op(indices, offsets, hash_indices, unique_indices, unique_offset,
+                                              unique_inverse, iteration)
         return _LookupFunction.apply(self.placeholder_autograd_tensor, self, indices, offsets, hash_indices,
                                      unique_indices, unique_offset, unique_inverse, iteration)
+
+    def _invoke_registered_op(self, indices, offsets, hash_indices, unique_indices, unique_offset, unique_inverse,
+                              iteration: int) -> Tensor:
+        """The call the reference's invokers make (hybrid_lookup_invoke/hybrid_lookup_{adagrad,adam,sgd}.py):
+        torch.ops.fbgemm.split_embedding_codegen_lookup_*_function with the same keyword names."""
+        a = self.optimizer_args
+        common = dict(
+            placeholder_autograd_tensor=self.placeholder_autograd_tensor, dev_weights=self.weights_dev.data,
+            uvm_weights=self.weights_uvm, lxu_cache_weights=self.lxu_cache_weights,
+            weights_placements=self.weights_placements, weights_offsets=self.weights_offsets,
+            D_offsets=self.D_offsets, total_D=self.total_D, max_D=self.max_D,
+            hash_size_cumsum=self.hash_size_cumsum, total_hash_size_bits=self.total_hash_size_bits,
+            indices=indices, offsets=offsets, hash_indices=hash_indices, unique_ids=unique_indices,
+            unique_offsets=unique_offset, unique_inverse=unique_inverse, pooling_mode=int(self.pooling_mode),
+            indice_weights=None, feature_requires_grad=None, lxu_cache_locations=self.lxu_cache_locations,
+            gradient_clipping=a.gradient_clipping, max_gradient=a.max_gradient,
+            stochastic_rounding=a.stochastic_rounding, learning_rate=a.learning_rate, iter=iteration,
+            output_dtype=self.output_dtype)
+        m1 = dict(momentum1_dev=self.momentum1_dev, momentum1_uvm=self.momentum1_uvm,
+                  momentum1_offsets=self.momentum1_offsets, momentum1_placements=self.momentum1_placements)
+        m2 = dict(momentum2_dev=self.momentum2_dev, momentum2_uvm=self.momentum2_uvm,
+                  momentum2_offsets=self.momentum2_offsets, momentum2_placements=self.momentum2_placements)
+        ns = torch.ops.fbgemm
+        if self.optimizer == EmbOptimType.EXACT_ADAGRAD:
+            return ns.split_embedding_codegen_lookup_adagrad_function(**common, **m1, eps=a.eps)
+        if self.optimizer == EmbOptimType.ADAM:
+            return ns.split_embedding_codegen_lookup_adam_function(**common, **m1, **m2, eps=a.eps, beta1=a.beta1,
+                                                                   beta2=a.beta2, weight_decay=a.weight_decay)
+        return ns.split_embedding_codegen_lookup_sgd_function(**common)
 
     # swap helpers (batched_embedding_kernel.py:297-345); rows move by bulk copies
     def _check_same_dim(self):

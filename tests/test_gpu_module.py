@@ -1,0 +1,166 @@
+"""The module mirror of HybridSplitTableBatchedEmbeddingBagsCodegen: registered torch ops (fbgemm:: schemas) vs the
+Python autograd Function vs the CPU oracle, swap helpers, and the recsdk:: IdsMapper torch class."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import port
+from tests.golden.driver import zipf_ids
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _module(opt, mode, use_torch_ops, specs, seed=3, **kw):
+    from recsdk_b200.tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
+
+    o = {1: EmbOptimType.EXACT_ADAGRAD, 2: EmbOptimType.ADAM, 3: EmbOptimType.EXACT_SGD}[opt]
+    return HybridSplitTableBatchedEmbeddingBagsCodegen(specs, optimizer=o, pooling_mode=PoolingMode(mode),
+                                                       learning_rate=0.05, eps=1e-8, beta1=0.9, beta2=0.999, device=DEV,
+                                                       weights_init=(-0.05, 0.05), seed=seed,
+                                                       initial_accumulator_value=0.1 if opt == 1 else 0.0,
+                                                       use_torch_ops=use_torch_ops, **kw)
+
+
+@pytest.mark.parametrize("opt", [1, 2, 3])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_registered_ops_match_python_function_and_oracle(opt, mode):
+    from recsdk_b200 import torch_ops
+
+    if not torch_ops.available():
+        pytest.skip("torch op library not built")
+    specs = [(300, 16), (500, 32), (200, 16)]
+    rng = np.random.default_rng(opt * 10 + mode)
+    B = 40
+    a = _module(opt, mode, True, specs)
+    b = _module(opt, mode, False, specs)
+    assert a.use_torch_ops and not b.use_torch_ops
+    assert torch.equal(a.weights_dev, b.weights_dev)
+    w = a.weights_dev.detach().cpu().numpy().copy()
+    m1 = np.full_like(w, 0.1 if opt == 1 else 0.0)
+    m2 = np.zeros_like(w)
+    T = len(specs)
+    wo, do, hs = (x.cpu().numpy() for x in (a.weights_offsets, a.D_offsets, a.hash_size_cumsum))
+    for step in range(3):
+        lens = rng.integers(0, 5, T * B)
+        offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        idx = np.concatenate([zipf_ids(rng, int(lens[t * B:(t + 1) * B].sum()), specs[t][0], 1.1) for t in range(T)])
+        ti, to = torch.as_tensor(idx, device=DEV), torch.as_tensor(offs, device=DEV)
+        oa, ob = a(ti, to), b(ti, to)
+        exp = port.tbe_forward(w, wo, do, idx, offs, T, B, a.total_D, a.max_D, mode)
+        np.testing.assert_array_equal(oa.detach().cpu().numpy(), exp)
+        assert torch.equal(oa, ob)
+        g = torch.as_tensor(rng.standard_normal(exp.shape).astype(np.float32), device=DEV)
+        oa.backward(g)
+        ob.backward(g)
+        port.tbe_backward(g.cpu().numpy(), w, m1, m2, wo, do, hs, idx, offs, T, B, a.total_D, a.max_D, mode, opt, 0.05,
+                          1e-8, 0.9, 0.999, step + 1, reduce_chunk=64)
+    for mod in (a, b):
+        np.testing.assert_array_equal(mod.weights_dev.detach().cpu().numpy(), w)
+        if opt != 3:
+            np.testing.assert_array_equal(mod.momentum1_dev.cpu().numpy(), m1)
+        if opt == 2:
+            np.testing.assert_array_equal(mod.momentum2_dev.cpu().numpy(), m2)
+    assert int(a.iter.item()) == 3
+
+
+def test_raw_registered_ops_and_errors():
+    from recsdk_b200 import torch_ops
+
+    if not torch_ops.available():
+        pytest.skip("torch op library not built")
+    torch_ops.load()
+    w = torch.arange(8, dtype=torch.float32, device=DEV)
+    e = torch.empty(0, device=DEV)
+    ei = torch.empty(0, dtype=torch.int64, device=DEV)
+    wo = torch.tensor([0], device=DEV)
+    do = torch.tensor([0, 2], dtype=torch.int32, device=DEV)
+    idx = torch.tensor([0, 1, 2, 3, 1], device=DEV)
+    offs = torch.tensor([0, 2, 4, 5], device=DEV)
+    pl = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for ns in (torch.ops.fbgemm, torch.ops.recsdk):
+        # the schema's `Tensor x = None` defaults cannot be omitted from Python: pass empty tensors, as the C++ callers do
+        out = ns.split_embedding_codegen_forward_unweighted_cuda(w, e, e, pl, wo, do, 2, 2, idx, offs, 0, e, e, 0, False, ei, ei)
+        np.testing.assert_array_equal(out.cpu().numpy(), [[2, 4], [10, 12], [2, 3]])
+    with pytest.raises(RuntimeError, match="incorrect for feature count"):
+        torch.ops.fbgemm.split_embedding_codegen_forward_unweighted_cuda(
+            w, e, e, torch.zeros(2, dtype=torch.int32, device=DEV), torch.tensor([0, 4], device=DEV),
+            torch.tensor([0, 2, 4], dtype=torch.int32, device=DEV), 4, 2, idx, offs, 0, e, e, 0, False, ei, ei)
+    # raw backward op (SGD, lr 1, grad 1): every touched row moves by its occurrence count
+    g = torch.ones(3, 2, device=DEV)
+    hs = torch.tensor([0, 4], device=DEV)
+    r = torch.ops.fbgemm.split_embedding_backward_codegen_sgd_unweighted_exact_cuda(
+        g, w, e, e, pl, wo, do, 2, hs, 3, idx, offs, 0, e, 32, 32, False, 0, 0, False, False, ei, ei, ei, ei, ei, 1.0)
+    np.testing.assert_array_equal(w.cpu().numpy().reshape(4, 2), [[-1, 0], [0, 1], [3, 4], [5, 6]])
+
+
+def test_swap_helpers():
+    m = _module(2, 0, False, [(1000, 32), (500, 32)])
+    rng = np.random.default_rng(0)
+    slots = torch.as_tensor(rng.permutation(1500)[:200].astype(np.int64), device=DEV)
+    rows = m.gather_embs(slots)
+    assert torch.equal(rows.view(-1, 32), m.weights_dev.view(-1, 32)[slots])
+    new = torch.randn(200, 32, device=DEV)
+    m.scatter_update_embs(slots, new)
+    assert torch.equal(m.weights_dev.view(-1, 32)[slots], new)
+    m.scatter_update_momentum(slots, [new, new * 2])
+    g1, g2 = m.gather_momentum(slots)
+    assert torch.equal(g1.view(-1, 32), new) and torch.equal(g2.view(-1, 32), new * 2)
+    mixed = _module(3, 0, False, [(10, 8), (10, 16)])
+    with pytest.raises(ValueError, match="Mixed dimensions"):
+        mixed.gather_embs(slots[:2])
+
+
+def test_ids_mapper_torch_class_matches_reference_golden(golden_dir):
+    from recsdk_b200 import torch_ops
+
+    if not torch_ops.available():
+        pytest.skip("torch op library not built")
+    torch_ops.load()
+    g = np.load(os.path.join(golden_dir, "ids_mapper.npz"))
+    T = 3
+    mappers = [torch.classes.recsdk.IdsMapper(4096, True) for _ in range(T)]
+    for s in range(3):
+        ids = torch.as_tensor(g[f"s{s}_ids"], device=DEV)
+        offset = torch.as_tensor(g[f"s{s}_offset"])
+        n = ids.numel()
+        hi, uq, uid, inv = (torch.full((max(n, 1),), -7, dtype=torch.int64, device=DEV) for _ in range(4))
+        uoff = torch.zeros(T + 1, dtype=torch.int64, device=DEV)
+        if s == 2:
+            torch.classes.recsdk.IdsMapper.parallel_ids2indices_unique_out(mappers, ids, hi, offset, uq, uid, inv, uoff)
+        else:
+            for t in range(T):
+                mappers[t].ids2indices_unique_out(ids, hi, offset, uq, uid, inv, uoff, t)
+        U = int(uoff[-1].item())
+        np.testing.assert_array_equal(uoff.cpu().numpy(), g[f"s{s}_unique_offset"])
+        np.testing.assert_array_equal(hi.cpu().numpy()[:n], g[f"s{s}_hash_indices"])
+        np.testing.assert_array_equal(uq.cpu().numpy()[:U], g[f"s{s}_unique"])
+        np.testing.assert_array_equal(uid.cpu().numpy()[:U], g[f"s{s}_unique_ids"])
+        np.testing.assert_array_equal(inv.cpu().numpy()[:n], g[f"s{s}_unique_inverse"])
+    m = torch.classes.recsdk.IdsMapper(100000, True)
+    for s in range(2):
+        hi, uq, inv = m.ids2indices_unique(torch.as_tensor(g[f"u{s}_ids"], device=DEV))
+        np.testing.assert_array_equal(hi.cpu().numpy(), g[f"u{s}_hash_indices"])
+        np.testing.assert_array_equal(uq.cpu().numpy(), g[f"u{s}_unique"])
+    with pytest.raises(RuntimeError, match="Invalid key value"):
+        torch.classes.recsdk.IdsMapper(8, True).ids2indices_unique(torch.tensor([3, -2], device=DEV))
+
+
+def test_bucketize_torch_op_matches_reference_golden(golden_dir):
+    from recsdk_b200 import torch_ops
+
+    if not torch_ops.available():
+        pytest.skip("torch op library not built")
+    torch_ops.load()
+    g = np.load(os.path.join(golden_dir, "bucketize.npz"))
+    for c in range(int(g["n_cases"][0])):
+        W, F, B, do_unique, ret_count = (int(x) for x in g[f"c{c}_meta"])
+        res = torch.ops.recsdk.block_bucketize_sparse_features(
+            torch.as_tensor(g[f"c{c}_lengths"], device=DEV), torch.as_tensor(g[f"c{c}_indices"], device=DEV), False, True,
+            torch.ones(F, dtype=torch.int64), W, None, None, None, 0, None, False, False, bool(do_unique), bool(ret_count))
+        np.testing.assert_array_equal(res[0].cpu().numpy(), g[f"c{c}_new_lengths"])
+        np.testing.assert_array_equal(res[1].cpu().numpy(), g[f"c{c}_new_indices"])
+        np.testing.assert_array_equal(res[4].cpu().numpy(), g[f"c{c}_unbucketize_permute"])
+        np.testing.assert_array_equal(res[6].cpu().numpy(), g[f"c{c}_ids_counts"])
