@@ -162,7 +162,8 @@ def run_ours(args):
 
         batches = [torch.stack([zipf_ids(gen, BATCH, r, ALPHA, dev) for r in rows_all]).view(N_TABLES, BATCH, 1)
                    for _ in range(n_batches)]
-        grad = torch.randn((BATCH, N_TABLES * DIM), generator=gen, device=dev, dtype=torch.float32)
+        # upstream gradient of this rank's samples, stored blocked by table owner (what the exchange sends)
+        grad = sh.blocked_gradient_buffer(BATCH, dev).normal_(generator=gen)
         owner_offsets = torch.arange(T * B + 1, dtype=torch.int64, device=dev)
 
     ev_pairs = []
@@ -179,8 +180,8 @@ def run_ours(args):
         idx, offs, g = owner_view(i)
         module.forward_into(idx, offs, out)
         if world > 1:
-            pooled = sh.exchange_outputs(out, BATCH)  # [BATCH, 26*DIM] on the sample owner (consumed by the dense part)
-            g = sh.exchange_gradients(grad)
+            pooled = sh.exchange_outputs(out, BATCH, assemble=False)  # per-owner [BATCH, D_owner] blocks on the sample owner
+            g = sh.exchange_gradients(grad, blocked=True)
             del pooled
         evs = None
         if timed:
@@ -251,8 +252,8 @@ def run_ours(args):
         else:
             idx, offs, _ = owner_view(i, ids_local=d_idx)
             o = module(idx, offs)
-            res = sh.exchange_outputs(o.detach(), BATCH)
-            o.backward(sh.exchange_gradients(grad))
+            res = sh.exchange_outputs(o.detach(), BATCH, assemble=False)[0]
+            o.backward(sh.exchange_gradients(grad, blocked=True))
         consumed[i % 2].record(main_stream)
         result_host.copy_(res.detach().reshape(-1)[:4096], non_blocking=True)
 

@@ -23,12 +23,17 @@ import torch.distributed as dist
 
 
 def greedy_table_placement(rows: Sequence[int], dims: Sequence[int], world: int) -> List[int]:
-    """Biggest table first onto the least loaded rank (bytes).  Deterministic on every rank."""
+    """Whole tables onto ranks.  Every table receives the same number of ids per step, so the lookup / update
+    work of a rank is proportional to its table COUNT while its memory is proportional to its table BYTES:
+    biggest table first onto the rank with the fewest tables so far, ties to the rank with the fewest bytes.
+    Counts differ by at most one and the big tables are spread out.  Deterministic on every rank."""
+    count = [0] * world
     load = [0] * world
     owner = [0] * len(rows)
     for t in sorted(range(len(rows)), key=lambda i: (-rows[i] * dims[i], i)):
-        r = min(range(world), key=lambda k: (load[k], k))
+        r = min(range(world), key=lambda k: (count[k], load[k], k))
         owner[t] = r
+        count[r] += 1
         load[r] += rows[t] * dims[t]
     return owner
 
@@ -68,9 +73,10 @@ class TableWiseSharding:
         return recv.view(W, Tl, B, L).permute(1, 0, 2, 3).reshape(Tl, W * B, L).contiguous()
 
     # ------------------------------------------------------------------ pooled outputs
-    def exchange_outputs(self, pooled: torch.Tensor, B_local: int) -> torch.Tensor:
+    def exchange_outputs(self, pooled: torch.Tensor, B_local: int, assemble: bool = True):
         """pooled [W*B_local, D_local] on the owner -> [B_local, sum_r D_r] on the sample owner
-        (columns ordered as `output_table_order`)."""
+        (columns ordered as `output_table_order`).  With assemble=False the result stays blocked by owner rank
+        (a list of [B_local, D_r] views of one receive buffer) and no second copy is made."""
         W = self.world
         Dl = self.dim_of_rank[self.rank]
         assert pooled.shape == (W * B_local, Dl)
@@ -82,19 +88,30 @@ class TableWiseSharding:
         for r in range(W):
             parts.append(recv[o:o + out_splits[r]].view(B_local, self.dim_of_rank[r]))
             o += out_splits[r]
+        if not assemble:
+            return parts
         return torch.cat(parts, dim=1) if W > 1 else parts[0]
 
     # ------------------------------------------------------------------ gradients
-    def exchange_gradients(self, grad: torch.Tensor) -> torch.Tensor:
-        """grad [B_local, sum_r D_r] (columns as `output_table_order`) -> [W*B_local, D_local] on the owner."""
+    def blocked_gradient_buffer(self, B_local: int, device, dtype=torch.float32) -> torch.Tensor:
+        """Flat buffer holding the upstream gradient blocked by owner rank: [B_local, D_0] | [B_local, D_1] | ..."""
+        return torch.empty(B_local * sum(self.dim_of_rank), dtype=dtype, device=device)
+
+    def exchange_gradients(self, grad: torch.Tensor, blocked: bool = False) -> torch.Tensor:
+        """grad [B_local, sum_r D_r] (columns as `output_table_order`) -> [W*B_local, D_local] on the owner.
+        blocked=True: `grad` is already the flat owner-blocked buffer (see blocked_gradient_buffer), sent as is."""
         W = self.world
-        B = grad.shape[0]
         Dl = self.dim_of_rank[self.rank]
-        cols, o = [], 0
-        for r in range(W):
-            cols.append(grad[:, o:o + self.dim_of_rank[r]].reshape(-1))
-            o += self.dim_of_rank[r]
-        send = torch.cat(cols) if W > 1 else cols[0]
+        if blocked:
+            B = grad.numel() // sum(self.dim_of_rank)
+            send = grad
+        else:
+            B = grad.shape[0]
+            cols, o = [], 0
+            for r in range(W):
+                cols.append(grad[:, o:o + self.dim_of_rank[r]].reshape(-1))
+                o += self.dim_of_rank[r]
+            send = torch.cat(cols) if W > 1 else cols[0]
         in_splits = [B * self.dim_of_rank[r] for r in range(W)]
         out_splits = [B * Dl] * W
         recv = torch.empty(W * B * Dl, dtype=grad.dtype, device=grad.device)
