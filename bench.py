@@ -160,11 +160,22 @@ def run_ours(args):
         # samples; ids travel to the table owners, pooled rows come back, gradients go out again
         from recsdk_b200.synthetic import zipf_ids
 
-        batches = [torch.stack([zipf_ids(gen, BATCH, r, ALPHA, dev) for r in rows_all]).view(N_TABLES, BATCH, 1)
-                   for _ in range(n_batches)]
-        # upstream gradient of this rank's samples, stored blocked by table owner (what the exchange sends)
-        grad = sh.blocked_gradient_buffer(BATCH, dev).normal_(generator=gen)
+        # the input pipeline lays the fields out grouped by table owner, so the ids are sent as they lie
+        batches = [torch.stack([zipf_ids(gen, BATCH, rows_all[t], ALPHA, dev) for t in sh.output_table_order])
+                   .view(N_TABLES, BATCH, 1) for _ in range(n_batches)]
         owner_offsets = torch.arange(T * B + 1, dtype=torch.int64, device=dev)
+        if args.exchange == "fused":
+            # pooled rows and gradients of this rank's samples live in peer-mapped buffers: the owners' forward
+            # kernels store into them and their backward kernels read from them over NVLink
+            from recsdk_b200.peer import FusedTableWiseExchange
+
+            del out
+            fx = FusedTableWiseExchange(sh, BATCH, dev)
+            fx.grads.local.normal_(generator=gen)
+            grad = None
+        else:
+            # upstream gradient of this rank's samples, stored blocked by table owner (what the exchange sends)
+            grad = sh.blocked_gradient_buffer(BATCH, dev).normal_(generator=gen)
 
     ev_pairs = []
 
@@ -173,23 +184,49 @@ def run_ours(args):
         if world == 1:
             idx, offs = batches[i % n_batches]
             return idx, offs, grad
-        ids = sh.exchange_ids(batches[i % n_batches] if ids_local is None else ids_local)
+        ids = sh.exchange_ids(batches[i % n_batches] if ids_local is None else ids_local, owner_ordered=True)
         return ids.view(-1), owner_offsets, None
 
-    def step_resident(i, timed=False):
-        idx, offs, g = owner_view(i)
-        module.forward_into(idx, offs, out)
-        if world > 1:
-            pooled = sh.exchange_outputs(out, BATCH, assemble=False)  # per-owner [BATCH, D_owner] blocks on the sample owner
-            g = sh.exchange_gradients(grad, blocked=True)
-            del pooled
+    fused = world > 1 and args.exchange == "fused"
+    phase_marks = []  # per timed step: events at the phase boundaries (this rank's stream)
+
+    def step_resident(i, timed=False, idx_offs=None):
+        marks = []
+
+        def mark():
+            if timed:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append(e)
+
+        mark()
+        idx, offs, g = owner_view(i) if idx_offs is None else (*idx_offs, grad)
+        mark()
         evs = None
         if timed:
             evs = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             for e in evs:
                 e.record()  # torch creates the CUDA event on first record; the library re-records it
             ev_pairs.append(evs)
+            phase_marks.append(marks)
+        if fused:
+            module.forward_into(idx, offs, out_shards=fx.out_shards)
+            mark()
+            fx.fence()  # every owner's stores have landed: fx.pooled.local is complete; the dense part runs here
+            fx.fence()  # ... and has written fx.grads.local on every rank
+            mark()
+            module.backward_from(None, idx, offs, update_events=evs, grad_shards=fx.grad_shards)
+            mark()
+            return
+        module.forward_into(idx, offs, out)
+        mark()
+        if world > 1:
+            pooled = sh.exchange_outputs(out, BATCH, assemble=False)  # per-owner [BATCH, D_owner] blocks on the sample owner
+            g = sh.exchange_gradients(grad, blocked=True)
+            del pooled
+        mark()
         module.backward_from(g, idx, offs, update_events=evs)
+        mark()
 
     def barrier():
         torch.cuda.synchronize()
@@ -212,6 +249,9 @@ def run_ours(args):
     barrier()
     ms_total = t0.elapsed_time(t1)
     upd_ms = [a.elapsed_time(b) for a, b in ev_pairs]
+    names = ("ids_exchange", "forward", "fences" if fused else "row_exchanges", "backward")
+    phases_ms = {n: sum(m[k].elapsed_time(m[k + 1]) for m in phase_marks) / len(phase_marks)
+                 for k, n in enumerate(names)}
     U, n_chunks, n_long = module.last_plan_counters()
 
     # ---- end to end through the module API with host index buffers.  The caller's pipeline double-buffers
@@ -249,6 +289,10 @@ def run_ours(args):
             o = module(d_idx, d_offs)  # autograd-tracked lookup; backward runs the fused optimizer
             o.backward(grad)
             res = o
+        elif fused:
+            idx, offs, _ = owner_view(i, ids_local=d_idx)
+            step_resident(i, idx_offs=(idx, offs))
+            res = fx.pooled.local
         else:
             idx, offs, _ = owner_view(i, ids_local=d_idx)
             o = module(idx, offs)
@@ -329,6 +373,9 @@ def run_ours(args):
                 "l2": "inputs larger than L2: 872 MB output + 872 MB gradient + 2.6 GB of touched rows per step; "
                       f"{n_batches} distinct batches rotate",
                 "reduce_chunk": 64,
+                "exchange": ("none (1 GPU)" if world == 1 else
+                             "ids: NCCL all-to-all; pooled rows and gradients: peer stores / loads inside the "
+                             "forward / backward kernels" if fused else "NCCL all-to-all x3"),
             },
             "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
             "step_hbm_frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
@@ -338,14 +385,18 @@ def run_ours(args):
             "e2e": {"value": ids_per_step / (e2e_ms_step * 1e-3), "unit": "ids/s", "ms_per_step": e2e_ms_step,
                     "h2d_bytes_per_step": int(h2d_bytes),
                     "d2h_bytes_per_step": int(result_host.numel() * 4)},
+            "phases_ms_rank0": phases_ms,
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample(budget_s=args.cpu_budget)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
+        if fused:
+            fx.close()
+            dist.barrier()
         dist.destroy_process_group()
 
 
@@ -436,16 +487,33 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": "ids/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "ids/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_FD = None
+
+
+def emit(line):
+    """The result goes to the process's ORIGINAL stdout as one line; everything else that the run prints
+    (library banners such as NCCL's version line included) was redirected to stderr in main()."""
+    data = (json.dumps(line) + "\n").encode()
+    os.write(_RESULT_FD if _RESULT_FD is not None else 1, data)
 
 
 def main():
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)  # native libraries write banners to fd 1; keep stdout to the single JSON line
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="N>1: pooled rows / gradients move inside the kernels over peer mappings (fused) or "
+                         "through NCCL all-to-alls (nccl, the reference's scheme)")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
     if args.impl == "reference":

@@ -58,6 +58,27 @@ RECSDK_API int recsdk_version(void);
 enum { RECSDK_POOL_SUM = 0, RECSDK_POOL_MEAN = 1, RECSDK_POOL_NONE = 2 };
 enum { RECSDK_OPT_ADAGRAD = 1, RECSDK_OPT_ADAM = 2, RECSDK_OPT_SGD = 3 };
 
+/* ---- sample-sharded [B,total_D] matrix (table-wise sharding on one box) -----
+ * With table-wise sharding (hybrid_torchrec/hybrid_torchrec/distributed/sharding/hybrid_tw_sharding.py:43-82)
+ * the table owner pools rows for the samples of EVERY rank and the reference then moves the pooled rows to
+ * the sample owners with an all-to-all (torchrec PooledEmbeddingsAllToAll), and the gradients back with a
+ * second one.  Here the forward kernel can store each pooled row straight into the sample owner's buffer
+ * and the backward kernels can read each gradient row straight from it, over NVLink peer mappings
+ * (recsdk_peer_*), so the exchange happens inside the kernels that produce / consume the data.
+ *
+ * num_shards == 0: off, the plain `out` / `grad_output` pointer is used.
+ * num_shards == W: sample g = s*shard_B + b (0 <= b < shard_B, B == W*shard_B) is row b of ptrs[s]; a row
+ * there is row_stride floats wide and feature t's columns start at col_offsets[t] (device array [T]).
+ * Pooled modes only. */
+#define RECSDK_MAX_SHARDS 16
+typedef struct {
+    int32_t num_shards;
+    int32_t row_stride;
+    int64_t shard_B;
+    const int32_t* col_offsets;
+    float* ptrs[RECSDK_MAX_SHARDS];
+} recsdk_sample_shards;
+
 /* =========================================================================
  * A6  pooled embedding gather (forward)
  * replaces aclnnSplitEmbeddingCodegenForwardUnweighted, called from
@@ -83,6 +104,7 @@ typedef struct {
     int32_t pooling_mode;
     int64_t weights_numel; /* >0: rows are bounds-checked against it, violations -> status, row read as 0 */
     int64_t* dev_status;   /* optional */
+    recsdk_sample_shards out_shards; /* optional (num_shards > 0): `out` is ignored */
 } recsdk_tbe_forward_args;
 RECSDK_API int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream);
 
@@ -174,6 +196,7 @@ typedef struct {
      * after the launch of the row-update kernel (the dominant kernel of the step); NULL = off */
     void* ev_update_start;
     void* ev_update_stop;
+    recsdk_sample_shards grad_shards; /* optional (num_shards > 0): `grad_output` is ignored; read only */
 } recsdk_tbe_backward_args;
 RECSDK_API size_t recsdk_tbe_backward_workspace_bytes(int64_t N, int32_t max_D);
 RECSDK_API int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stream);
@@ -349,6 +372,28 @@ RECSDK_API int recsdk_bucketize(const int64_t* lengths, int64_t lengths_size, co
                                 int64_t* new_lengths, int64_t* new_indices, int64_t* unbucketize_permute,
                                 int64_t* ids_counts, int64_t* num_out, void* workspace, size_t workspace_bytes,
                                 void* stream);
+
+/* =========================================================================
+ * Peer mappings for the sample-sharded buffers (one process per GPU on one box).
+ * Replaces the two pooled-embedding all-to-alls of the reference's table-wise path
+ * (torchrec PooledEmbeddingsAllToAll behind hybrid_torchrec/.../embeddingbag.py:550-593):
+ * every rank exports the buffer that holds ITS samples' pooled rows (and the one with
+ * their gradients), the other ranks map it and hand the mapped addresses to
+ * recsdk_tbe_forward / recsdk_tbe_backward in a recsdk_sample_shards.
+ *
+ * export: handle (64 bytes, cudaIpcMemHandle_t) of the cudaMalloc allocation that
+ *         contains dev_ptr, and the byte offset of dev_ptr inside it.  The memory must
+ *         come from cudaMalloc (torch's default caching allocator qualifies).
+ * import: maps a peer's allocation into this process (peer access enabled lazily by the
+ *         driver) and returns the address that corresponds to the exported pointer.
+ * release: unmaps; pass the pointer import returned and the same offset.
+ * These three calls are setup-time host calls (they synchronise); plain loads and stores
+ * are used on the mapped memory -- no multicast objects are created.
+ * ========================================================================= */
+#define RECSDK_PEER_HANDLE_BYTES 64
+RECSDK_API int recsdk_peer_export(const void* dev_ptr, unsigned char* handle_out, int64_t* offset_out);
+RECSDK_API int recsdk_peer_import(const unsigned char* handle, int64_t offset, void** dev_ptr_out);
+RECSDK_API int recsdk_peer_release(void* imported_ptr, int64_t offset);
 
 #ifdef __cplusplus
 }

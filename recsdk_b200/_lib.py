@@ -26,11 +26,22 @@ POOL_SUM, POOL_MEAN, POOL_NONE = 0, 1, 2
 OPT_ADAGRAD, OPT_ADAM, OPT_SGD = 1, 2, 3
 
 
+MAX_SHARDS = 16
+
+
+class SampleShards(C.Structure):
+    _fields_ = [
+        ("num_shards", C.c_int32), ("row_stride", C.c_int32), ("shard_B", C.c_int64), ("col_offsets", vp),
+        ("ptrs", vp * MAX_SHARDS),
+    ]
+
+
 class TbeForwardArgs(C.Structure):
     _fields_ = [
         ("dev_weights", vp), ("weights_offsets", vp), ("D_offsets", vp), ("indices", vp), ("offsets", vp),
         ("out", vp), ("T", C.c_int64), ("B", C.c_int64), ("N", C.c_int64), ("total_D", C.c_int32),
         ("max_D", C.c_int32), ("pooling_mode", C.c_int32), ("weights_numel", C.c_int64), ("dev_status", vp),
+        ("out_shards", SampleShards),
     ]
 
 
@@ -44,7 +55,7 @@ class TbeBackwardArgs(C.Structure):
         ("reduce_chunk", C.c_int32), ("learning_rate", C.c_float), ("eps", C.c_float), ("beta1", C.c_float),
         ("beta2", C.c_float), ("iter", C.c_int64), ("gradient_clipping", C.c_int32), ("max_gradient", C.c_float),
         ("weights_numel", C.c_int64), ("dev_status", vp), ("workspace", vp), ("workspace_bytes", C.c_size_t),
-        ("ev_update_start", vp), ("ev_update_stop", vp),
+        ("ev_update_start", vp), ("ev_update_stop", vp), ("grad_shards", SampleShards),
     ]
 
 
@@ -91,6 +102,9 @@ SIGNATURES = {
     "recsdk_sgd": (C.c_int, [vp, vp, C.c_int64, C.c_int32, vp, C.c_float, C.c_float, C.c_int32, vp, C.c_size_t,
                              vp]),
     "recsdk_restore": (C.c_int, [vp, vp, vp, vp, C.c_int64, C.c_int64, vp, vp]),
+    "recsdk_peer_export": (C.c_int, [vp, vp, C.POINTER(C.c_int64)]),
+    "recsdk_peer_import": (C.c_int, [vp, C.c_int64, C.POINTER(vp)]),
+    "recsdk_peer_release": (C.c_int, [vp, C.c_int64]),
     "recsdk_mapper_table_bytes": (C.c_size_t, [C.c_int64]),
     "recsdk_mapper_init": (C.c_int, [C.POINTER(MapperT), vp]),
     "recsdk_mapper_workspace_bytes": (C.c_size_t, [C.c_int64]),

@@ -101,3 +101,5 @@ if __name__ == "__main__":
         print(build_torch_ops(verbose=True))
         sys.exit(0)
     print(build(verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv))
+    if "--native-only" not in sys.argv and "--ptxas" not in sys.argv:
+        print(build_torch_ops(verbose="-v" in sys.argv))  # shares the header's structs: keep the two in step

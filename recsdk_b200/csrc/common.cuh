@@ -41,6 +41,17 @@ struct WorkspaceCarver {
     size_t used() const { return off; }
 };
 
+// Host-side validation of a sample-sharded matrix description for B samples.
+static inline bool sample_shards_valid(const recsdk_sample_shards& sh, int64_t B)
+{
+    if (sh.num_shards < 1 || sh.num_shards > RECSDK_MAX_SHARDS || sh.shard_B <= 0 || sh.row_stride <= 0 ||
+        sh.col_offsets == nullptr || static_cast<int64_t>(sh.num_shards) * sh.shard_B != B)
+        return false;
+    for (int s = 0; s < sh.num_shards; ++s)
+        if (sh.ptrs[s] == nullptr) return false;
+    return true;
+}
+
 // Grid for a grid-stride kernel over `work` items handled `per_block` at a time.
 static inline int grid_for(int64_t work, int64_t per_block, int max_blocks_per_sm = 16)
 {

@@ -58,6 +58,7 @@ struct BwdParams {
     const int2* __restrict__ chunk_desc;  // [chunks] {begin, end} sorted positions of each chunk
     float* __restrict__ partial;         // [chunks, max_D]
     const int64_t* __restrict__ counters;  // {U, total_chunks}
+    recsdk_sample_shards sh;  // num_shards > 0: gradient rows are read from the sample owners' buffers
 };
 
 // ---------------------------------------------------------------------------- 1. expand
@@ -158,7 +159,12 @@ __device__ __forceinline__ GradRow grad_row_of(const BwdParams& p, uint32_t v)
     } else {
         const uint32_t f = v >> p.bshift;
         const uint32_t b = v & ((1u << p.bshift) - 1u);
-        g.ptr = p.grad + static_cast<int64_t>(b) * p.total_D + p.dofs[f];
+        if (p.sh.num_shards == 0) {
+            g.ptr = p.grad + static_cast<int64_t>(b) * p.total_D + p.dofs[f];
+        } else {
+            const int64_t s = static_cast<int64_t>(b) / p.sh.shard_B;
+            g.ptr = p.sh.ptrs[s] + (static_cast<int64_t>(b) - s * p.sh.shard_B) * p.sh.row_stride + p.sh.col_offsets[f];
+        }
         if (p.mode == RECSDK_POOL_MEAN) {
             const int64_t bag = static_cast<int64_t>(f) * p.B + b;
             g.scale = __fdiv_rn(1.0f, static_cast<float>(p.offs[bag + 1] - p.offs[bag]));
@@ -223,6 +229,8 @@ __device__ __forceinline__ void run_geometry(const BwdParams& p, uint32_t v0, in
 
 __device__ __forceinline__ bool vec_ok_for(const BwdParams& p, int64_t wofs, int32_t D, int64_t f)
 {
+    if (p.sh.num_shards > 0)
+        return p.base_aligned && (((wofs | D | p.sh.col_offsets[f] | p.sh.row_stride | p.max_D) & 3) == 0);
     return p.base_aligned && (((wofs | D | p.dofs[f] | p.total_D | p.max_D) & 3) == 0);
 }
 
@@ -373,7 +381,7 @@ __device__ __forceinline__ void opt_update_vec(const BwdParams& p, float g, floa
 // a single 32-byte read instead of a chain of five dependent loads.
 struct __align__(16) RunMeta {
     int64_t row_off;     // element offset of the row in dev_weights; -1: out of range, skip
-    int64_t g0_off;      // element offset in grad_output of the run's first gradient row
+    int64_t g0_ptr;      // address of the run's first gradient row
     int32_t rs, len;     // sorted positions [rs, rs + len)
     int32_t D;           // row width in elements; kMetaVecBit set when the 128-bit path applies
     int32_t chunk_base;  // first slot of the run in the partial buffer (len > kChunk), else -1
@@ -406,7 +414,7 @@ __global__ void __launch_bounds__(256) run_meta_kernel(BwdParams p, const KeyT* 
             set_status(p.status, RECSDK_ERR_INDEX_RANGE, row, m.row_off);
             m.row_off = -1;
         }
-        m.g0_off = grad_row_of(p, v0).ptr - p.grad;
+        m.g0_ptr = reinterpret_cast<int64_t>(grad_row_of(p, v0).ptr);
         m.rs = rs;
         m.len = len;
         m.D = D | (vec_ok_for(p, wofs, D, f) ? kMetaVecBit : 0);
@@ -448,7 +456,7 @@ __device__ __forceinline__ void update_body(const BwdParams& p, const RunMeta& m
                 w[k] = V::ld(p.w + row_off + V::W * col);
                 if (OPT != RECSDK_OPT_SGD) m1[k] = V::ld(p.m1 + row_off + V::W * col);
                 if (OPT == RECSDK_OPT_ADAM) m2[k] = V::ld(p.m2 + row_off + V::W * col);
-                if (first_direct) g0[k] = V::ld_stream(p.grad + m.g0_off + V::W * col);
+                if (first_direct) g0[k] = V::ld_stream(reinterpret_cast<const float*>(m.g0_ptr) + V::W * col);
             }
         }
         if (chunked) {
@@ -510,7 +518,7 @@ __global__ void __launch_bounds__(256) update_kernel(BwdParams p, const RunMeta*
         const int4 hi = *(reinterpret_cast<const int4*>(meta + r) + 1);
         RunMeta m;
         m.row_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.y)) << 32) | static_cast<uint32_t>(lo.x);
-        m.g0_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
+        m.g0_ptr = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
         m.rs = hi.x;
         m.len = hi.y;
         m.D = hi.z;
@@ -680,8 +688,14 @@ extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stre
     if (a->optimizer < RECSDK_OPT_ADAGRAD || a->optimizer > RECSDK_OPT_SGD) return RECSDK_ERR_INVALID_ARG;
     if (a->reduce_chunk != 0 && a->reduce_chunk != kChunk) return RECSDK_ERR_INVALID_ARG;
     if (a->T == 0 || a->B == 0 || a->N == 0) return RECSDK_OK;
-    if (!a->grad_output || !a->dev_weights || !a->weights_offsets || !a->D_offsets || !a->indices || !a->offsets)
+    if (!a->dev_weights || !a->weights_offsets || !a->D_offsets || !a->indices || !a->offsets)
         return RECSDK_ERR_INVALID_ARG;
+    const recsdk_sample_shards& sh = a->grad_shards;
+    if (sh.num_shards == 0) {
+        if (!a->grad_output) return RECSDK_ERR_INVALID_ARG;
+    } else {
+        if (!sample_shards_valid(sh, a->B) || a->pooling_mode == RECSDK_POOL_NONE) return RECSDK_ERR_INVALID_ARG;
+    }
     if (a->optimizer != RECSDK_OPT_SGD && !a->momentum1) return RECSDK_ERR_INVALID_ARG;
     if (a->optimizer == RECSDK_OPT_ADAM && !a->momentum2) return RECSDK_ERR_INVALID_ARG;
     const bool have_unique = a->unique_ids != nullptr;
@@ -728,7 +742,14 @@ extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stre
     p.w_numel = a->weights_numel;
     p.grad_numel = a->pooling_mode == RECSDK_POOL_NONE ? a->N * a->max_D : a->B * static_cast<int64_t>(a->total_D);
     p.status = a->dev_status;
-    p.base_aligned = (aligned16(a->grad_output) && aligned16(a->dev_weights) && aligned16(a->momentum1) &&
+    bool grad_aligned = true;
+    if (sh.num_shards == 0) {
+        grad_aligned = aligned16(a->grad_output);
+    } else {
+        for (int s = 0; s < sh.num_shards; ++s) grad_aligned = grad_aligned && aligned16(sh.ptrs[s]);
+    }
+    p.sh = sh;
+    p.base_aligned = (grad_aligned && aligned16(a->dev_weights) && aligned16(a->momentum1) &&
                       aligned16(a->momentum2) && aligned16(ws.partial))
                          ? 1
                          : 0;

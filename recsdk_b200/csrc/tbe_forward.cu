@@ -30,8 +30,17 @@ struct FwdParams {
     int32_t total_D, max_D, mode;
     int64_t w_numel;
     int64_t* status;
-    int base_aligned;  // dev_weights and out are 16-byte aligned and total_D % 4 == 0
+    int base_aligned;  // dev_weights is 16-byte aligned
+    recsdk_sample_shards sh;  // num_shards > 0: pooled rows go to the sample owners' buffers
 };
+
+// Where the pooled row of bag (t, b) goes.
+__device__ __forceinline__ float* out_row_ptr(const FwdParams& p, int64_t t, int64_t b, int32_t d0)
+{
+    if (p.sh.num_shards == 0) return p.out + b * p.total_D + d0;
+    const int64_t s = b / p.sh.shard_B;
+    return p.sh.ptrs[s] + (b - s * p.sh.shard_B) * p.sh.row_stride + p.sh.col_offsets[t];
+}
 
 __device__ __forceinline__ bool row_ok(const FwdParams& p, int64_t idx, int64_t row_off, int32_t D)
 {
@@ -53,7 +62,7 @@ __device__ void forward_bag_scalar(const FwdParams& p, int lane, int64_t bag)
     const int32_t d0 = p.dofs[t];
     const int32_t D = p.dofs[t + 1] - d0;
     const int64_t wofs = p.wofs[t];
-    float* out_row = p.out + b * p.total_D + d0;
+    float* out_row = out_row_ptr(p, t, b, d0);
     const float mean = __fdiv_rn(1.0f, static_cast<float>(e - s));
     for (int c = lane; c < D; c += G) {
         float acc = 0.f;
@@ -98,8 +107,8 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
         const int32_t d0_l = p.dofs[t_l];
         const int32_t D_l = p.dofs[t_l + 1] - d0_l;
         const int64_t wofs_l = p.wofs[t_l];
-        const int64_t oofs_l = b_l * p.total_D + d0_l;
-        const bool ok_l = !valid || (((wofs_l | D_l | d0_l) & 3) == 0);
+        const int64_t optr_l = valid ? reinterpret_cast<int64_t>(out_row_ptr(p, t_l, b_l, d0_l)) : 0;
+        const bool ok_l = !valid || ((((wofs_l | D_l) & 3) == 0) && ((optr_l & 15) == 0));
         const bool all_ok = __all_sync(gmask, ok_l) != 0;  // executed by every lane of the group
         if (!(p.base_aligned && all_ok)) {
             for (int j = 0; j < nb; ++j) forward_bag_scalar<G>(p, gl, bag0 + j);
@@ -109,7 +118,7 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
 
         // flush bag j: write `acc` (scaled for MEAN) or zeros
         auto flush = [&](int j, const float4 (&acc)[K], bool has_rows, int cb) {
-            const int64_t oofs = __shfl_sync(gmask, oofs_l, j, G);
+            float* optr = reinterpret_cast<float*>(__shfl_sync(gmask, optr_l, j, G));
             const int nvec = __shfl_sync(gmask, D_l, j, G) >> 2;
             const int64_t sj = __shfl_sync(gmask, start_l, j, G);
             const int64_t nx = __shfl_sync(gmask, start_l, (j + 1) & (G - 1), G);
@@ -121,7 +130,7 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
                 if (c < nvec) {
                     float4 r = has_rows ? acc[k] : make_float4(0.f, 0.f, 0.f, 0.f);
                     if (has_rows && p.mode == RECSDK_POOL_MEAN) r = mul4s(r, mean);
-                    st_f4_stream(p.out + oofs + 4 * c, r);
+                    st_f4_stream(optr + 4 * c, r);
                 }
             }
         };
@@ -257,12 +266,18 @@ extern "C" int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream
     if (a->T < 0 || a->B < 0 || a->N < 0 || a->max_D <= 0 || a->total_D <= 0) return RECSDK_ERR_INVALID_ARG;
     if (a->pooling_mode < RECSDK_POOL_SUM || a->pooling_mode > RECSDK_POOL_NONE) return RECSDK_ERR_INVALID_ARG;
     if (a->T == 0 || a->B == 0) return RECSDK_OK;
-    if (!a->dev_weights || !a->weights_offsets || !a->D_offsets || !a->offsets || !a->out) return RECSDK_ERR_INVALID_ARG;
+    if (!a->dev_weights || !a->weights_offsets || !a->D_offsets || !a->offsets) return RECSDK_ERR_INVALID_ARG;
     if (a->N > 0 && !a->indices) return RECSDK_ERR_INVALID_ARG;
+    const recsdk_sample_shards& sh = a->out_shards;
+    if (sh.num_shards == 0) {
+        if (!a->out) return RECSDK_ERR_INVALID_ARG;
+    } else {
+        if (!sample_shards_valid(sh, a->B) || a->pooling_mode == RECSDK_POOL_NONE) return RECSDK_ERR_INVALID_ARG;
+    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     FwdParams p{a->dev_weights, a->weights_offsets, a->D_offsets, a->indices, a->offsets, a->out, a->T, a->B, a->N,
                 a->total_D, a->max_D, a->pooling_mode, a->weights_numel, a->dev_status,
-                (aligned16(a->dev_weights) && aligned16(a->out) && (a->total_D & 3) == 0) ? 1 : 0};
+                aligned16(a->dev_weights) ? 1 : 0, sh};
     const int vec_per_row = (a->max_D + 3) / 4;
     const int G = group_lanes_for(vec_per_row);
     if (a->pooling_mode == RECSDK_POOL_NONE) {

@@ -67,9 +67,31 @@ def _workspace(nbytes: int, device) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------- A6 forward
+class SampleShards:
+    """A [B, total_D] matrix stored split by sample over several buffers (one per GPU of the box): sample
+    s*shard_B + b is row b of buffer s, rows are ``row_stride`` floats wide and feature t's columns start at
+    ``col_offsets[t]`` (int32 device tensor).  ``ptrs`` are device addresses valid on THIS GPU (the local buffer's
+    data_ptr and peer mappings of the others, see recsdk_b200.peer)."""
+
+    def __init__(self, ptrs, shard_B: int, row_stride: int, col_offsets: torch.Tensor):
+        if not 1 <= len(ptrs) <= _lib.MAX_SHARDS:
+            raise RuntimeError(f"1..{_lib.MAX_SHARDS} shards supported, got {len(ptrs)}")
+        _chk(col_offsets, torch.int32, "col_offsets")
+        self.ptrs, self.shard_B, self.row_stride, self.col_offsets = list(ptrs), shard_B, row_stride, col_offsets
+
+    def fill(self, c_struct) -> None:
+        c_struct.num_shards = len(self.ptrs)
+        c_struct.row_stride = self.row_stride
+        c_struct.shard_B = self.shard_B
+        c_struct.col_offsets = _ptr(self.col_offsets)
+        for i, q in enumerate(self.ptrs):
+            c_struct.ptrs[i] = q
+
+
 def tbe_forward(dev_weights, weights_offsets, D_offsets, indices, offsets, total_D: int, max_D: int,
                 pooling_mode: int, status: Optional[torch.Tensor] = None, bounds_check: bool = True,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, out_shards: Optional[SampleShards] = None):
+    """With ``out_shards`` the pooled rows are stored into the sample owners' buffers and None is returned."""
     lib = _lib.load()
     _chk(dev_weights, torch.float32, "dev_weights")
     _chk(weights_offsets, torch.int64, "weights_offsets")
@@ -82,6 +104,13 @@ def tbe_forward(dev_weights, weights_offsets, D_offsets, indices, offsets, total
     B = (offsets.numel() - 1) // T
     N = indices.numel()
     shape = (N, max_D) if pooling_mode == POOL_NONE else (B, total_D)
+    if out_shards is not None:
+        a = _lib.TbeForwardArgs(_ptr(dev_weights), _ptr(weights_offsets), _ptr(D_offsets), _ptr(indices),
+                                _ptr(offsets), None, T, B, N, total_D, max_D, pooling_mode,
+                                dev_weights.numel() if bounds_check else 0, _ptr(status))
+        out_shards.fill(a.out_shards)
+        check(lib.recsdk_tbe_forward(C.byref(a), _stream()), "recsdk_tbe_forward")
+        return None
     if out is None:
         out = torch.empty(shape, dtype=torch.float32, device=dev_weights.device)
     else:
@@ -140,11 +169,14 @@ def tbe_backward(grad_output, dev_weights, momentum1, momentum2, weights_offsets
                  unique_ids=None, unique_offsets=None, unique_inverse=None, total_hash_size_bits: int = 0,
                  reduce_chunk: int = 64, gradient_clipping: bool = False, max_gradient: float = 0.0,
                  status: Optional[torch.Tensor] = None, bounds_check: bool = True,
-                 workspace: Optional[torch.Tensor] = None, update_events=None) -> None:
+                 workspace: Optional[torch.Tensor] = None, update_events=None,
+                 grad_shards: Optional[SampleShards] = None) -> None:
     """``update_events``: optional (start, stop) torch.cuda.Event pair (created with enable_timing=True and
-    recorded at least once before) that the library records around the row-update kernel."""
+    recorded at least once before) that the library records around the row-update kernel.
+    ``grad_shards``: read the gradient rows from the sample owners' buffers (``grad_output`` is then None)."""
     lib = _lib.load()
-    _chk(grad_output, torch.float32, "grad_output")
+    if grad_shards is None:
+        _chk(grad_output, torch.float32, "grad_output")
     _chk(dev_weights, torch.float32, "dev_weights")
     if momentum1 is not None:
         _chk(momentum1, torch.float32, "momentum1")
@@ -168,7 +200,9 @@ def tbe_backward(grad_output, dev_weights, momentum1, momentum2, weights_offsets
     if workspace is None or workspace.numel() < wsz:
         workspace = _workspace(wsz, dev_weights.device)
     a = _lib.TbeBackwardArgs()
-    a.grad_output = _ptr(grad_output)
+    a.grad_output = _ptr(grad_output) if grad_shards is None else None
+    if grad_shards is not None:
+        grad_shards.fill(a.grad_shards)
     a.dev_weights = _ptr(dev_weights)
     a.momentum1 = _ptr(momentum1)
     a.momentum2 = _ptr(momentum2)

@@ -59,12 +59,16 @@ class TableWiseSharding:
         dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
 
     # ------------------------------------------------------------------ ids
-    def exchange_ids(self, ids: torch.Tensor) -> torch.Tensor:
+    def exchange_ids(self, ids: torch.Tensor, owner_ordered: bool = False) -> torch.Tensor:
         """ids [T_total, B_local, L] (this rank's samples, every table) -> [T_local, W*B_local, L] on the owner,
-        sample s*B_local + b being sample b of rank s."""
+        sample s*B_local + b being sample b of rank s.  owner_ordered=True: the tables of `ids` are already in
+        `output_table_order` (grouped by owner), so the tensor is sent as it lies."""
         T, B, L = ids.shape
         W = self.world
-        send = torch.cat([ids[self.tables_of[r]].reshape(-1) for r in range(W)]) if W > 1 else ids.reshape(-1)
+        if owner_ordered or W == 1:
+            send = ids.reshape(-1)
+        else:
+            send = torch.cat([ids[self.tables_of[r]].reshape(-1) for r in range(W)])
         in_splits = [len(self.tables_of[r]) * B * L for r in range(W)]
         Tl = len(self.local_tables)
         out_splits = [Tl * B * L] * W

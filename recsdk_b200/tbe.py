@@ -213,14 +213,14 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         self._ws_counters: Optional[Tensor] = None
 
     # ------------------------------------------------------------------ kernels
-    def _forward_impl(self, indices: Tensor, offsets: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    def _forward_impl(self, indices: Tensor, offsets: Tensor, out: Optional[Tensor] = None, out_shards=None):
         return ops.tbe_forward(self.weights_dev.data, self.weights_offsets, self.D_offsets, indices, offsets,
                                self.total_D, self.max_D, int(self.pooling_mode),
                                status=self._status if self.bounds_check else None, bounds_check=self.bounds_check,
-                               out=out)
+                               out=out, out_shards=out_shards)
 
     def _backward_impl(self, grad_output, indices, offsets, unique_ids, unique_offsets, unique_inverse, iteration,
-                       update_events=None) -> None:
+                       update_events=None, grad_shards=None) -> None:
         a = self.optimizer_args
         need = ops.tbe_backward_workspace_bytes(indices.numel(), self.max_D)
         if self._ws is None or self._ws.numel() < need:
@@ -234,7 +234,7 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
                          total_hash_size_bits=self.total_hash_size_bits, reduce_chunk=self.reduce_chunk,
                          gradient_clipping=a.gradient_clipping, max_gradient=a.max_gradient,
                          status=self._status if self.bounds_check else None, bounds_check=self.bounds_check,
-                         workspace=self._ws, update_events=update_events)
+                         workspace=self._ws, update_events=update_events, grad_shards=grad_shards)
 
     # ------------------------------------------------------------------ reference interface
     def forward(self, indices: Tensor, offsets: Tensor, hash_indices: Optional[Tensor] = None,
@@ -334,16 +334,18 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         ops.raise_on_status(self._status, "HybridSplitTableBatchedEmbeddingBagsCodegen")
 
     # ------------------------------------------------------------------ allocation-free stepping (benchmarks, pipelines)
-    def forward_into(self, indices: Tensor, offsets: Tensor, out: Tensor) -> Tensor:
-        """Forward without autograd bookkeeping, writing into a caller-owned output."""
-        return self._forward_impl(indices, offsets, out=out)
+    def forward_into(self, indices: Tensor, offsets: Tensor, out: Optional[Tensor] = None, out_shards=None):
+        """Forward without autograd bookkeeping, writing into a caller-owned output, or (``out_shards``, an
+        ops.SampleShards) straight into the sample owners' peer-mapped buffers."""
+        return self._forward_impl(indices, offsets, out=out, out_shards=out_shards)
 
-    def backward_from(self, grad_output: Tensor, indices: Tensor, offsets: Tensor, unique_indices=None,
-                      unique_offset=None, unique_inverse=None, update_events=None) -> None:
-        """Fused backward + optimizer for the batch of the preceding forward_into."""
+    def backward_from(self, grad_output: Optional[Tensor], indices: Tensor, offsets: Tensor, unique_indices=None,
+                      unique_offset=None, unique_inverse=None, update_events=None, grad_shards=None) -> None:
+        """Fused backward + optimizer for the batch of the preceding forward_into.  With ``grad_shards`` the
+        gradient rows are read from the sample owners' peer-mapped buffers and ``grad_output`` is None."""
         self.iter[0] += 1
         self._backward_impl(grad_output, indices, offsets, unique_indices, unique_offset, unique_inverse,
-                            int(self.iter.item()), update_events=update_events)
+                            int(self.iter.item()), update_events=update_events, grad_shards=grad_shards)
 
     def last_plan_counters(self) -> Tuple[int, int, int]:
         """(unique rows, chunk sums, indices that live in chunked runs) of the most recent backward (synchronises)."""
