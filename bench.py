@@ -42,6 +42,7 @@ LR, BETA1, BETA2, EPS = 1e-3, 0.9, 0.999, 1e-8
 # Adam state is 3 x rows x 512 B.  The 26 seeded tables hold 144.9 M rows = 222 GB, more than one
 # GPU's HBM, so single-GPU runs cap every table at this many rows (Zipf ids are drawn over the capped vocab).
 ROW_CAP_1GPU = 16_000_000
+UPDATE_KERNEL_DRAM_BYTES = 879_443_968 + 429_988_096
 HBM_BUDGET_BYTES = 150e9
 
 
@@ -133,10 +134,17 @@ def run_ours(args):
     row_cap = None
     if world == 1:
         row_cap = ROW_CAP_1GPU
+        if args.profile_tables > 0:
+            # reduced case for profiler captures: the largest tables only, rows capped, so that a few GB are
+            # held on the device; the kernels and the batch per table are those of the full workload
+            rows_all = sorted(rows_all, reverse=True)[:args.profile_tables]
+            row_cap = args.profile_row_cap
         rows_all = [min(r, row_cap) for r in rows_all]
+    elif args.profile_tables > 0:
+        raise SystemExit("--profile-tables is a 1-GPU option")
     from recsdk_b200.sharding import TableWiseSharding
 
-    sh = TableWiseSharding(rows_all, [DIM] * N_TABLES, world, rank)
+    sh = TableWiseSharding(rows_all, [DIM] * len(rows_all), world, rank)
     my_tables = sh.local_tables
     rows = [rows_all[t] for t in my_tables]
     state_bytes = sum(rows) * DIM * 4 * 3
@@ -242,11 +250,13 @@ def run_ours(args):
         sampler.start()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.cudart().cudaProfilerStart()  # a profiler started with "--profile-from-start off" sees only the timed steps
     t0.record()
     for i in range(args.steps):
         step_resident(args.warmup + i, timed=True)
     t1.record()
     barrier()
+    torch.cuda.cudart().cudaProfilerStop()
     ms_total = t0.elapsed_time(t1)
     upd_ms = [a.elapsed_time(b) for a, b in ev_pairs]
     names = ("ids_exchange", "forward", "fences" if fused else "row_exchanges", "backward")
@@ -308,13 +318,17 @@ def run_ours(args):
         for i in range(n):
             step_e2e(i, i == n - 1)
 
-    run_e2e(max(args.warmup, 3))
-    barrier()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
-    e0.record()
-    run_e2e(args.steps)
-    e1.record()
+    if args.profile_tables > 0:  # profiler captures look at the resident loop only
+        e0.record()
+        e1.record()
+    else:
+        run_e2e(max(args.warmup, 3))
+        barrier()
+        e0.record()
+        run_e2e(args.steps)
+        e1.record()
     barrier()
     e2e_ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
@@ -364,8 +378,10 @@ def run_ours(args):
             "dtype": "f32",
             "data": "synthetic",
             "config": {
-                "workload": "configs[1]: 26 tables dim 128 fp32, batch 65536 per GPU one-hot Zipf(1.1), sparse Adam, "
-                            "table-wise sharding",
+                "workload": ("configs[1]: 26 tables dim 128 fp32, batch 65536 per GPU one-hot Zipf(1.1), sparse Adam, "
+                             "table-wise sharding") if args.profile_tables == 0 else
+                            (f"REDUCED profiling case, not the benchmark: the {T} largest tables of configs[1] with rows "
+                             f"capped at {row_cap}, batch 65536, sparse Adam"),
                 "tables_this_rank": T, "rows_this_rank": sum(rows), "row_cap": row_cap,
                 "table_state_gb_this_rank": round(state_bytes / 1e9, 1),
                 "ids_per_step": ids_per_step, "unique_rows_per_step_rank0": U,
@@ -381,8 +397,12 @@ def run_ours(args):
             "step_hbm_frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
             "roofline": {"kernel": "update_kernel<Adam>", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "bytes_per_launch": upd_bytes, "ms_per_launch": upd_ms_avg, "traffic": None},
-            "e2e": {"value": ids_per_step / (e2e_ms_step * 1e-3), "unit": "ids/s", "ms_per_step": e2e_ms_step,
+                         "bytes_per_launch": upd_bytes, "ms_per_launch": upd_ms_avg,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one update_kernel launch of THIS workload
+                         # (full size, 1 GPU), from the ncu capture summarised in profiles/dram_traffic_configs1_1gpu.md
+                         "traffic": UPDATE_KERNEL_DRAM_BYTES if (world == 1 and args.profile_tables == 0) else None},
+            "e2e": None if args.profile_tables > 0 else
+                   {"value": ids_per_step / (e2e_ms_step * 1e-3), "unit": "ids/s", "ms_per_step": e2e_ms_step,
                     "h2d_bytes_per_step": int(h2d_bytes),
                     "d2h_bytes_per_step": int(result_host.numel() * 4)},
             "phases_ms_rank0": phases_ms,
@@ -511,6 +531,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-tables", type=int, default=0,
+                    help="reduced case for profiler captures: keep only the K largest tables (1 GPU, no e2e loop)")
+    ap.add_argument("--profile-row-cap", type=int, default=524288, help="row cap of the reduced case")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N>1: pooled rows / gradients move inside the kernels over peer mappings (fused) or "
                          "through NCCL all-to-alls (nccl, the reference's scheme)")
