@@ -52,6 +52,17 @@ static inline bool sample_shards_valid(const recsdk_sample_shards& sh, int64_t B
     return true;
 }
 
+// Base address of shard s.  The table sits in the kernel's parameter space; a chain of selects over constant
+// indices keeps it there (indexing it with a run-time value would make every thread copy it to local memory).
+__device__ __forceinline__ float* shard_base(const recsdk_sample_shards& sh, int64_t s)
+{
+    float* q = sh.ptrs[0];
+#pragma unroll
+    for (int i = 1; i < RECSDK_MAX_SHARDS; ++i)
+        if (s == i) q = sh.ptrs[i];
+    return q;
+}
+
 // Grid for a grid-stride kernel over `work` items handled `per_block` at a time.
 static inline int grid_for(int64_t work, int64_t per_block, int max_blocks_per_sm = 16)
 {

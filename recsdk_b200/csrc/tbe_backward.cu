@@ -163,7 +163,7 @@ __device__ __forceinline__ GradRow grad_row_of(const BwdParams& p, uint32_t v)
             g.ptr = p.grad + static_cast<int64_t>(b) * p.total_D + p.dofs[f];
         } else {
             const int64_t s = static_cast<int64_t>(b) / p.sh.shard_B;
-            g.ptr = p.sh.ptrs[s] + (static_cast<int64_t>(b) - s * p.sh.shard_B) * p.sh.row_stride + p.sh.col_offsets[f];
+            g.ptr = shard_base(p.sh, s) + (static_cast<int64_t>(b) - s * p.sh.shard_B) * p.sh.row_stride + p.sh.col_offsets[f];
         }
         if (p.mode == RECSDK_POOL_MEAN) {
             const int64_t bag = static_cast<int64_t>(f) * p.B + b;
@@ -505,17 +505,29 @@ __device__ __forceinline__ void update_body(const BwdParams& p, const RunMeta& m
     }
 }
 
-// G lanes per unique row; the row's record tells where everything is.
+// G lanes per unique row; the row's record tells where everything is.  The record of the group's NEXT row is
+// fetched before the current row is processed, so the record load is off the critical path of every row but
+// the first.
 template <int G, int K, int OPT>
 __global__ void __launch_bounds__(256) update_kernel(BwdParams p, const RunMeta* __restrict__ meta)
 {
     const int groups_per_block = blockDim.x / G;
     const int lane = threadIdx.x % G;
     const int64_t U = p.counters[0];
-    for (int64_t r = static_cast<int64_t>(blockIdx.x) * groups_per_block + threadIdx.x / G; r < U;
-         r += static_cast<int64_t>(gridDim.x) * groups_per_block) {
-        const int4 lo = *reinterpret_cast<const int4*>(meta + r);
-        const int4 hi = *(reinterpret_cast<const int4*>(meta + r) + 1);
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * groups_per_block;
+    int64_t r = static_cast<int64_t>(blockIdx.x) * groups_per_block + threadIdx.x / G;
+    int4 lo = make_int4(0, 0, 0, 0), hi = lo;
+    if (r < U) {
+        lo = __ldg(reinterpret_cast<const int4*>(meta + r));
+        hi = __ldg(reinterpret_cast<const int4*>(meta + r) + 1);
+    }
+    while (r < U) {
+        const int64_t rn = r + stride;
+        int4 nlo = make_int4(0, 0, 0, 0), nhi = nlo;
+        if (rn < U) {
+            nlo = __ldg(reinterpret_cast<const int4*>(meta + rn));
+            nhi = __ldg(reinterpret_cast<const int4*>(meta + rn) + 1);
+        }
         RunMeta m;
         m.row_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.y)) << 32) | static_cast<uint32_t>(lo.x);
         m.g0_ptr = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
@@ -523,12 +535,16 @@ __global__ void __launch_bounds__(256) update_kernel(BwdParams p, const RunMeta*
         m.len = hi.y;
         m.D = hi.z;
         m.chunk_base = hi.w;
-        if (m.row_off < 0) continue;
-        const int32_t D = m.D & (kMetaVecBit - 1);
-        if (m.D & kMetaVecBit)
-            update_body<V4, G, K, OPT>(p, m, lane, D);
-        else
-            update_body<V1, G, K, OPT>(p, m, lane, D);
+        if (m.row_off >= 0) {
+            const int32_t D = m.D & (kMetaVecBit - 1);
+            if (m.D & kMetaVecBit)
+                update_body<V4, G, K, OPT>(p, m, lane, D);
+            else
+                update_body<V1, G, K, OPT>(p, m, lane, D);
+        }
+        lo = nlo;
+        hi = nhi;
+        r = rn;
     }
 }
 
