@@ -390,9 +390,11 @@ static void raise_on_status(const Tensor& status, const char* where)
     TORCH_CHECK(false, where, ": ", recsdk_error_string(code));
 }
 
-class IdsMapper : public torch::CustomClassHolder {
+// NS tags the registration namespace (a C++ type can back only one registered class): 0 = recsdk::, 1 = hybrid::
+template <int NS>
+class IdsMapperT : public torch::CustomClassHolder {
 public:
-    IdsMapper(int64_t initMaxIndex, bool onlyDeviceMem) : initMaxIndex_(initMaxIndex)
+    IdsMapperT(int64_t initMaxIndex, bool onlyDeviceMem) : initMaxIndex_(initMaxIndex)
     {
         TORCH_CHECK(initMaxIndex > 0, "initMaxIndex must be positive");
         const auto dev = at::Device(at::kCUDA, at::cuda::current_device());
@@ -435,17 +437,17 @@ public:
         raise_on_status(status_, "ids2indices_unique_out");
     }
 
-    static void ParallelUniqueHashOut(const c10::List<c10::intrusive_ptr<IdsMapper>>& mappers, const Tensor& globalIds,
+    static void ParallelUniqueHashOut(const c10::List<c10::intrusive_ptr<IdsMapperT>>& mappers, const Tensor& globalIds,
                                       const Tensor& hashIndices, const Tensor& offsets, const Tensor& unique,
                                       const Tensor& uniqueIds, const Tensor& uniqueInverse, const Tensor& uniqueOffset)
     {
         for (size_t t = 0; t < mappers.size(); ++t) {
-            const c10::intrusive_ptr<IdsMapper> m = mappers.get(t);
+            const c10::intrusive_ptr<IdsMapperT> m = mappers.get(t);
             m->enqueue_out(globalIds, hashIndices, offsets, unique, uniqueIds, uniqueInverse, uniqueOffset,
                            static_cast<int64_t>(t));
         }
         for (size_t t = 0; t < mappers.size(); ++t) {
-            const c10::intrusive_ptr<IdsMapper> m = mappers.get(t);
+            const c10::intrusive_ptr<IdsMapperT> m = mappers.get(t);
             raise_on_status(m->status_, "parallel_ids2indices_unique_out");
         }
     }
@@ -483,6 +485,8 @@ private:
     Tensor table_, slot_key_, mark_, counters_, status_, ws_;
     recsdk_mapper_t m_;
 };
+using IdsMapper = IdsMapperT<0>;
+using HybridIdsMapper = IdsMapperT<1>;
 
 // (new_lengths, new_indices, None, None, unbucketize_permute, None, ids_counts), bucketize.cpp:214-282
 std::tuple<Tensor, Tensor, std::optional<Tensor>, std::optional<Tensor>, std::optional<Tensor>, std::optional<Tensor>, Tensor>
@@ -542,3 +546,19 @@ TORCH_LIBRARY(recsdk, m)
         .def_static("parallel_ids2indices_unique_out", &recsdk_torch::IdsMapper::ParallelUniqueHashOut);
     m.def("block_bucketize_sparse_features", &recsdk_torch::block_bucketize_sparse_features);
 }
+
+// The reference's own registration names (hybrid_torchrec/src/bind_torch_lib.cpp:9-19): callers that say
+// torch.classes.hybrid.IdsMapper / torch.ops.hybrid.block_bucketize_sparse_features_cpu keep working, with CUDA
+// tensors.  Compile with -DRECSDK_NO_HYBRID_NS when the reference's libhybrid_cpp.so is loaded in the same process.
+#ifndef RECSDK_NO_HYBRID_NS
+TORCH_LIBRARY(hybrid, m)
+{
+    m.class_<recsdk_torch::HybridIdsMapper>("IdsMapper")
+        .def(torch::init<int64_t, bool>())
+        .def("ids2indices_unique", &recsdk_torch::HybridIdsMapper::UniqueAndLookup)
+        .def("ids2indices_unique_out", &recsdk_torch::HybridIdsMapper::UniqueAndLookupOut)
+        .def("size", &recsdk_torch::HybridIdsMapper::size)
+        .def_static("parallel_ids2indices_unique_out", &recsdk_torch::HybridIdsMapper::ParallelUniqueHashOut);
+    m.def("block_bucketize_sparse_features_cpu", &recsdk_torch::block_bucketize_sparse_features);
+}
+#endif

@@ -113,15 +113,18 @@ def test_swap_helpers():
         mixed.gather_embs(slots[:2])
 
 
-def test_ids_mapper_torch_class_matches_reference_golden(golden_dir):
+@pytest.mark.parametrize("ns", ["recsdk", "hybrid"])
+def test_ids_mapper_torch_class_matches_reference_golden(golden_dir, ns):
+    """`hybrid` is the reference's own registration name (hybrid_torchrec/src/bind_torch_lib.cpp:9-19)."""
     from recsdk_b200 import torch_ops
 
     if not torch_ops.available():
         pytest.skip("torch op library not built")
     torch_ops.load()
+    IdsMapper = getattr(torch.classes, ns).IdsMapper
     g = np.load(os.path.join(golden_dir, "ids_mapper.npz"))
     T = 3
-    mappers = [torch.classes.recsdk.IdsMapper(4096, True) for _ in range(T)]
+    mappers = [IdsMapper(4096, True) for _ in range(T)]
     for s in range(3):
         ids = torch.as_tensor(g[f"s{s}_ids"], device=DEV)
         offset = torch.as_tensor(g[f"s{s}_offset"])
@@ -129,7 +132,7 @@ def test_ids_mapper_torch_class_matches_reference_golden(golden_dir):
         hi, uq, uid, inv = (torch.full((max(n, 1),), -7, dtype=torch.int64, device=DEV) for _ in range(4))
         uoff = torch.zeros(T + 1, dtype=torch.int64, device=DEV)
         if s == 2:
-            torch.classes.recsdk.IdsMapper.parallel_ids2indices_unique_out(mappers, ids, hi, offset, uq, uid, inv, uoff)
+            IdsMapper.parallel_ids2indices_unique_out(mappers, ids, hi, offset, uq, uid, inv, uoff)
         else:
             for t in range(T):
                 mappers[t].ids2indices_unique_out(ids, hi, offset, uq, uid, inv, uoff, t)
@@ -139,16 +142,17 @@ def test_ids_mapper_torch_class_matches_reference_golden(golden_dir):
         np.testing.assert_array_equal(uq.cpu().numpy()[:U], g[f"s{s}_unique"])
         np.testing.assert_array_equal(uid.cpu().numpy()[:U], g[f"s{s}_unique_ids"])
         np.testing.assert_array_equal(inv.cpu().numpy()[:n], g[f"s{s}_unique_inverse"])
-    m = torch.classes.recsdk.IdsMapper(100000, True)
+    m = IdsMapper(100000, True)
     for s in range(2):
         hi, uq, inv = m.ids2indices_unique(torch.as_tensor(g[f"u{s}_ids"], device=DEV))
         np.testing.assert_array_equal(hi.cpu().numpy(), g[f"u{s}_hash_indices"])
         np.testing.assert_array_equal(uq.cpu().numpy(), g[f"u{s}_unique"])
     with pytest.raises(RuntimeError, match="Invalid key value"):
-        torch.classes.recsdk.IdsMapper(8, True).ids2indices_unique(torch.tensor([3, -2], device=DEV))
+        IdsMapper(8, True).ids2indices_unique(torch.tensor([3, -2], device=DEV))
 
 
-def test_bucketize_torch_op_matches_reference_golden(golden_dir):
+@pytest.mark.parametrize("op", ["recsdk.block_bucketize_sparse_features", "hybrid.block_bucketize_sparse_features_cpu"])
+def test_bucketize_torch_op_matches_reference_golden(golden_dir, op):
     from recsdk_b200 import torch_ops
 
     if not torch_ops.available():
@@ -157,7 +161,8 @@ def test_bucketize_torch_op_matches_reference_golden(golden_dir):
     g = np.load(os.path.join(golden_dir, "bucketize.npz"))
     for c in range(int(g["n_cases"][0])):
         W, F, B, do_unique, ret_count = (int(x) for x in g[f"c{c}_meta"])
-        res = torch.ops.recsdk.block_bucketize_sparse_features(
+        ns, name = op.split(".")
+        res = getattr(getattr(torch.ops, ns), name)(
             torch.as_tensor(g[f"c{c}_lengths"], device=DEV), torch.as_tensor(g[f"c{c}_indices"], device=DEV), False, True,
             torch.ones(F, dtype=torch.int64), W, None, None, None, 0, None, False, False, bool(do_unique), bool(ret_count))
         np.testing.assert_array_equal(res[0].cpu().numpy(), g[f"c{c}_new_lengths"])

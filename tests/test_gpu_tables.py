@@ -169,6 +169,31 @@ def test_cache_policy_small_capacity_vs_oracle():
     assert any(r["swapout_keys"].size for r in ro)
 
 
+def test_cache_policy_full_size_dynamic_table_config():
+    """The dynamic-table config at its full size: 64 Mi cache slots, 200 steps x 131072 keys (30 % fresh keys per
+    step), admit threshold 2, evict after 50 idle steps checked every 10 steps.  Every per-step output (admitted
+    keys, evicted set, swap-in / swap-out lists, batch offsets) must equal the compiled reference classes'
+    (SwapManager + FeatureFilter) when they are available, else the C restatement's."""
+    from oracle import ref
+
+    steps, n = 200, 131072
+    keys = cache_driver_steps(99, steps, n, 0.3, key_bits=63)
+    cache = 64 << 20
+    try:
+        if not ref.available():
+            raise OSError("compiled reference classes not present")
+        os_, of = ref.SwapManager(cache, 1), ref.FeatureFilter(2, 50, 10)
+    except OSError:
+        os_, of = port.SwapManager(cache, 1), port.FeatureFilter(2, 50, 10)
+    gs, gf = _GpuSwap(cache, 1), _GpuFilter(2, 50, 10, capacity=1 << 25)
+    ro = run_cache_driver(os_, of, keys, 10)
+    rg = run_cache_driver(gs, gf, keys, 10)
+    for s, (a, b) in enumerate(zip(rg, ro)):
+        for k in b:
+            np.testing.assert_array_equal(a[k], b[k], err_msg=f"step {s} {k}")
+    assert sum(r["evicted"].size for r in ro) > 0 and sum(r["swapin_keys"].size for r in ro) > n
+
+
 def test_cache_too_small_raises():
     from recsdk_b200 import SwapManager
 

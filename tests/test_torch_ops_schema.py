@@ -31,3 +31,6 @@ def test_ids_mapper_class_and_bucketize_are_registered():
     assert torch.classes.recsdk.IdsMapper is not None
     s = str(torch.ops.recsdk.block_bucketize_sparse_features.default._schema)
     assert s.count("Tensor") >= 10 and "bool" in s
+    # the reference's own names (hybrid_torchrec/src/bind_torch_lib.cpp:9-19)
+    assert torch.classes.hybrid.IdsMapper is not None
+    assert str(torch.ops.hybrid.block_bucketize_sparse_features_cpu.default._schema).count("Tensor") >= 10
