@@ -20,6 +20,9 @@
  * the reference's vector instructions Mul/Muls/Add/Div/Sqrt are.)
  */
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -724,7 +727,10 @@ int orc_tbe_backward(const float* grad_output, float* weights, float* momentum1,
     } else {
         U = unique_offsets[T];
     }
-    G = (float*)calloc((size_t)(U > 0 ? U : 1) * (size_t)max_D, sizeof(float));
+    /* malloc + memset, not calloc: the pages are touched here, by one thread, instead of faulting in from all
+     * threads at once inside the parallel walk below */
+    G = (float*)malloc((size_t)(U > 0 ? U : 1) * (size_t)max_D * sizeof(float));
+    memset(G, 0, (size_t)(U > 0 ? U : 1) * (size_t)max_D * sizeof(float));
     /* (1) segment-sum in ascending index position.  reduce_chunk == 0: one
      * sequential sum.  reduce_chunk == C: a row with more than C contributions
      * sums consecutive chunks of C contributions (each from 0.0f) and then the
@@ -733,44 +739,74 @@ int orc_tbe_backward(const float* grad_output, float* weights, float* momentum1,
         const int64_t* inv = unique_ids ? unique_inverse : own_inv;
         int64_t* cnt = (int64_t*)calloc((size_t)(U > 0 ? U : 1), sizeof(int64_t));
         int64_t* seen = (int64_t*)calloc((size_t)(U > 0 ? U : 1), sizeof(int64_t));
-        float* P = (float*)calloc((size_t)(U > 0 ? U : 1) * (size_t)max_D, sizeof(float)); /* open chunk */
+        float* P = (float*)malloc((size_t)(U > 0 ? U : 1) * (size_t)max_D * sizeof(float)); /* open chunk */
+        memset(P, 0, (size_t)(U > 0 ? U : 1) * (size_t)max_D * sizeof(float));
         if (reduce_chunk > 0)
             for (t = 0; t < T; t++) {
                 int64_t uoff = unique_ids ? unique_offsets[t] : 0;
                 for (i = offsets[t * B]; i < offsets[(t + 1) * B]; i++) cnt[inv[i] + uoff]++;
             }
-        for (t = 0; t < T; t++) {
-            int32_t D = D_offsets[t + 1] - D_offsets[t], d;
-            int64_t b;
-            int64_t uoff = unique_ids ? unique_offsets[t] : 0;
-            for (b = 0; b < B; b++) {
-                int64_t s = offsets[t * B + b], e = offsets[t * B + b + 1];
-                float mean = 1.0f / (float)(e - s);
-                for (i = s; i < e; i++) {
-                    const float* g =
-                        pooling_mode == 2 ? grad_output + i * max_D : grad_output + b * total_D + D_offsets[t];
-                    int64_t u2 = inv[i] + uoff;
-                    int chunked = reduce_chunk > 0 && cnt[u2] > reduce_chunk;
-                    float* acc = chunked ? P + u2 * max_D : G + u2 * max_D;
-                    for (d = 0; d < D; d++) {
-                        float v = g[d];
-                        if (gradient_clipping)
-                            v = v < -max_gradient ? -max_gradient : (v > max_gradient ? max_gradient : v);
-                        if (pooling_mode == 1) v = v * mean;
-                        acc[d] = acc[d] + v;
+        /* The order of additions is what fixes the result, and it is per unique row: the contributions of a
+         * row are taken in ascending index position.  Threads therefore own disjoint sets of unique rows
+         * (row u belongs to thread u mod nth); every thread walks all indices in the serial order and performs
+         * the additions of its own rows only, so each row sees exactly the serial sequence of additions.
+         * Whether index i closes a chunk is integer bookkeeping, resolved once beforehand. */
+        {
+            unsigned char* closes = (unsigned char*)calloc((size_t)(N > 0 ? N : 1), 1);
+            if (reduce_chunk > 0)
+                for (t = 0; t < T; t++) {
+                    int64_t uoff = unique_ids ? unique_offsets[t] : 0;
+                    for (i = offsets[t * B]; i < offsets[(t + 1) * B]; i++) {
+                        int64_t u2 = inv[i] + uoff;
+                        if (cnt[u2] > reduce_chunk) {
+                            seen[u2]++;
+                            closes[i] = (unsigned char)((seen[u2] % reduce_chunk == 0 || seen[u2] == cnt[u2]) ? 2 : 1);
+                        }
                     }
-                    if (chunked) {
-                        seen[u2]++;
-                        if (seen[u2] % reduce_chunk == 0 || seen[u2] == cnt[u2]) { /* chunk closed */
-                            float* tot = G + u2 * max_D;
-                            for (d = 0; d < D; d++) {
-                                tot[d] = tot[d] + acc[d];
-                                acc[d] = 0.0f;
+                }
+#pragma omp parallel
+            {
+                int nth = 1, tid = 0;
+                int64_t tt, ii;
+#ifdef _OPENMP
+                nth = omp_get_num_threads();
+                tid = omp_get_thread_num();
+#endif
+                for (tt = 0; tt < T; tt++) {
+                    int32_t D = D_offsets[tt + 1] - D_offsets[tt], d;
+                    const int32_t d_lo = 0, d_hi = D;
+                    int64_t b;
+                    int64_t uoff = unique_ids ? unique_offsets[tt] : 0;
+                    for (b = 0; b < B; b++) {
+                        int64_t s0 = offsets[tt * B + b], e0 = offsets[tt * B + b + 1];
+                        float mean = 1.0f / (float)(e0 - s0);
+                        for (ii = s0; ii < e0; ii++) {
+                            const float* g = pooling_mode == 2 ? grad_output + ii * max_D
+                                                               : grad_output + b * total_D + D_offsets[tt];
+                            int64_t u2 = inv[ii] + uoff;
+                            int chunked = closes[ii] != 0;
+                            float* acc;
+                            if (u2 % nth != tid) continue;
+                            acc = chunked ? P + u2 * max_D : G + u2 * max_D;
+                            for (d = d_lo; d < d_hi; d++) {
+                                float v = g[d];
+                                if (gradient_clipping)
+                                    v = v < -max_gradient ? -max_gradient : (v > max_gradient ? max_gradient : v);
+                                if (pooling_mode == 1) v = v * mean;
+                                acc[d] = acc[d] + v;
+                            }
+                            if (closes[ii] == 2) { /* chunk closed */
+                                float* tot = G + u2 * max_D;
+                                for (d = d_lo; d < d_hi; d++) {
+                                    tot[d] = tot[d] + acc[d];
+                                    acc[d] = 0.0f;
+                                }
                             }
                         }
                     }
                 }
             }
+            free(closes);
         }
         free(cnt);
         free(seen);
