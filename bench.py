@@ -161,7 +161,7 @@ def run_ours(args):
     ids_per_step_rank = T * B
     out = torch.empty((B, T * DIM), device=dev, dtype=torch.float32)
     if world == 1:
-        batches = [one_hot_batch(gen, rows, B, ALPHA, dev) for _ in range(n_batches)]
+        batches = [one_hot_batch(gen, rows, B, args.zipf_alpha, dev) for _ in range(n_batches)]
         grad = torch.randn((B, T * DIM), generator=gen, device=dev, dtype=torch.float32)
     else:
         # every rank holds the ids of ITS 65536 samples for all 26 fields and the upstream gradient of its
@@ -379,7 +379,8 @@ def run_ours(args):
             "data": "synthetic",
             "config": {
                 "workload": ("configs[1]: 26 tables dim 128 fp32, batch 65536 per GPU one-hot Zipf(1.1), sparse Adam, "
-                             "table-wise sharding") if args.profile_tables == 0 else
+                             "table-wise sharding") if (args.profile_tables == 0 and args.zipf_alpha == ALPHA) else
+                            f"EXPERIMENT, not the benchmark: Zipf alpha {args.zipf_alpha}" if args.profile_tables == 0 else
                             (f"REDUCED profiling case, not the benchmark: the {T} largest tables of configs[1] with rows "
                              f"capped at {row_cap}, batch 65536, sparse Adam"),
                 "tables_this_rank": T, "rows_this_rank": sum(rows), "row_cap": row_cap,
@@ -531,6 +532,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--zipf-alpha", type=float, default=ALPHA,
+                    help="1-GPU experiments only: skew of the ids (the benchmark's is 1.1; not the benchmark otherwise)")
     ap.add_argument("--profile-tables", type=int, default=0,
                     help="reduced case for profiler captures: keep only the K largest tables (1 GPU, no e2e loop)")
     ap.add_argument("--profile-row-cap", type=int, default=524288, help="row cap of the reduced case")

@@ -165,6 +165,10 @@ RECSDK_API int recsdk_unique_sorted_static(const int64_t* ids, int64_t n, int ke
  * 0.0f.  Both are run-to-run deterministic; C = 64 is the fast default (hot
  * rows do not serialise on one warp).
  * ========================================================================= */
+/* flags of recsdk_tbe_backward_args.  STAGED_UPDATE: move the rows of the update through shared memory with bulk
+ * asynchronous copies (rows of 128..1024 floats, 16-byte aligned tables; other shapes ignore the flag).  Same
+ * results bit for bit; measured slightly slower than the default on the benchmark workload, so it is opt-in. */
+#define RECSDK_BWD_STAGED_UPDATE 1
 typedef struct {
     const float* grad_output; /* [B,total_D]  (NONE: [N,max_D]) */
     float* dev_weights;
@@ -197,6 +201,7 @@ typedef struct {
     void* ev_update_start;
     void* ev_update_stop;
     recsdk_sample_shards grad_shards; /* optional (num_shards > 0): `grad_output` is ignored; read only */
+    int32_t flags;                    /* RECSDK_BWD_* */
 } recsdk_tbe_backward_args;
 RECSDK_API size_t recsdk_tbe_backward_workspace_bytes(int64_t N, int32_t max_D);
 RECSDK_API int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stream);

@@ -55,7 +55,7 @@ class TbeBackwardArgs(C.Structure):
         ("reduce_chunk", C.c_int32), ("learning_rate", C.c_float), ("eps", C.c_float), ("beta1", C.c_float),
         ("beta2", C.c_float), ("iter", C.c_int64), ("gradient_clipping", C.c_int32), ("max_gradient", C.c_float),
         ("weights_numel", C.c_int64), ("dev_status", vp), ("workspace", vp), ("workspace_bytes", C.c_size_t),
-        ("ev_update_start", vp), ("ev_update_stop", vp), ("grad_shards", SampleShards),
+        ("ev_update_start", vp), ("ev_update_stop", vp), ("grad_shards", SampleShards), ("flags", C.c_int32),
     ]
 
 

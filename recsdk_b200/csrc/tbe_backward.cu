@@ -18,11 +18,13 @@
 // order of the reference kernels (ComputeAdagrad / ComputeAdam / ComputeSgd).
 #include <limits.h>
 #include <math.h>
+#include <stdlib.h>
 
 #ifdef RECSDK_EMULATE
 #include "common.cuh"
 #else
 #include "prims.cuh"
+#include "tma.cuh"
 #endif
 
 namespace recsdk {
@@ -59,6 +61,7 @@ struct BwdParams {
     float* __restrict__ partial;         // [chunks, max_D]
     const int64_t* __restrict__ counters;  // {U, total_chunks}
     recsdk_sample_shards sh;  // num_shards > 0: gradient rows are read from the sample owners' buffers
+    int staged_update;        // use update_staged_kernel where the shape allows
 };
 
 // ---------------------------------------------------------------------------- 1. expand
@@ -435,6 +438,50 @@ __global__ void __launch_bounds__(256) run_meta_kernel(BwdParams p, const KeyT* 
 }
 
 // ---------------------------------------------------------------------------- 5b. row update
+// Summed gradient of one unique row, columns (cb + lane + k*G), into `acc` (zero on entry): its chunk sums when
+// the run was chunked, else its gradient rows in position order; `g0` is the already loaded first row of the
+// run (first_direct).
+template <typename V, int G, int K>
+__device__ __forceinline__ void row_gradient(const BwdParams& p, const RunMeta& m, int cb, int lane, int nvec,
+                                             bool first_direct, const typename V::T (&g0)[K], typename V::T (&acc)[K])
+{
+    const int rs = m.rs, re = m.rs + m.len;
+    const bool chunked = m.chunk_base >= 0;
+    if (chunked) {
+        const int nc = (m.len + kChunk - 1) / kChunk;
+        int c = 0;
+        for (; c + 4 <= nc; c += 4) {
+            typename V::T v[4][K];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    const int col = cb + lane + k * G;
+                    v[u][k] = col < nvec ? V::ld(p.partial + static_cast<int64_t>(m.chunk_base + c + u) * p.max_D + V::W * col)
+                                         : V::zero();
+                }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < K; ++k) acc[k] = add4(acc[k], v[u][k]);
+        }
+        for (; c < nc; ++c) {
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const int col = cb + lane + k * G;
+                if (col < nvec)
+                    acc[k] = add4(acc[k], V::ld(p.partial + static_cast<int64_t>(m.chunk_base + c) * p.max_D + V::W * col));
+            }
+        }
+    } else if (first_direct) {
+#pragma unroll
+        for (int k = 0; k < K; ++k) acc[k] = add4(acc[k], map4(g0[k], [&](float x) { return prep_grad(p, x, 1.0f); }));
+        if (re > rs + 1) sum_grad_rows<V, G, K>(p, rs + 1, re, cb, lane, nvec, acc);
+    } else {
+        sum_grad_rows<V, G, K>(p, rs, re, cb, lane, nvec, acc);
+    }
+}
+
 template <typename V, int G, int K, int OPT>
 __device__ __forceinline__ void update_body(const BwdParams& p, const RunMeta& m, int lane, int32_t D)
 {
@@ -459,39 +506,7 @@ __device__ __forceinline__ void update_body(const BwdParams& p, const RunMeta& m
                 if (first_direct) g0[k] = V::ld_stream(reinterpret_cast<const float*>(m.g0_ptr) + V::W * col);
             }
         }
-        if (chunked) {
-            const int nc = (m.len + kChunk - 1) / kChunk;
-            int c = 0;
-            for (; c + 4 <= nc; c += 4) {
-                typename V::T v[4][K];
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                    for (int k = 0; k < K; ++k) {
-                        const int col = cb + lane + k * G;
-                        v[u][k] = col < nvec ? V::ld(p.partial + static_cast<int64_t>(m.chunk_base + c + u) * p.max_D + V::W * col)
-                                             : V::zero();
-                    }
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                    for (int k = 0; k < K; ++k) acc[k] = add4(acc[k], v[u][k]);
-            }
-            for (; c < nc; ++c) {
-#pragma unroll
-                for (int k = 0; k < K; ++k) {
-                    const int col = cb + lane + k * G;
-                    if (col < nvec)
-                        acc[k] = add4(acc[k], V::ld(p.partial + static_cast<int64_t>(m.chunk_base + c) * p.max_D + V::W * col));
-                }
-            }
-        } else if (first_direct) {
-#pragma unroll
-            for (int k = 0; k < K; ++k) acc[k] = add4(acc[k], map4(g0[k], [&](float x) { return prep_grad(p, x, 1.0f); }));
-            if (re > rs + 1) sum_grad_rows<V, G, K>(p, rs + 1, re, cb, lane, nvec, acc);
-        } else {
-            sum_grad_rows<V, G, K>(p, rs, re, cb, lane, nvec, acc);
-        }
+        row_gradient<V, G, K>(p, m, cb, lane, nvec, first_direct, g0, acc);
 #pragma unroll
         for (int k = 0; k < K; ++k) {
             const int col = cb + lane + k * G;
@@ -504,6 +519,144 @@ __device__ __forceinline__ void update_body(const BwdParams& p, const RunMeta& m
         }
     }
 }
+
+#ifndef RECSDK_EMULATE
+// ---------------------------------------------------------------------------- 5c. row update, rows staged by TMA
+// Same result as update_kernel<32, K, OPT>, different data movement: a warp owns a ring of kStages shared-memory
+// stages and keeps the rows of its next kStages-1 unique rows in flight as bulk asynchronous copies (w, m1, m2
+// and the run's first gradient row, one mbarrier per stage) while it updates the current one.  The copies hold no
+// registers while they are in flight, so a block of 8 warps x 4 stages x 2 KB keeps ~50 KB of row data moving
+// per block; three blocks fit an SM.  Lane s of the warp is the producer of stage s: it fetches the row record
+// one iteration ahead, arms the barrier and issues the copies; all lanes consume.  Records of rows that cannot
+// use 128-bit accesses are not staged and take the plain path.
+constexpr int32_t kMetaStagedBit = 1 << 29;
+
+template <int OPT>
+struct StagedArrays {
+    static constexpr int kState = OPT == RECSDK_OPT_ADAM ? 2 : (OPT == RECSDK_OPT_ADAGRAD ? 1 : 0);
+    static constexpr int kCount = 1 + kState + 1;  // w, states, first gradient row
+};
+
+static inline size_t update_staged_smem_bytes(int warps, int stages, int arrays, int32_t max_D)
+{
+    return static_cast<size_t>(warps) * stages * (static_cast<size_t>(arrays) * max_D * 4 + sizeof(int4) * 2 + sizeof(uint64_t));
+}
+
+template <int OPT, int kStages>
+__global__ void __launch_bounds__(256, 3) update_staged_kernel(BwdParams p, const RunMeta* __restrict__ meta)
+{
+    constexpr int NARR = StagedArrays<OPT>::kCount;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int W = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t row_bytes_max = static_cast<size_t>(p.max_D) * 4;
+    const size_t data_bytes = static_cast<size_t>(W) * kStages * NARR * row_bytes_max;
+    unsigned char* data = smem_raw + static_cast<size_t>(warp) * kStages * NARR * row_bytes_max;
+    int4* smeta = reinterpret_cast<int4*>(smem_raw + data_bytes) + static_cast<size_t>(warp) * kStages * 2;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + data_bytes + static_cast<size_t>(W) * kStages * 2 * sizeof(int4)) +
+                     static_cast<size_t>(warp) * kStages;
+    if (lane < kStages) mbar_init(&bars[lane], 1);
+    mbar_fence_init();
+    __syncwarp();
+
+    const int64_t U = p.counters[0];
+    const int64_t warps_total = static_cast<int64_t>(gridDim.x) * W;
+    const int64_t wid = static_cast<int64_t>(blockIdx.x) * W + warp;
+    const bool mean = p.mode == RECSDK_POOL_MEAN;
+
+    // producer side, run by lane `s` alone: publish the record of the row that stage s will hold and start its copies
+    auto arm = [&](int s, int4 lo, int4 hi) {
+        const int64_t row_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.y)) << 32) | static_cast<uint32_t>(lo.x);
+        const int64_t g0_ptr = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
+        const bool staged = row_off >= 0 && (hi.z & kMetaVecBit) != 0;
+        if (staged) hi.z |= kMetaStagedBit;
+        smeta[2 * s] = lo;
+        smeta[2 * s + 1] = hi;
+        if (!staged) return;
+        const uint32_t rb = static_cast<uint32_t>(hi.z & (kMetaStagedBit - 1)) * 4u;
+        const bool direct = hi.w < 0 && !mean;  // the first gradient row is used as it lies
+        unsigned char* st = data + static_cast<size_t>(s) * NARR * row_bytes_max;
+        mbar_expect_tx(&bars[s], (1u + StagedArrays<OPT>::kState + (direct ? 1u : 0u)) * rb);
+        bulk_g2s(st, p.w + row_off, rb, &bars[s]);
+        if (OPT != RECSDK_OPT_SGD) bulk_g2s(st + row_bytes_max, p.m1 + row_off, rb, &bars[s]);
+        if (OPT == RECSDK_OPT_ADAM) bulk_g2s(st + 2 * row_bytes_max, p.m2 + row_off, rb, &bars[s]);
+        if (direct) bulk_g2s(st + (NARR - 1) * row_bytes_max, reinterpret_cast<const float*>(g0_ptr), rb, &bars[s]);
+    };
+
+    // prologue: lane s fills stage s with the warp's s-th row
+    if (lane < kStages) {
+        const int64_t r = wid + static_cast<int64_t>(lane) * warps_total;
+        if (r < U) arm(lane, __ldg(reinterpret_cast<const int4*>(meta + r)), __ldg(reinterpret_cast<const int4*>(meta + r) + 1));
+    }
+    __syncwarp();
+
+    uint32_t phase = 0;  // bit s: parity the consumer waits for on stage s
+    int s = 0;
+    bool failed = false;
+    for (int64_t r = wid; r < U; r += warps_total) {
+        // the record of the row that will take this stage over, requested before the stage is consumed
+        const int64_t rn = r + static_cast<int64_t>(kStages) * warps_total;
+        int4 nlo = make_int4(0, 0, 0, 0), nhi = nlo;
+        if (lane == s && rn < U) {
+            nlo = __ldg(reinterpret_cast<const int4*>(meta + rn));
+            nhi = __ldg(reinterpret_cast<const int4*>(meta + rn) + 1);
+        }
+        const int4 lo = smeta[2 * s], hi = smeta[2 * s + 1];
+        RunMeta m;
+        m.row_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.y)) << 32) | static_cast<uint32_t>(lo.x);
+        m.g0_ptr = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
+        m.rs = hi.x;
+        m.len = hi.y;
+        m.D = hi.z;
+        m.chunk_base = hi.w;
+        const int32_t D = m.D & (kMetaStagedBit - 1);
+        if (m.D & kMetaStagedBit) {
+            const bool ok = mbar_wait_bounded(&bars[s], (phase >> s) & 1u);
+            if (!__all_sync(kFullMask, ok)) {
+                set_status(p.status, RECSDK_ERR_CUDA, -2, r);
+                failed = true;
+                break;
+            }
+            phase ^= 1u << s;
+            const unsigned char* st = data + static_cast<size_t>(s) * NARR * row_bytes_max;
+            const float4* sw = reinterpret_cast<const float4*>(st);
+            const float4* sm1 = reinterpret_cast<const float4*>(st + row_bytes_max);
+            const float4* sm2 = reinterpret_cast<const float4*>(st + 2 * row_bytes_max);
+            const float4* sg = reinterpret_cast<const float4*>(st + (NARR - 1) * row_bytes_max);
+            const int nvec = D >> 2;
+            const bool first_direct = m.chunk_base < 0 && !mean;
+            for (int cb = 0; cb < nvec; cb += 32) {
+                const int col = cb + lane;
+                const bool on = col < nvec;
+                float4 acc[1], g0[1];
+                acc[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                g0[0] = (on && first_direct) ? sg[col] : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 w = on ? sw[col] : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 m1 = (on && OPT != RECSDK_OPT_SGD) ? sm1[col] : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 m2 = (on && OPT == RECSDK_OPT_ADAM) ? sm2[col] : make_float4(0.f, 0.f, 0.f, 0.f);
+                row_gradient<V4, 32, 1>(p, m, cb, lane, nvec, first_direct, g0, acc);
+                if (on) {
+                    opt_update_vec<OPT>(p, acc[0], w, m1, m2);
+                    st_f4(p.w + m.row_off + 4 * col, w);
+                    if (OPT != RECSDK_OPT_SGD) st_f4(p.m1 + m.row_off + 4 * col, m1);
+                    if (OPT == RECSDK_OPT_ADAM) st_f4(p.m2 + m.row_off + 4 * col, m2);
+                }
+            }
+        } else if (m.row_off >= 0) {
+            update_body<V1, 32, 1, OPT>(p, m, lane, D);
+        }
+        __syncwarp();  // every lane is done with the stage before its producer refills it
+        if (lane == s && rn < U) arm(s, nlo, nhi);
+        __syncwarp();
+        s = s + 1 == kStages ? 0 : s + 1;
+    }
+    if (failed) {
+        // never expected: give the copies still in flight a bounded time to land before the block's shared
+        // memory is released
+        for (int q = 0; q < kStages; ++q) (void)mbar_wait_bounded(&bars[q], (phase >> q) & 1u, 1 << 12);
+    }
+}
+#endif  // RECSDK_EMULATE
 
 // G lanes per unique row; the row's record tells where everything is.  The record of the group's NEXT row is
 // fetched before the current row is processed, so the record load is off the critical path of every row but
@@ -596,9 +749,47 @@ static int bits_for(int64_t x)
     return b < 1 ? 1 : b;
 }
 
+// Staged update: rows of 128..1024 floats with 16-byte aligned tables.  Returns false when the shape does not
+// qualify (the caller then launches update_kernel).
+template <int OPT, int kStages>
+static bool launch_update_staged_impl(const BwdParams& p, const RunMeta* meta, int warps, cudaStream_t st)
+{
+    const size_t smem = update_staged_smem_bytes(warps, kStages, StagedArrays<OPT>::kCount, p.max_D);
+    static bool attr_set = false;  // one attribute per instantiation; setting it again is harmless
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(update_staged_kernel<OPT, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024) !=
+            cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        attr_set = true;
+    }
+    update_staged_kernel<OPT, kStages><<<kNumSMs * 3, warps * 32, smem, st>>>(p, meta);
+    return true;
+}
+
+static bool launch_update_staged(const BwdParams& p, const RunMeta* meta, cudaStream_t st)
+{
+    if (!p.staged_update || !p.base_aligned || (p.max_D & 3) != 0 || p.max_D < 128 || p.max_D > 1024) return false;
+    const int arrays = p.opt == RECSDK_OPT_ADAM ? 4 : (p.opt == RECSDK_OPT_ADAGRAD ? 3 : 2);
+    const int stages = p.max_D <= 256 ? 4 : 2;
+    int warps = 8;
+    while (warps > 1 && update_staged_smem_bytes(warps, stages, arrays, p.max_D) > 72 * 1024) warps >>= 1;
+    if (update_staged_smem_bytes(warps, stages, arrays, p.max_D) > 72 * 1024) return false;
+#define RECSDK_STAGED(OPT) \
+    (stages == 4 ? launch_update_staged_impl<OPT, 4>(p, meta, warps, st) : launch_update_staged_impl<OPT, 2>(p, meta, warps, st))
+    switch (p.opt) {
+        case RECSDK_OPT_ADAGRAD: return RECSDK_STAGED(RECSDK_OPT_ADAGRAD);
+        case RECSDK_OPT_ADAM: return RECSDK_STAGED(RECSDK_OPT_ADAM);
+        default: return RECSDK_STAGED(RECSDK_OPT_SGD);
+    }
+#undef RECSDK_STAGED
+}
+
 template <int G, int K>
 static void launch_update(const BwdParams& p, const RunMeta* meta, int64_t N, cudaStream_t st)
 {
+    if (G == 32 && launch_update_staged(p, meta, st)) return;
     const int groups_per_block = 256 / G;
     const int grid = grid_for(N, groups_per_block, 8);
     switch (p.opt) {
@@ -765,6 +956,7 @@ extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stre
         for (int s = 0; s < sh.num_shards; ++s) grad_aligned = grad_aligned && aligned16(sh.ptrs[s]);
     }
     p.sh = sh;
+    p.staged_update = (a->flags & RECSDK_BWD_STAGED_UPDATE) ? 1 : 0;
     p.base_aligned = (grad_aligned && aligned16(a->dev_weights) && aligned16(a->momentum1) &&
                       aligned16(a->momentum2) && aligned16(ws.partial))
                          ? 1

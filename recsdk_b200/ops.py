@@ -170,7 +170,7 @@ def tbe_backward(grad_output, dev_weights, momentum1, momentum2, weights_offsets
                  reduce_chunk: int = 64, gradient_clipping: bool = False, max_gradient: float = 0.0,
                  status: Optional[torch.Tensor] = None, bounds_check: bool = True,
                  workspace: Optional[torch.Tensor] = None, update_events=None,
-                 grad_shards: Optional[SampleShards] = None) -> None:
+                 grad_shards: Optional[SampleShards] = None, staged_update: bool = False) -> None:
     """``update_events``: optional (start, stop) torch.cuda.Event pair (created with enable_timing=True and
     recorded at least once before) that the library records around the row-update kernel.
     ``grad_shards``: read the gradient rows from the sample owners' buffers (``grad_output`` is then None)."""
@@ -200,6 +200,7 @@ def tbe_backward(grad_output, dev_weights, momentum1, momentum2, weights_offsets
     if workspace is None or workspace.numel() < wsz:
         workspace = _workspace(wsz, dev_weights.device)
     a = _lib.TbeBackwardArgs()
+    a.flags = 1 if staged_update else 0  # RECSDK_BWD_STAGED_UPDATE
     a.grad_output = _ptr(grad_output) if grad_shards is None else None
     if grad_shards is not None:
         grad_shards.fill(a.grad_shards)

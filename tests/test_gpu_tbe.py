@@ -195,6 +195,37 @@ def test_backward_bit_exact(case, mode, opt, unique, chunk):
         np.testing.assert_array_equal(dm2.cpu().numpy(), em2)
 
 
+@pytest.mark.parametrize("opt", [1, 2, 3])
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("case", [3, 5, 8])
+def test_backward_staged_update_bit_exact(case, mode, opt):
+    """RECSDK_BWD_STAGED_UPDATE (rows moved through shared memory by bulk asynchronous copies) gives the same bits
+    as the default update; shapes of 128, 256 and 1024 floats per row, hot rows included."""
+    rng = np.random.default_rng(2500 + case)
+    c = make_case(rng, **BWD_CASES[case])
+    from recsdk_b200 import ops
+
+    grad = rng.standard_normal((c["B"], c["total_D"])).astype(np.float32)
+    w = c["w"].copy()
+    m1 = np.full_like(w, 0.1) if opt == 1 else rng.uniform(0, 0.01, w.size).astype(np.float32)
+    m2 = rng.uniform(0, 0.01, w.size).astype(np.float32)
+    dw, dm1, dm2 = _t(w), _t(m1), _t(m2)
+    st = ops.new_status(DEV)
+    bits = int(c["hs"][-1]).bit_length()
+    for it in (1, 2, 3):
+        port.tbe_backward(grad, w, m1, m2, c["wo"], c["do"], c["hs"], c["indices"], c["offsets"], c["T"], c["B"],
+                          c["total_D"], c["max_D"], mode, opt, 0.05, 1e-8, 0.9, 0.999, it, reduce_chunk=64)
+        ops.tbe_backward(_t(grad), dw, dm1, dm2, _t(c["wo"]), _t(c["do"]), _t(c["hs"]), _t(c["indices"]),
+                         _t(c["offsets"]), c["total_D"], c["max_D"], mode, opt, 0.05, 1e-8, 0.9, 0.999, it,
+                         total_hash_size_bits=bits, reduce_chunk=64, status=st, staged_update=True)
+    ops.raise_on_status(st)
+    np.testing.assert_array_equal(dw.cpu().numpy(), w)
+    if opt != 3:
+        np.testing.assert_array_equal(dm1.cpu().numpy(), m1)
+    if opt == 2:
+        np.testing.assert_array_equal(dm2.cpu().numpy(), m2)
+
+
 def test_backward_gradient_clipping_and_64bit_keys():
     rng = np.random.default_rng(7)
     c = make_case(rng, rows=[300, 200], dims=[16, 16], B=40, max_len=5)
