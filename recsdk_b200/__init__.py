@@ -8,6 +8,8 @@ from . import _lib
 _lib.load()
 
 from . import ops  # noqa: E402
+from .embcache import AdmitAndEvictConfig, EmbcacheManager, EmbConfig, SwapInfo  # noqa: E402
 from .tables import FeatureFilter, IdsMapper, SwapManager  # noqa: E402
 
-__all__ = ["ops", "IdsMapper", "SwapManager", "FeatureFilter"]
+__all__ = ["ops", "IdsMapper", "SwapManager", "FeatureFilter", "EmbcacheManager", "EmbConfig", "AdmitAndEvictConfig",
+           "SwapInfo"]

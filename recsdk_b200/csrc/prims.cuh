@@ -191,6 +191,34 @@ constexpr int kMaxRadix = 512;
 static inline int64_t sort_num_tiles(int64_t n) { return ceil_div(n > 0 ? n : 1, kSortTile); }
 // uint32 scratch needed: histogram [radix][tiles] + digit totals [radix]
 static inline size_t sort_scratch_u32(int64_t n) { return static_cast<size_t>(sort_num_tiles(n)) * kMaxRadix + kMaxRadix; }
+// Fused mode (see radix_sort_pairs_fused): one histogram per pass, all zeroed up front and filled by the kernel
+// that PRODUCES that pass's input, so no pass reads its keys twice.
+constexpr int kMaxSortPasses = 8;
+static inline size_t sort_scratch_u32_fused(int64_t n)
+{
+    return static_cast<size_t>(sort_num_tiles(n)) * kMaxRadix * kMaxSortPasses + kMaxRadix;
+}
+
+// What the producer of a pass's input adds for the element it writes at position `pos`: one count in the
+// histogram cell (digit of the key in that pass, tile of pos).
+struct SortHistSink {
+    uint32_t* hist;  // [radix][tiles] of the pass that will read the keys; nullptr = off
+    int64_t tiles;
+    int shift;
+    uint32_t mask;
+    // Called by ALL lanes of a warp (valid = this lane carries an element): lanes that hit the same cell --
+    // the usual case for the runs of equal keys a skewed batch has -- are combined into one atomic.
+    template <typename KeyT>
+    __device__ __forceinline__ void add_warp(bool valid, KeyT key, int64_t pos) const
+    {
+        if (hist == nullptr) return;
+        const unsigned lane = threadIdx.x & 31;
+        const unsigned cell = valid ? static_cast<unsigned>(static_cast<int64_t>((key >> shift) & mask) * tiles + pos / kSortTile)
+                                    : 0xffffffffu - lane;
+        const unsigned peers = __match_any_sync(kFullMask, cell);
+        if (valid && (peers & lanemask_lt()) == 0) atomicAdd(hist + cell, static_cast<uint32_t>(__popc(peers)));
+    }
+};
 
 template <typename KeyT, int BITS>
 __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const KeyT* __restrict__ keys, int64_t n, int shift,
@@ -240,7 +268,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
                                                                     uint32_t* __restrict__ vals_out, int64_t n,
                                                                     int shift, const uint32_t* __restrict__ hist,
                                                                     const uint32_t* __restrict__ totals,
-                                                                    int64_t tiles)
+                                                                    int64_t tiles, SortHistSink next)
 {
     constexpr int RADIX = 1 << BITS;
     constexpr int PER = RADIX / kSortThreads;  // digits per thread in the block-wide steps
@@ -303,12 +331,14 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
 #pragma unroll
     for (int r = 0; r < kSortRounds; ++r) {
         const int64_t i = tile0 + r * 32 + lane;
+        uint32_t pos = 0;
         if (i < n) {
             const unsigned d = static_cast<unsigned>((key[r] >> shift) & (RADIX - 1));
-            const uint32_t pos = warp_cnt[warp][d] + rank[r];
+            pos = warp_cnt[warp][d] + rank[r];
             keys_out[pos] = key[r];
             vals_out[pos] = vals_in[i];
         }
+        next.add_warp(i < n, key[r], static_cast<int64_t>(pos));
     }
 }
 
@@ -322,8 +352,21 @@ static inline void radix_sort_pass(const KeyT* kin, const uint32_t* vin, KeyT* k
     uint32_t* totals = scratch + tiles * RADIX;
     sort_hist_kernel<KeyT, BITS><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, n, shift, hist, tiles);
     sort_scan_kernel<<<RADIX, 256, 0, st>>>(hist, tiles, totals);
+    sort_scatter_kernel<KeyT, BITS><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(
+        kin, vin, kout, vout, n, shift, hist, totals, tiles, SortHistSink{nullptr, 0, 0, 0u});
+}
+
+// One pass of the fused mode: the histogram of this pass already exists (its producer filled it); the scatter
+// fills the histogram of the next pass (`next`) while it writes that pass's input.
+template <typename KeyT, int BITS>
+static inline void radix_sort_pass_fused(const KeyT* kin, const uint32_t* vin, KeyT* kout, uint32_t* vout, int64_t n,
+                                         int shift, uint32_t* hist, uint32_t* totals, SortHistSink next, cudaStream_t st)
+{
+    constexpr int RADIX = 1 << BITS;
+    const int64_t tiles = sort_num_tiles(n);
+    sort_scan_kernel<<<RADIX, 256, 0, st>>>(hist, tiles, totals);
     sort_scatter_kernel<KeyT, BITS><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, vin, kout, vout, n, shift,
-                                                                                          hist, totals, tiles);
+                                                                                          hist, totals, tiles, next);
 }
 
 // Number of passes and bits per pass for keys of `key_bits` significant bits.
@@ -354,6 +397,50 @@ static inline int radix_sort_pairs(KeyT* keys_a, uint32_t* vals_a, KeyT* keys_b,
             radix_sort_pass<KeyT, 9>(kin, vin, kout, vout, n, p * 9, scratch, st);
         else
             radix_sort_pass<KeyT, 8>(kin, vin, kout, vout, n, p * 8, scratch, st);
+        cur ^= 1;
+    }
+    return cur;
+}
+
+// Fused mode.  The caller (1) asks for the sink of pass 0 with radix_fused_begin -- which also zeroes all
+// histograms -- (2) lets the kernel that writes keys_a call sink.add(key, position) for every element, and
+// (3) calls radix_sort_pairs_fused.  Each pass is then a scan and a scatter: three launches fewer per pass
+// than the plain mode and no second read of the keys.
+struct RadixFusedPlan {
+    int passes, bits;
+    int64_t tiles;
+    SortHistSink first;
+};
+static inline RadixFusedPlan radix_fused_begin(int64_t n, int key_bits, uint32_t* scratch, cudaStream_t st)
+{
+    RadixFusedPlan pl;
+    radix_plan(key_bits, &pl.passes, &pl.bits);
+    pl.tiles = sort_num_tiles(n);
+    const size_t per_pass = static_cast<size_t>(pl.tiles) * (size_t(1) << pl.bits);
+    cudaMemsetAsync(scratch, 0, per_pass * pl.passes * sizeof(uint32_t), st);
+    pl.first = SortHistSink{scratch, pl.tiles, 0, (1u << pl.bits) - 1u};
+    return pl;
+}
+template <typename KeyT>
+static inline int radix_sort_pairs_fused(const RadixFusedPlan& pl, KeyT* keys_a, uint32_t* vals_a, KeyT* keys_b,
+                                         uint32_t* vals_b, int64_t n, uint32_t* scratch, cudaStream_t st)
+{
+    if (n <= 1) return 0;
+    const size_t per_pass = static_cast<size_t>(pl.tiles) * (size_t(1) << pl.bits);
+    uint32_t* totals = scratch + static_cast<size_t>(pl.tiles) * kMaxRadix * kMaxSortPasses;
+    int cur = 0;
+    for (int p = 0; p < pl.passes; ++p) {
+        KeyT* kin = cur ? keys_b : keys_a;
+        uint32_t* vin = cur ? vals_b : vals_a;
+        KeyT* kout = cur ? keys_a : keys_b;
+        uint32_t* vout = cur ? vals_a : vals_b;
+        uint32_t* hist = scratch + per_pass * p;
+        SortHistSink next{nullptr, 0, 0, 0u};
+        if (p + 1 < pl.passes) next = SortHistSink{scratch + per_pass * (p + 1), pl.tiles, (p + 1) * pl.bits, (1u << pl.bits) - 1u};
+        if (pl.bits == 9)
+            radix_sort_pass_fused<KeyT, 9>(kin, vin, kout, vout, n, p * 9, hist, totals, next, st);
+        else
+            radix_sort_pass_fused<KeyT, 8>(kin, vin, kout, vout, n, p * 8, hist, totals, next, st);
         cur ^= 1;
     }
     return cur;

@@ -78,7 +78,7 @@ __device__ __forceinline__ int64_t feature_of_position(const int64_t* offs, int6
 
 template <typename KeyT>
 __global__ void __launch_bounds__(256) expand_pooled_kernel(BwdParams p, KeyT* __restrict__ keys,
-                                                            uint32_t* __restrict__ vals)
+                                                            uint32_t* __restrict__ vals, SortHistSink sink)
 {
     const int lane = threadIdx.x & 31;
     const int64_t num_bags = p.T * p.B;
@@ -103,25 +103,33 @@ __global__ void __launch_bounds__(256) expand_pooled_kernel(BwdParams p, KeyT* _
             }
             const uint32_t f = __shfl_sync(kFullMask, f_l, j);
             const uint32_t b = __shfl_sync(kFullMask, b_l, j);
+            int64_t key = 0;
             if (pos < p1) {
-                int64_t key = p.uid != nullptr ? p.uinv[pos] + p.uoff[f] : p.cumsum[f] + p.idx[pos];
+                key = p.uid != nullptr ? p.uinv[pos] + p.uoff[f] : p.cumsum[f] + p.idx[pos];
                 keys[pos] = static_cast<KeyT>(key);
                 vals[pos] = (f << p.bshift) | b;
             }
+            sink.add_warp(pos < p1, static_cast<KeyT>(key), pos);
         }
     }
 }
 
 template <typename KeyT>
 __global__ void __launch_bounds__(256) expand_nobag_kernel(BwdParams p, KeyT* __restrict__ keys,
-                                                           uint32_t* __restrict__ vals)
+                                                           uint32_t* __restrict__ vals, SortHistSink sink)
 {
-    for (int64_t pos = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; pos < p.N;
-         pos += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t f = feature_of_position(p.offs, p.T, p.B, pos);
-        int64_t key = p.uid != nullptr ? p.uinv[pos] + p.uoff[f] : p.cumsum[f] + p.idx[pos];
-        keys[pos] = static_cast<KeyT>(key);
-        vals[pos] = static_cast<uint32_t>(pos);
+    // warp-uniform trip count: the histogram sink is a warp-wide call
+    for (int64_t pos0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31); pos0 < p.N;
+         pos0 += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t pos = pos0 + (threadIdx.x & 31);
+        int64_t key = 0;
+        if (pos < p.N) {
+            const int64_t f = feature_of_position(p.offs, p.T, p.B, pos);
+            key = p.uid != nullptr ? p.uinv[pos] + p.uoff[f] : p.cumsum[f] + p.idx[pos];
+            keys[pos] = static_cast<KeyT>(key);
+            vals[pos] = static_cast<uint32_t>(pos);
+        }
+        sink.add_warp(pos < p.N, static_cast<KeyT>(key), pos);
     }
 }
 
@@ -732,7 +740,7 @@ static BwdWorkspace carve_bwd(void* base, int64_t N, int32_t max_D)
     w.keys_b = c.take<uint64_t>(n);
     w.vals_a = c.take<uint32_t>(n);
     w.vals_b = c.take<uint32_t>(n);
-    w.sort_scratch = c.take<uint32_t>(sort_scratch_u32(N));
+    w.sort_scratch = c.take<uint32_t>(sort_scratch_u32_fused(N));
     w.run_start = c.take<int>(n + 1);
     w.meta = c.take<RunMeta>(n);
     w.desc = c.take<int2>(max_chunks);
@@ -832,13 +840,14 @@ static int run_backward(const recsdk_tbe_backward_args* a, BwdParams p, const Bw
     KeyT* ka = static_cast<KeyT*>(ws.keys_a);
     KeyT* kb = static_cast<KeyT*>(ws.keys_b);
     cudaMemsetAsync(ws.counters, 0, 8 * sizeof(int64_t), st);  // {U, chunks, indices in chunked runs, ...}
-    // 1. expand
+    // 1. expand; it also fills the histogram of the first sort pass
+    const RadixFusedPlan plan = radix_fused_begin(N, key_bits, ws.sort_scratch, st);
     if (a->pooling_mode == RECSDK_POOL_NONE)
-        expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, ka, ws.vals_a);
+        expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, ka, ws.vals_a, plan.first);
     else
-        expand_pooled_kernel<KeyT><<<grid_for(a->T * a->B, 8 * 32), 256, 0, st>>>(p, ka, ws.vals_a);
-    // 2. sort
-    const int which = radix_sort_pairs<KeyT>(ka, ws.vals_a, kb, ws.vals_b, N, key_bits, ws.sort_scratch, st);
+        expand_pooled_kernel<KeyT><<<grid_for(a->T * a->B, 8 * 32), 256, 0, st>>>(p, ka, ws.vals_a, plan.first);
+    // 2. sort: per pass a scan and a scatter that fills the next pass's histogram
+    const int which = radix_sort_pairs_fused<KeyT>(plan, ka, ws.vals_a, kb, ws.vals_b, N, ws.sort_scratch, st);
     const KeyT* keys = which ? kb : ka;
     p.vals = which ? ws.vals_b : ws.vals_a;
     // 3. runs
