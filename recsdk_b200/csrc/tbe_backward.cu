@@ -5,15 +5,22 @@
 //   1. expand   : every index position p -> (key, val); key identifies the row
 //                 (hash_size_cumsum[t] + idx, or inverse[p] + unique_offsets[t]),
 //                 val packs (feature, sample) of the bag whose gradient row p takes.
-//   2. sort     : stable LSD radix sort of the pairs by key (prims.cuh).  Equal
+//                 The kernel also counts the first sort pass's histogram.
+//   2. sort     : stable LSD radix sort of the pairs by key (prims.cuh), per pass a
+//                 scan and a scatter that counts the next pass's histogram.  Equal
 //                 keys stay in ascending position order -> fixed reduction order.
-//   3. runs     : head flags -> inclusive scan -> run id per position, run starts, U.
-//   4. chunks   : runs longer than C are cut into chunks of C positions; chunk
-//                 sums go to a partial buffer (keeps Zipf-hot rows off one warp).
-//   5. update   : G lanes per unique row: sum its gradient rows (or its chunk
-//                 sums) in order, apply the optimizer, write w / m1 / m2 once.
-//                 128-bit accesses; w, m1, m2 of a row are read and written
-//                 exactly once per step.
+//   3. runs     : head flags (computed inside the scan) -> run starts, U.
+//   4. records  : one thread per unique row resolves everything the update needs
+//                 (row address, first gradient row address, run, width) into a
+//                 32-byte record; runs longer than C reserve chunk slots.
+//   4b. partial : chunk sums of the long runs (keeps Zipf-hot rows off one warp).
+//   5. update   : G lanes per unique row: record (fetched one row ahead) -> w / m1 /
+//                 m2 / first gradient row in one wave of loads -> remaining gradient
+//                 rows or chunk sums in order -> optimizer -> one write of w / m1 /
+//                 m2.  Optionally (RECSDK_BWD_STAGED_UPDATE) the rows travel through
+//                 a shared-memory ring filled by bulk asynchronous copies.
+// Gradient rows may live in the sample owners' buffers on other GPUs
+// (recsdk_sample_shards): the same kernels then read them over peer mappings.
 // The float arithmetic uses explicit round-to-nearest intrinsics in the operand
 // order of the reference kernels (ComputeAdagrad / ComputeAdam / ComputeSgd).
 #include <limits.h>
