@@ -42,7 +42,7 @@ LR, BETA1, BETA2, EPS = 1e-3, 0.9, 0.999, 1e-8
 # Adam state is 3 x rows x 512 B.  The 26 seeded tables hold 144.9 M rows = 222 GB, more than one
 # GPU's HBM, so single-GPU runs cap every table at this many rows (Zipf ids are drawn over the capped vocab).
 ROW_CAP_1GPU = 16_000_000
-UPDATE_KERNEL_DRAM_BYTES = 879_443_968 + 429_988_096
+UPDATE_KERNEL_DRAM_BYTES = 880_223_488 + 442_036_224
 HBM_BUDGET_BYTES = 150e9
 
 
