@@ -1,5 +1,5 @@
-"""Row-wise sharded lookup (rows split by id % W) on 2 GPUs against the CPU oracle run on the whole tables and the
-global batch.  The forward pools the same rows in the same order -> bit-exact.  The backward sums a row's gradients
+"""Dedup-exchange lookups -- row-wise (rows split by id % W) and table-wise (whole tables on ranks, distinct rows
+fetched by the sample owners) -- on 2 GPUs against the CPU oracle run on the whole tables and the global batch.  The forward pools the same rows in the same order -> bit-exact.  The backward sums a row's gradients
 in two levels (per source rank, then across ranks in rank order) where the single-table oracle sums them flat, so
 the updated tables are compared at 1e-5; running the step twice from the same state must give identical bits.
 Needs two GPUs; skipped otherwise."""
@@ -25,7 +25,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, errors):
+def _worker(rank, world, port, errors, scheme="row"):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
@@ -36,11 +36,12 @@ def _worker(rank, world, port, errors):
         dev = torch.device("cuda", rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
         from oracle import port as orc
-        from recsdk_b200.rowwise import RowWiseShardedEmbeddingBag
+        from recsdk_b200.rowwise import RowWiseShardedEmbeddingBag, TableWiseDedupEmbeddingBag
         from recsdk_b200.tbe import EmbOptimType, PoolingMode
 
         F, D = len(ROWS), DIM
         B = world * B_LOCAL
+        owner = [f % world for f in range(F)]
         rng = np.random.default_rng(321)  # identical global data on every rank
         weights = [rng.uniform(-0.1, 0.1, (ROWS[f], D)).astype(np.float32) for f in range(F)]
         lens = rng.integers(0, MAX_L + 1, size=(F, B))
@@ -53,11 +54,18 @@ def _worker(rank, world, port, errors):
             ln = np.array([lens[f, b] for f in range(F) for b in sample_range], np.int64)
             return idx.astype(np.int64), np.concatenate([[0], np.cumsum(ln)]).astype(np.int64)
 
-        bag = RowWiseShardedEmbeddingBag(ROWS, D, world, rank, optimizer=EmbOptimType.ADAM,
-                                         pooling_mode=PoolingMode.SUM, device=dev, learning_rate=0.05, eps=1e-8,
-                                         beta1=0.9, beta2=0.999)
-        for f in range(F):
-            shard = weights[f][rank::world]
+        kw = dict(optimizer=EmbOptimType.ADAM, pooling_mode=PoolingMode.SUM, device=dev, learning_rate=0.05, eps=1e-8,
+                  beta1=0.9, beta2=0.999)
+        if scheme == "row":
+            bag = RowWiseShardedEmbeddingBag(ROWS, D, world, rank, **kw)
+            mine_tables = list(range(F))
+            shard_of = lambda a: a[rank::world]  # noqa: E731
+        else:
+            bag = TableWiseDedupEmbeddingBag(ROWS, D, owner, world, rank, **kw)
+            mine_tables = [f for f in range(F) if owner[f] == rank]
+            shard_of = lambda a: a  # noqa: E731
+        for f in mine_tables:
+            shard = shard_of(weights[f])
             bag.local_table(f)[:shard.shape[0]].copy_(torch.from_numpy(shard))
         mine = range(rank * B_LOCAL, (rank + 1) * B_LOCAL)
         idx_l, offs_l = csr(mine)
@@ -84,14 +92,14 @@ def _worker(rank, world, port, errors):
                 if attempt == 0 and it == 1:
                     np.testing.assert_array_equal(out.cpu().numpy(), exp_out[rank * B_LOCAL:(rank + 1) * B_LOCAL])
                 bag.backward(g_t)
-            results.append([bag.local_table(f).clone() for f in range(F)])
-        for f in range(F):
+            results.append({f: bag.local_table(f).clone() for f in mine_tables})
+        for f in mine_tables:
             assert torch.equal(results[0][f], results[1][f])  # run-to-run identical bits
         for it in (1, 2):
             orc.tbe_backward(grad, ew, em1, em2, wo, do, hs, idx_g, offs_g, F, B, F * D, D, 0, 2, 0.05, 1e-8, 0.9,
                              0.999, it, reduce_chunk=64)
-        for f in range(F):
-            exp = ew[wo[f]:wo[f] + ROWS[f] * D].reshape(ROWS[f], D)[rank::world]
+        for f in mine_tables:
+            exp = shard_of(ew[wo[f]:wo[f] + ROWS[f] * D].reshape(ROWS[f], D))
             got = results[0][f][:exp.shape[0]].cpu().numpy()
             np.testing.assert_allclose(got, exp, rtol=0, atol=1e-5)
         dist.barrier()
@@ -101,7 +109,8 @@ def _worker(rank, world, port, errors):
         raise
 
 
-def test_row_wise_sharded_lookup_two_gpus():
+@pytest.mark.parametrize("scheme", ["row", "table"])
+def test_dedup_exchange_lookup_two_gpus(scheme):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -110,7 +119,7 @@ def test_row_wise_sharded_lookup_two_gpus():
     ctx = mp.get_context("spawn")
     errors = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, errors)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, errors, scheme)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -122,10 +131,11 @@ def test_row_wise_sharded_lookup_two_gpus():
     assert all(p.exitcode == 0 for p in procs)
 
 
-def test_row_wise_single_rank_is_bit_exact():
+@pytest.mark.parametrize("scheme", ["row", "table"])
+def test_dedup_exchange_single_rank_is_bit_exact(scheme):
     """World 1: the same code path without a process group; both summation levels collapse to the oracle's order."""
     from oracle import port as orc
-    from recsdk_b200.rowwise import RowWiseShardedEmbeddingBag
+    from recsdk_b200.rowwise import RowWiseShardedEmbeddingBag, TableWiseDedupEmbeddingBag
     from recsdk_b200.tbe import EmbOptimType, PoolingMode
 
     F, D, B = len(ROWS), DIM, 40
@@ -137,8 +147,10 @@ def test_row_wise_single_rank_is_bit_exact():
     offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
     grad = rng.standard_normal((B, F * D)).astype(np.float32)
     for mode in (PoolingMode.SUM, PoolingMode.MEAN):
-        bag = RowWiseShardedEmbeddingBag(ROWS, D, 1, 0, optimizer=EmbOptimType.EXACT_ADAGRAD, pooling_mode=mode,
-                                         device="cuda", learning_rate=0.05, eps=1e-8, initial_accumulator_value=0.1)
+        kw = dict(optimizer=EmbOptimType.EXACT_ADAGRAD, pooling_mode=mode, device="cuda", learning_rate=0.05, eps=1e-8,
+                  initial_accumulator_value=0.1)
+        bag = (RowWiseShardedEmbeddingBag(ROWS, D, 1, 0, **kw) if scheme == "row"
+               else TableWiseDedupEmbeddingBag(ROWS, D, [0] * F, 1, 0, **kw))
         for f in range(F):
             bag.local_table(f).copy_(torch.from_numpy(weights[f]))
         w_flat = np.concatenate([w.reshape(-1) for w in weights])
