@@ -152,9 +152,19 @@ def run_ours(args):
     T = len(rows)
     B = BATCH * world  # a table owner sees the samples of every rank (weak scaling: BATCH per GPU)
 
-    module = HybridSplitTableBatchedEmbeddingBagsCodegen(
-        [(r, DIM) for r in rows], optimizer=EmbOptimType.ADAM, pooling_mode=PoolingMode.SUM, learning_rate=LR,
-        eps=EPS, beta1=BETA1, beta2=BETA2, device=dev, weights_init=(-0.01, 0.01), seed=SEED + rank)
+    dedup = world > 1 and args.exchange == "dedup"
+    opt_kw = dict(optimizer=EmbOptimType.ADAM, pooling_mode=PoolingMode.SUM, learning_rate=LR, eps=EPS, beta1=BETA1,
+                  beta2=BETA2, device=dev, weights_init=(-0.01, 0.01), seed=SEED + rank)
+    if dedup:
+        # the sample owners fetch the DISTINCT rows their samples need and pool locally; gradients return summed
+        # per distinct row: ids, rows and gradient rows cross in NCCL all-to-alls, ~5x fewer bytes than pooled rows
+        from recsdk_b200.rowwise import TableWiseDedupEmbeddingBag
+
+        bag = TableWiseDedupEmbeddingBag([rows_all[t] for t in sh.output_table_order], DIM,
+                                         [sh.owner[t] for t in sh.output_table_order], world, rank, **opt_kw)
+        module = bag.owner
+    else:
+        module = HybridSplitTableBatchedEmbeddingBagsCodegen([(r, DIM) for r in rows], **opt_kw)
     gen = torch.Generator(device=dev)
     gen.manual_seed(SEED + 17 * rank)
     n_batches = 4  # rotate distinct batches so consecutive steps touch different rows
@@ -172,7 +182,11 @@ def run_ours(args):
         batches = [torch.stack([zipf_ids(gen, BATCH, rows_all[t], ALPHA, dev) for t in sh.output_table_order])
                    .view(N_TABLES, BATCH, 1) for _ in range(n_batches)]
         owner_offsets = torch.arange(T * B + 1, dtype=torch.int64, device=dev)
-        if args.exchange == "fused":
+        if dedup:
+            del out
+            grad = torch.randn((BATCH, N_TABLES * DIM), generator=gen, device=dev, dtype=torch.float32)
+            local_offsets = torch.arange(N_TABLES * BATCH + 1, dtype=torch.int64, device=dev)
+        elif args.exchange == "fused":
             # pooled rows and gradients of this rank's samples live in peer-mapped buffers: the owners' forward
             # kernels store into them and their backward kernels read from them over NVLink
             from recsdk_b200.peer import FusedTableWiseExchange
@@ -197,6 +211,7 @@ def run_ours(args):
 
     fused = world > 1 and args.exchange == "fused"
     phase_marks = []  # per timed step: events at the phase boundaries (this rank's stream)
+    last_out = [None]
 
     def step_resident(i, timed=False, idx_offs=None):
         marks = []
@@ -208,6 +223,22 @@ def run_ours(args):
                 marks.append(e)
 
         mark()
+        if dedup:
+            ids_local = batches[i % n_batches] if idx_offs is None else idx_offs[0]
+            mark()
+            evs = None
+            if timed:
+                evs = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                for e in evs:
+                    e.record()
+                ev_pairs.append(evs)
+                phase_marks.append(marks)
+            last_out[0] = bag.forward(ids_local.view(-1), local_offsets)
+            mark()
+            mark()
+            bag.backward(grad, update_events=evs)
+            mark()
+            return
         idx, offs, g = owner_view(i) if idx_offs is None else (*idx_offs, grad)
         mark()
         evs = None
@@ -299,6 +330,9 @@ def run_ours(args):
             o = module(d_idx, d_offs)  # autograd-tracked lookup; backward runs the fused optimizer
             o.backward(grad)
             res = o
+        elif dedup:
+            step_resident(i, idx_offs=(d_idx, None))
+            res = last_out[0]
         elif fused:
             idx, offs, _ = owner_view(i, ids_local=d_idx)
             step_resident(i, idx_offs=(idx, offs))
@@ -351,6 +385,8 @@ def run_ours(args):
         peak, peak_kind = measured_peak_gbs()
         S = 2  # Adam state slots
         N = ids_per_step_rank
+        if dedup:
+            N = module._last_N  # the owner's update runs over the distinct rows the ranks asked for
         # algorithmic bytes of one row-update launch: per unique row read+write of w, m, v and three 4-byte
         # plan entries; per index that it reduces itself (runs of <= 64) the gradient row and its 4-byte
         # (feature, sample) tag; per chunk sum of a longer run one row of the partial buffer.  The gradient
@@ -392,7 +428,9 @@ def run_ours(args):
                 "reduce_chunk": 64,
                 "exchange": ("none (1 GPU)" if world == 1 else
                              "ids: NCCL all-to-all; pooled rows and gradients: peer stores / loads inside the "
-                             "forward / backward kernels" if fused else "NCCL all-to-all x3"),
+                             "forward / backward kernels" if fused else
+                             "distinct rows fetched by the sample owners: NCCL all-to-alls of unique ids, rows and "
+                             "per-row gradient sums" if dedup else "NCCL all-to-all x3"),
             },
             "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
             "step_hbm_frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
@@ -537,7 +575,7 @@ def main():
     ap.add_argument("--profile-tables", type=int, default=0,
                     help="reduced case for profiler captures: keep only the K largest tables (1 GPU, no e2e loop)")
     ap.add_argument("--profile-row-cap", type=int, default=524288, help="row cap of the reduced case")
-    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl", "dedup"],
                     help="N>1: pooled rows / gradients move inside the kernels over peer mappings (fused) or "
                          "through NCCL all-to-alls (nccl, the reference's scheme)")
     ap.add_argument("--cpu-budget", type=float, default=15.0)

@@ -303,6 +303,7 @@ __global__ void __launch_bounds__(256) tbe_forward_nobag_kernel(FwdParams p)
     }
 }
 
+#ifndef RECSDK_EMULATE  // host side: not part of host-side SIMT emulation builds (tests/emu)
 template <int G, int K>
 static void launch_pooled(const FwdParams& p, cudaStream_t st)
 {
@@ -370,3 +371,6 @@ extern "C" int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream
     RECSDK_CUDA_CHECK_LAUNCH();
     return RECSDK_OK;
 }
+#else
+}  // namespace recsdk
+#endif  // RECSDK_EMULATE

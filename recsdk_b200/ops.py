@@ -124,13 +124,17 @@ def tbe_forward(dev_weights, weights_offsets, D_offsets, indices, offsets, total
 
 
 # --------------------------------------------------------------------------- A1 sorted unique
-def unique_sorted(ids: torch.Tensor, key_bits: int = 64) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Returns (unique_buffer[n], inverse[n], num_unique[1]); the first num_unique entries of the buffer are valid."""
+def unique_sorted(ids: torch.Tensor, key_bits: int = 64,
+                  fill: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (unique_buffer[n], inverse[n], num_unique[1]); the first num_unique entries of the buffer are valid.
+    ``fill``: value the rest of the buffer is set to beforehand (e.g. INT64_MAX keeps the whole buffer sorted, so it
+    can be searched without reading num_unique back)."""
     lib = _lib.load()
     _chk(ids, torch.int64, "ids")
     n = ids.numel()
     dev = ids.device
-    uniq = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
+    uniq = (torch.empty(max(n, 1), dtype=torch.int64, device=dev) if fill is None
+            else torch.full((max(n, 1),), fill, dtype=torch.int64, device=dev))
     inv = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
     cnt = torch.zeros(1, dtype=torch.int64, device=dev)
     wsz = lib.recsdk_unique_sorted_workspace_bytes(n)

@@ -60,13 +60,14 @@ class _DedupExchangeLookup:
     def forward(self, indices: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
         """indices [N] int64 (global row ids), offsets [F*B+1] feature-major -> pooled [B, F*dim]."""
         F, D, W, G, dev = self.F, self.dim, self.world, self.G, self.device
-        uniq, perm, send_counts = self._partition(indices, offsets)
-        n_u = uniq.numel()
+        uniq_buf, perm, send_counts = self._partition(indices, offsets)
         recv_counts = torch.empty_like(send_counts)
         _a2a(recv_counts.view(-1), send_counts.view(-1).contiguous(), [G] * W, [G] * W, self.group)
-        send_splits = send_counts.sum(1).tolist()
-        recv_splits = recv_counts.sum(1).tolist()
-        n_recv = int(sum(recv_splits))
+        # the one host read of the forward: how many ids go to / come from every rank
+        splits = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).tolist()
+        send_splits, recv_splits = [int(x) for x in splits[0]], [int(x) for x in splits[1]]
+        n_u, n_recv = sum(send_splits), sum(recv_splits)
+        uniq = uniq_buf[:n_u]
         recv_ids = torch.empty(n_recv, dtype=torch.int64, device=dev)
         _a2a(recv_ids, uniq, recv_splits, send_splits, self.group)
         # owner: one row per received id; group (s, g) is feature s*G + g of the owner's module
@@ -85,8 +86,9 @@ class _DedupExchangeLookup:
         return out
 
     # ------------------------------------------------------------------ backward + optimizer
-    def backward(self, grad_output: torch.Tensor) -> None:
-        """grad_output [B, F*dim]: gradient of this rank's pooled rows.  Updates the owners' tables in place."""
+    def backward(self, grad_output: torch.Tensor, update_events=None) -> None:
+        """grad_output [B, F*dim]: gradient of this rank's pooled rows.  Updates the owners' tables in place.
+        ``update_events``: passed to the owner's fused backward (events around its row-update kernel)."""
         perm, offsets, n_u, send_splits, recv_splits, local, owner_offsets, n_recv = self._ctx
         F, D, dev = self.F, self.dim, self.device
         # per fetched row: sum of the bag gradients that used it (SGD with lr = -1 on zeros yields the sum itself)
@@ -100,7 +102,7 @@ class _DedupExchangeLookup:
         _a2a(recv_grad.view(-1), fetched_grad[:n_u * D], [r * D for r in recv_splits], [s * D for s in send_splits],
              self.group)
         if n_recv:
-            self.owner.backward_from(recv_grad, local, owner_offsets)
+            self.owner.backward_from(recv_grad, local, owner_offsets, update_events=update_events)
         else:
             self.owner.iter[0] += 1
 
@@ -130,10 +132,10 @@ class RowWiseShardedEmbeddingBag(_DedupExchangeLookup):
         _, uniq_buf, perm, _, num_out = ops.bucketize(lengths, indices, F, W, do_unique=True)
         # (destination, feature) group of every unique id: scatter the group of the inputs that map to it
         grp_in = (indices % W) * F + self._feature_of_position(offsets, N, B)
-        n_u = int(num_out.item())
-        grp = torch.empty(n_u, dtype=torch.int64, device=dev)
+        # entries of `grp` past the number of unique ids keep the sentinel and fall into the extra bin
+        grp = torch.full((N,), W * F, dtype=torch.int64, device=dev)
         grp[perm] = grp_in
-        return uniq_buf[:n_u].contiguous(), perm, torch.bincount(grp, minlength=W * F).view(W, F)
+        return uniq_buf, perm, torch.bincount(grp, minlength=W * F + 1)[:W * F].view(W, F)
 
     def _owner_rows(self, recv_ids):
         return torch.div(recv_ids, self.world, rounding_mode="floor")
@@ -185,12 +187,11 @@ class TableWiseDedupEmbeddingBag(_DedupExchangeLookup):
             lin = (indices.view(F, B) + self.table_base.view(F, 1)).view(-1)
         else:
             lin = indices + self.table_base[self._feature_of_position(offsets, N, B)]
-        uniq_buf, inv, cnt = ops.unique_sorted(lin, key_bits=self.key_bits)
-        n_u = int(cnt.item())
-        uniq = uniq_buf[:n_u]
+        # the unused tail of the buffer holds INT64_MAX, so the whole buffer is sorted and can be searched
+        uniq_buf, inv, _ = ops.unique_sorted(lin, key_bits=self.key_bits, fill=torch.iinfo(torch.int64).max)
         # ascending linear rows are grouped by owner rank already
-        bounds = torch.searchsorted(uniq, self.rank_base)
-        return uniq, inv, (bounds[1:] - bounds[:-1]).view(self.world, 1)
+        bounds = torch.searchsorted(uniq_buf, self.rank_base)
+        return uniq_buf, inv, (bounds[1:] - bounds[:-1]).view(self.world, 1)
 
     def _owner_rows(self, recv_ids):
         return recv_ids - self._rank_base_host[self.rank]

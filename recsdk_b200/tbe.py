@@ -222,6 +222,7 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
     def _backward_impl(self, grad_output, indices, offsets, unique_ids, unique_offsets, unique_inverse, iteration,
                        update_events=None, grad_shards=None) -> None:
         a = self.optimizer_args
+        self._last_N = indices.numel()  # indices of the most recent backward (bandwidth accounting)
         need = ops.tbe_backward_workspace_bytes(indices.numel(), self.max_D)
         if self._ws is None or self._ws.numel() < need:
             self._ws = torch.empty(need, dtype=torch.uint8, device=self.current_device)
