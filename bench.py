@@ -459,6 +459,188 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+
+# ============================================================================ per-operator measurements
+def run_ops(args):
+    """`--workload ops`: every other entry point of the path (dedup, key tables, cache policy, bucketize, row
+    moves, TF-flavour optimizers, restore) timed on the GPU at the sizes the configs give them, with the CPU
+    implementation timed beside it on the same inputs: the reference's own compiled classes where oracle/_ref holds
+    them ("reference"), else the C restatement ("port").  Small ops (a few MB) are launch- and latency-bound; the
+    bandwidth fraction is printed for orientation only.  One JSON line."""
+    import numpy as np
+    import torch
+
+    from oracle import port, ref
+    from recsdk_b200 import FeatureFilter, IdsMapper, SwapManager, ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, peak_kind = measured_peak_gbs()
+    rng = np.random.default_rng(SEED)
+    res = {}
+
+    def gpu_ms(fn, iters=20, warm=3, setup=None):
+        for i in range(warm):
+            if setup:
+                setup(i)
+            fn(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if setup is None:
+            a.record()
+            for i in range(iters):
+                fn(warm + i)
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / iters
+        tot = 0.0
+        for i in range(iters):
+            setup(warm + i)
+            a.record()
+            fn(warm + i)
+            b.record()
+            torch.cuda.synchronize()
+            tot += a.elapsed_time(b)
+        return tot / iters
+
+    def cpu_ms(fn, iters=3):
+        fn(0)
+        t0 = time.perf_counter()
+        for i in range(iters):
+            fn(1 + i)
+        return (time.perf_counter() - t0) / iters * 1e3
+
+    def entry(name, n, unit, g_ms, c_ms, kind, alg_bytes):
+        res[name] = {"n": n, "unit": unit, "gpu_ms": g_ms, "gpu_per_s": n / (g_ms * 1e-3), "cpu_ms": c_ms,
+                     "cpu_kind": kind, "cpu_per_s": n / (c_ms * 1e-3), "algorithmic_bytes": alg_bytes,
+                     "gbs": alg_bytes / (g_ms * 1e-3) / 1e9, "frac_of_peak": alg_bytes / (g_ms * 1e-3) / 1e9 / peak}
+
+    try:
+        have_ref = ref.available() and ref.embcache() is not None
+    except OSError:
+        have_ref = False
+
+    # ---- A1 sorted unique + inverse: the ids of one configs[1] step (26 x 65536, linearised, 28-bit keys)
+    rows = [min(r, ROW_CAP_1GPU) for r in seeded_rows()]
+    base = np.concatenate([[0], np.cumsum(rows)])[:-1]
+    ids_np = np.concatenate([base[t] + np.minimum((rng.pareto(1.1, BATCH) * 10).astype(np.int64), rows[t] - 1)
+                             for t in range(N_TABLES)]).astype(np.int64)
+    ids = torch.from_numpy(ids_np).to(dev)
+    bits = int(sum(rows)).bit_length()
+    g = gpu_ms(lambda i: ops.unique_sorted(ids, key_bits=bits))
+    u = int(ops.unique_sorted(ids, key_bits=bits)[2].item())
+    c = cpu_ms(lambda i: port.unique_sorted(ids_np))
+    entry("unique_sorted", ids_np.size, "ids", g, c, "port", 16 * ids_np.size + 8 * u)
+
+    # ---- A2 IdsMapper.ids2indices_unique: dynamic-table config, 131072 keys per step, 30 % new
+    n_keys, steps = 131072, 26
+    issued = rng.integers(0, 2**62, size=n_keys, dtype=np.int64)
+    stream = []
+    for s_ in range(steps):
+        fresh = rng.integers(0, 2**62, size=int(n_keys * 0.3), dtype=np.int64)
+        keys = np.concatenate([fresh, issued[rng.integers(0, issued.size, size=n_keys - fresh.size)]])
+        rng.shuffle(keys)
+        issued = np.concatenate([issued, fresh])
+        stream.append(keys)
+    d_stream = [torch.from_numpy(k).to(dev) for k in stream]
+    gm = IdsMapper(64 << 20, True, device=dev)
+    g = gpu_ms(lambda i: gm.ids2indices_unique(d_stream[i], check=False))
+    if have_ref:
+        t = ref.load_hybrid()
+        cm = t.classes.hybrid.IdsMapper(64 << 20, True)
+        c_stream = [torch.from_numpy(k) for k in stream]
+        c = cpu_ms(lambda i: cm.ids2indices_unique(c_stream[i]), iters=5)
+        kind = "reference"
+    else:
+        cm = port.IdsMapper(64 << 20, True)
+        c = cpu_ms(lambda i: cm.ids2indices_unique(stream[i]), iters=5)
+        kind = "port"
+    entry("ids_mapper_ids2indices_unique", n_keys, "keys", g, c, kind, n_keys * (8 + 16 + 24))
+
+    # ---- A4 + A5 cache policy step (record_timestamp, statistics, count_filter, compute_swap_info)
+    gs, gf = SwapManager(64 << 20, 1, device=dev), FeatureFilter("t", 2, 50, 10, capacity=1 << 24, device=dev)
+
+    def gpu_policy(i):
+        k = d_stream[i]
+        ts = torch.full_like(k, i)
+        gf.RecordTimestamp(k, ts)
+        gf.StatisticsKeyCount(k)
+        uq_buf, _, uq_n = ops.unique_sorted(k)  # the caller's dedup (sorted here; order does not change the work)
+        uq = uq_buf[:int(uq_n.item())]
+        gf.CountFilter(uq)
+        gs.ComputeSwapInfoDevice(uq)
+
+    g = gpu_ms(gpu_policy)
+    if have_ref:
+        cs, cf, kind = ref.SwapManager(64 << 20, 1), ref.FeatureFilter(2, 50, 10), "reference"
+    else:
+        cs, cf, kind = port.SwapManager(64 << 20, 1), port.FeatureFilter(2, 50, 10), "port"
+
+    def cpu_policy(i):
+        k = stream[i]
+        cf.record_timestamp(k, np.full(k.size, i, np.int64))
+        cf.statistics_key_count(k)
+        uq = np.unique(k)
+        cs.compute_swap_info(cf.count_filter(uq))
+
+    c = cpu_ms(cpu_policy, iters=5)
+    entry("cache_policy_step", n_keys, "keys", g, c, kind, n_keys * (32 * 2 + 16 + 40))
+
+    # ---- A3 bucketize: row-wise config, 262144 ids, 8 buckets, with dedup
+    nb, Fb, Wb = 262144, 4, 8
+    b_idx = rng.integers(0, 10**9, size=nb, dtype=np.int64)
+    b_idx[: nb // 2] = b_idx[nb // 2:][: nb // 2] % 100000
+    b_len = np.ones(nb, np.int64)
+    d_idx, d_len = torch.from_numpy(b_idx).to(dev), torch.from_numpy(b_len).to(dev)
+    g = gpu_ms(lambda i: ops.bucketize(d_len, d_idx, Fb, Wb, do_unique=True, return_count=True))
+    if have_ref:
+        t = ref.load_hybrid()
+        ci, cl = torch.from_numpy(b_idx), torch.from_numpy(b_len)
+        c = cpu_ms(lambda i: t.ops.hybrid.block_bucketize_sparse_features_cpu(
+            cl, ci, False, True, torch.ones(Fb, dtype=torch.int64), Wb, None, None, None, 0, None, False, False, True, True))
+        kind = "reference"
+    else:
+        c = cpu_ms(lambda i: port.bucketize(b_len, b_idx, Fb, Wb, do_unique=True, return_count=True))
+        kind = "port"
+    entry("bucketize_unique", nb, "ids", g, c, kind, nb * (8 + 8 + 8 + 8))
+
+    # ---- A8 swap rows: gather + scatter of 65536 rows of 128 floats out of a 4 M-row table
+    D, k_rows, t_rows = DIM, 65536, 4 << 20
+    table = torch.empty(t_rows * D, device=dev).uniform_(-1, 1)
+    slots = torch.randperm(t_rows, device=dev)[:k_rows].contiguous()
+    buf = ops.gather_rows(table, slots, D)
+
+    def swap_rows(i):
+        r = ops.gather_rows(table, slots, D)
+        ops.scatter_rows(table, slots, D, r)
+
+    g = gpu_ms(swap_rows)
+    t_np, s_np = table[: (1 << 20) * D].cpu().numpy(), (slots % (1 << 20)).cpu().numpy()
+    c = cpu_ms(lambda i: port.scatter_rows(t_np, s_np, D, port.gather_rows(t_np, s_np, D)))
+    entry("gather_plus_scatter_rows", k_rows, "rows", g, c, "port", k_rows * D * 4 * 4)
+
+    # ---- A9 LazyAdam on 65536 rows of 128
+    idx32 = slots.to(torch.int32)
+    m_t, v_t = torch.zeros_like(table), torch.zeros_like(table)
+    grad = torch.randn(k_rows, D, device=dev)
+    g = gpu_ms(lambda i: ops.lazy_adam(grad, idx32, m_t, v_t, table, 1e-3, 0.9, 0.999, 1e-8))
+    g_np, i_np = grad.cpu().numpy(), (idx32 % (1 << 20)).cpu().numpy()
+    var_np, m_np, v_np = t_np.copy(), np.zeros_like(t_np), np.zeros_like(t_np)
+    c = cpu_ms(lambda i: port.lazy_adam(g_np, i_np, m_np, v_np, var_np, 1e-3, 0.9, 0.999, 1e-8))
+    entry("lazy_adam", k_rows, "rows", g, c, "port", k_rows * D * 4 * 7)
+
+    # ---- A10 restore: hash_indices[r] = unique[inverse[r] + offset[t]] over one configs[1] step
+    uq, inv, cnt = ops.unique_sorted(ids, key_bits=bits)
+    uoff = torch.tensor([0, u], dtype=torch.int64, device=dev)
+    per_table = torch.tensor([0, ids.numel()], dtype=torch.int64, device=dev)
+    g = gpu_ms(lambda i: ops.restore(uq, inv, uoff, per_table))
+    uq_np, inv_np = uq.cpu().numpy(), inv.cpu().numpy()
+    c = cpu_ms(lambda i: port.restore(uq_np, inv_np, np.array([0, u], np.int64), np.array([0, ids_np.size], np.int64)))
+    entry("restore", ids_np.size, "ids", g, c, "port", ids_np.size * 24)
+
+    emit({"workload": "ops", "n_gpus": 1, "peak_gbs": peak, "peak_kind": peak_kind, "cores": os.cpu_count(),
+          "data": "synthetic", "ops": res})
+
 # ============================================================================ CPU arms (oracle)
 CPU_SAMPLE_ROW_CAP = 262_144
 CPU_SAMPLE_BATCH = 8192
@@ -569,18 +751,26 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="step", choices=["step", "ops"],
+                    help="step: the benchmark (default).  ops: per-operator measurements of the other entry points")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--zipf-alpha", type=float, default=ALPHA,
                     help="1-GPU experiments only: skew of the ids (the benchmark's is 1.1; not the benchmark otherwise)")
     ap.add_argument("--profile-tables", type=int, default=0,
                     help="reduced case for profiler captures: keep only the K largest tables (1 GPU, no e2e loop)")
     ap.add_argument("--profile-row-cap", type=int, default=524288, help="row cap of the reduced case")
-    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl", "dedup"],
-                    help="N>1: pooled rows / gradients move inside the kernels over peer mappings (fused) or "
-                         "through NCCL all-to-alls (nccl, the reference's scheme)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl", "dedup"],
+                    help="N>1: pooled rows / gradients move inside the kernels over peer mappings (fused), through "
+                         "NCCL all-to-alls (nccl, the reference's scheme), or the sample owners fetch distinct rows "
+                         "and pool locally (dedup).  auto: fused at 2 GPUs, dedup from 3 GPUs on (measured: 1.92 vs "
+                         "2.25 ms/step at 2 GPUs, 4.08 vs 2.40 at 8)")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.exchange == "auto":
+        args.exchange = "fused" if int(os.environ.get("WORLD_SIZE", "1")) <= 2 else "dedup"
+    if args.workload == "ops":
+        run_ops(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         if args.warmup < 3:
