@@ -399,7 +399,12 @@ def run_ours(args):
                      (4 * DIM * N + 8 * N + 8 * U + U * 4 * DIM * 2 * (1 + S))
         bits = module.total_hash_size_bits
         passes = min(math.ceil(bits / 8), math.ceil(bits / 9))  # the sort takes 9-bit digits when that saves a pass
-        launches_per_step = 1 + (1 + 3 * passes + 3 + 1 + 1 + 1)  # forward + expand, sort, run scan, plan, partial, update
+        # forward + expand, (scan + scatter) per sort pass, 3 run-scan kernels, records, partial sums, update
+        launches_per_step = 1 + (1 + 2 * passes + 3 + 1 + 1 + 1)
+        if dedup:
+            # + sorted unique of the local ids (load, 3 launches per pass of 4, flag scan 3, write), the owner's
+            # gather, the local pooling, and a second fused backward (local per-row sums, then the owner's update)
+            launches_per_step += (1 + 3 * 4 + 3 + 1) + 1 + (1 + 2 * passes + 3 + 1 + 1 + 1)
         line = {
             "metric": "embedding ids/sec (fwd+bwd+sparse Adam)",
             "value": value,
