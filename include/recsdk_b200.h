@@ -379,6 +379,37 @@ RECSDK_API int recsdk_bucketize(const int64_t* lengths, int64_t lengths_size, co
                                 void* stream);
 
 /* =========================================================================
+ * Jagged-batch utilities either side of the lookup (input / output distribution).
+ * They replace the operators of cust_op/framework/torch_plugin/torch_library/2.6.0/:
+ *   permute2d_sparse_data/permute2d_sparse_data.cpp:21-48   permute_2D_sparse_data
+ *   permute1d_sparse_data/permute1d_sparse_data.cpp:57-93   permute_1D_sparse_data (the same call with B = 1)
+ *   asynchronous_complete_cumsum/asynchronous_complete_cumsum.cpp:18-25
+ *   jagged_to_padded_dense/jagged_to_padded_dense.cpp       jagged_to_padded_dense (+ backward = dense_to_jagged)
+ *   dense_to_jagged/dense_to_jagged.cpp
+ *
+ * permute: out_lengths[t', :] = lengths[permute[t'], :]; the values (and weights) of output row t' are the
+ * whole segment of input row permute[t'] (rows may repeat or be dropped).  values are 4- or 8-byte elements.
+ * *out_total (device, optional) receives the number of output values; they must fit out_capacity
+ * (else RECSDK_ERR_TOO_LARGE in the status block).  permute entries outside [0, T_in) -> RECSDK_ERR_INDEX_RANGE.
+ * complete_cumsum: out[0] = 0, out[i+1] = x[0] + ... + x[i]  (out has n + 1 entries).
+ * jagged_to_padded_dense: dense[b, l, :] = values[offsets[b] + l, :] for l < len_b, else padding_value.
+ * dense_to_jagged: values[offsets[b] + l, :] = dense[b, l, :] for l < min(len_b, max_length), else 0.
+ * ========================================================================= */
+RECSDK_API size_t recsdk_complete_cumsum_workspace_bytes(int64_t n);
+RECSDK_API int recsdk_complete_cumsum(const int64_t* x, int64_t n, int64_t* out, void* workspace, size_t workspace_bytes,
+                                      void* stream);
+RECSDK_API size_t recsdk_permute_sparse_workspace_bytes(int64_t T_in, int64_t T_out);
+RECSDK_API int recsdk_permute_2d_sparse_data(const int64_t* permute, int64_t T_out, const int64_t* lengths, int64_t T_in,
+                                             int64_t B, const void* values, int32_t value_bytes, const float* weights,
+                                             int64_t* out_lengths, void* out_values, float* out_weights,
+                                             int64_t out_capacity, int64_t* out_total, int64_t* dev_status,
+                                             void* workspace, size_t workspace_bytes, void* stream);
+RECSDK_API int recsdk_jagged_to_padded_dense(const float* values, const int64_t* offsets, int64_t B, int32_t D,
+                                             int64_t max_length, float padding_value, float* dense, void* stream);
+RECSDK_API int recsdk_dense_to_jagged(const float* dense, const int64_t* offsets, int64_t B, int32_t D, int64_t max_length,
+                                      float* values, void* stream);
+
+/* =========================================================================
  * Peer mappings for the sample-sharded buffers (one process per GPU on one box).
  * Replaces the two pooled-embedding all-to-alls of the reference's table-wise path
  * (torchrec PooledEmbeddingsAllToAll behind hybrid_torchrec/.../embeddingbag.py:550-593):

@@ -282,3 +282,48 @@ def restore(unique_indices, unique_inverse, unique_offset, offsets_per_table):
     out = np.empty(inv.size, np.int64)
     lib().orc_restore(p64(ui), p64(inv), p64(uo), p64(opt), C.c_int64(opt.size - 1), p64(out))
     return out
+
+
+# ----------------------------------------------------------------------------- jagged-batch utilities (numpy)
+def asynchronous_complete_cumsum(x):
+    """cust_op/framework/torch_plugin/torch_library/2.6.0/asynchronous_complete_cumsum/asynchronous_complete_cumsum.cpp:18-25"""
+    x = np.asarray(x)
+    return np.concatenate([[0], np.cumsum(x)]).astype(x.dtype)
+
+
+def permute_2D_sparse_data(permute, lengths, values, weights=None):
+    """.../permute2d_sparse_data/permute2d_sparse_data.cpp:21-48: row t' of the output is row permute[t'] of the
+    input, lengths and value segments alike."""
+    permute, lengths, values = np.asarray(permute), np.asarray(lengths), np.asarray(values)
+    starts = np.concatenate([[0], np.cumsum(lengths.sum(axis=1))])
+    segs = [np.arange(starts[t], starts[t + 1]) for t in permute]
+    sel = np.concatenate(segs).astype(np.int64) if segs else np.empty(0, np.int64)
+    return lengths[permute], values[sel], (np.asarray(weights)[sel] if weights is not None else None)
+
+
+def permute_1D_sparse_data(permute, lengths, values, weights=None):
+    """.../permute1d_sparse_data/permute1d_sparse_data.cpp:57-93"""
+    out_len, v, w = permute_2D_sparse_data(permute, np.asarray(lengths).reshape(-1, 1), values, weights)
+    return out_len.reshape(-1), v, w
+
+
+def jagged_to_padded_dense(values, offsets, max_length, padding_value=0.0):
+    """.../jagged_to_padded_dense/jagged_to_padded_dense.cpp (v1)"""
+    values, offsets = np.asarray(values, np.float32), np.asarray(offsets)
+    B, D = offsets.size - 1, values.shape[1]
+    out = np.full((B, max_length, D), padding_value, np.float32)
+    for b in range(B):
+        n = min(int(offsets[b + 1] - offsets[b]), max_length)
+        out[b, :n] = values[offsets[b]:offsets[b] + n]
+    return out
+
+
+def dense_to_jagged(dense, offsets):
+    """.../dense_to_jagged/dense_to_jagged.cpp"""
+    dense, offsets = np.asarray(dense, np.float32), np.asarray(offsets)
+    B, L, D = dense.shape
+    out = np.zeros((int(offsets[-1]), D), np.float32)
+    for b in range(B):
+        n = min(int(offsets[b + 1] - offsets[b]), L)
+        out[offsets[b]:offsets[b] + n] = dense[b, :n]
+    return out

@@ -102,6 +102,13 @@ SIGNATURES = {
     "recsdk_sgd": (C.c_int, [vp, vp, C.c_int64, C.c_int32, vp, C.c_float, C.c_float, C.c_int32, vp, C.c_size_t,
                              vp]),
     "recsdk_restore": (C.c_int, [vp, vp, vp, vp, C.c_int64, C.c_int64, vp, vp]),
+    "recsdk_complete_cumsum_workspace_bytes": (C.c_size_t, [C.c_int64]),
+    "recsdk_complete_cumsum": (C.c_int, [vp, C.c_int64, vp, vp, C.c_size_t, vp]),
+    "recsdk_permute_sparse_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
+    "recsdk_permute_2d_sparse_data": (C.c_int, [vp, C.c_int64, vp, C.c_int64, C.c_int64, vp, C.c_int32, vp, vp, vp, vp,
+                                                C.c_int64, vp, vp, vp, C.c_size_t, vp]),
+    "recsdk_jagged_to_padded_dense": (C.c_int, [vp, vp, C.c_int64, C.c_int32, C.c_int64, C.c_float, vp, vp]),
+    "recsdk_dense_to_jagged": (C.c_int, [vp, vp, C.c_int64, C.c_int32, C.c_int64, vp, vp]),
     "recsdk_peer_export": (C.c_int, [vp, vp, C.POINTER(C.c_int64)]),
     "recsdk_peer_import": (C.c_int, [vp, C.c_int64, C.POINTER(vp)]),
     "recsdk_peer_release": (C.c_int, [vp, C.c_int64]),

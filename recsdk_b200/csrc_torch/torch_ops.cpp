@@ -529,10 +529,196 @@ block_bucketize_sparse_features(const Tensor& lengths, const Tensor& indices, bo
     return {new_lengths, new_indices, std::nullopt, std::nullopt, perm, std::nullopt, counts};
 }
 
+// ---------------------------------------------------------------------------- jagged-batch utilities
+// permute2d_sparse_data.cpp:21-48, permute1d_sparse_data.cpp:57-93, asynchronous_complete_cumsum.cpp:18-25,
+// jagged_to_padded_dense.cpp, dense_to_jagged.cpp of cust_op/framework/torch_plugin/torch_library/2.6.0
+static std::tuple<Tensor, Tensor, std::optional<Tensor>> permute_sparse_impl(const Tensor& permute, const Tensor& lengths2d,
+                                                                             const Tensor& values,
+                                                                             const std::optional<Tensor>& weights,
+                                                                             const std::optional<c10::SymInt>& sum)
+{
+    TORCH_CHECK(values.is_cuda(), "values must be a CUDA tensor");
+    const c10::cuda::OptionalCUDAGuard guard(device_of(values));
+    const Tensor perm = permute.to(at::kLong).contiguous();
+    const Tensor len = lengths2d.to(at::kLong).contiguous();
+    const Tensor vals = values.contiguous();
+    TORCH_CHECK(vals.element_size() == 4 || vals.element_size() == 8, "values must have 4- or 8-byte elements");
+    const int64_t T_in = len.size(0), B = len.size(1), T_out = perm.numel();
+    Tensor w;
+    if (weights.has_value() && weights->defined()) {
+        TORCH_CHECK(weights->numel() == vals.numel(), "weights and values length mismatch: ", weights->numel(), " vs ",
+                    vals.numel());
+        w = weights->to(at::kFloat).contiguous();
+    }
+    int64_t total;
+    if (sum.has_value() && sum->guard_int(__FILE__, __LINE__) > 0)
+        total = sum->guard_int(__FILE__, __LINE__);
+    else
+        total = (T_out && B) ? len.index_select(0, perm).sum().item<int64_t>() : 0;
+    Tensor out_len = at::empty({T_out, B}, len.options());
+    Tensor out_vals = at::empty({total}, vals.options());
+    Tensor out_w = w.defined() ? at::empty({total}, w.options()) : Tensor();
+    Tensor status = at::zeros({RECSDK_STATUS_WORDS}, len.options());
+    Tensor ws = at::empty({static_cast<int64_t>(recsdk_permute_sparse_workspace_bytes(T_in, T_out))},
+                          len.options().dtype(at::kByte));
+    check_rc(recsdk_permute_2d_sparse_data(perm.data_ptr<int64_t>(), T_out, len.data_ptr<int64_t>(), T_in, B, vals.data_ptr(),
+                                           static_cast<int32_t>(vals.element_size()),
+                                           w.defined() ? w.data_ptr<float>() : nullptr, out_len.data_ptr<int64_t>(),
+                                           out_vals.data_ptr(), out_w.defined() ? out_w.data_ptr<float>() : nullptr, total,
+                                           nullptr, status.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), cur_stream()),
+             "permute_sparse_data");
+    const Tensor st = status.cpu();
+    TORCH_CHECK(st.data_ptr<int64_t>()[0] == 0, "permute_sparse_data: ", recsdk_error_string(static_cast<int>(st.data_ptr<int64_t>()[0])));
+    std::optional<Tensor> ow;
+    if (out_w.defined()) ow = out_w;
+    return {out_len.to(lengths2d.scalar_type()), out_vals, ow};
+}
+
+std::tuple<Tensor, Tensor, std::optional<Tensor>> permute_2D_sparse_data(const Tensor& permute, const Tensor& lengths,
+                                                                         const Tensor& values,
+                                                                         const std::optional<Tensor>& weights,
+                                                                         std::optional<c10::SymInt> permuted_lengths_sum)
+{
+    TORCH_CHECK(lengths.dim() == 2, "lengths must be 2-D");
+    return permute_sparse_impl(permute, lengths, values, weights, permuted_lengths_sum);
+}
+
+std::tuple<Tensor, Tensor, std::optional<Tensor>> permute_1D_sparse_data(const Tensor& permute, const Tensor& lengths,
+                                                                         const Tensor& values,
+                                                                         const std::optional<Tensor>& weights,
+                                                                         std::optional<c10::SymInt> permuted_lengths_sum)
+{
+    TORCH_CHECK(permute.dim() == 1 && lengths.dim() == 1 && values.dim() == 1, "permute, lengths and values must be 1-D");
+    auto r = permute_sparse_impl(permute, lengths.view({-1, 1}), values, weights, permuted_lengths_sum);
+    return {std::get<0>(r).view({-1}), std::get<1>(r), std::get<2>(r)};
+}
+
+Tensor asynchronous_complete_cumsum(const Tensor& offset)
+{
+    TORCH_CHECK(offset.is_cuda(), "offset must be a CUDA tensor");
+    const c10::cuda::OptionalCUDAGuard guard(device_of(offset));
+    const Tensor x = offset.to(at::kLong).contiguous();
+    const int64_t n = x.numel();
+    Tensor out = at::empty({n + 1}, x.options());
+    Tensor ws = at::empty({static_cast<int64_t>(recsdk_complete_cumsum_workspace_bytes(n))}, x.options().dtype(at::kByte));
+    check_rc(recsdk_complete_cumsum(x.data_ptr<int64_t>(), n, out.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), cur_stream()),
+             "asynchronous_complete_cumsum");
+    return out.to(offset.scalar_type());
+}
+
+static Tensor jagged_to_dense_impl(const Tensor& values, const std::vector<Tensor>& offsets, int64_t max_lengths,
+                                   double padding_value)
+{
+    TORCH_CHECK(values.dim() == 2, "values must be 2-D");
+    TORCH_CHECK(offsets.size() == 1, "offsets must contain exactly 1 tensor, but got ", offsets.size(), " tensors");
+    TORCH_CHECK(max_lengths > 0, "max_lengths must be positive, but got ", max_lengths);
+    TORCH_CHECK(values.is_cuda() && values.scalar_type() == at::kFloat, "values must be a CUDA fp32 tensor");
+    const c10::cuda::OptionalCUDAGuard guard(device_of(values));
+    const Tensor v = values.contiguous();
+    const Tensor offs = offsets[0].to(at::kLong).contiguous();
+    const int64_t B = offs.numel() - 1, D = v.size(1);
+    Tensor out = at::empty({B, max_lengths, D}, v.options());
+    check_rc(recsdk_jagged_to_padded_dense(v.data_ptr<float>(), offs.data_ptr<int64_t>(), B, static_cast<int32_t>(D),
+                                           max_lengths, static_cast<float>(padding_value), out.data_ptr<float>(), cur_stream()),
+             "jagged_to_padded_dense");
+    return out;
+}
+
+static Tensor dense_to_jagged_impl(const Tensor& dense, const std::vector<Tensor>& offsets, int64_t total_L)
+{
+    TORCH_CHECK(dense.dim() == 3, "dense must be 3-D [B, L, D]");
+    TORCH_CHECK(offsets.size() == 1, "offsets must contain exactly 1 tensor, but got ", offsets.size(), " tensors");
+    TORCH_CHECK(dense.is_cuda() && dense.scalar_type() == at::kFloat, "dense must be a CUDA fp32 tensor");
+    const c10::cuda::OptionalCUDAGuard guard(device_of(dense));
+    const Tensor d = dense.contiguous();
+    const Tensor offs = offsets[0].to(at::kLong).contiguous();
+    const int64_t B = d.size(0), L = d.size(1), D = d.size(2);
+    if (total_L < 0) total_L = offs[-1].item<int64_t>();
+    Tensor values = at::empty({total_L, D}, d.options());
+    check_rc(recsdk_dense_to_jagged(d.data_ptr<float>(), offs.data_ptr<int64_t>(), B, static_cast<int32_t>(D), L,
+                                    values.data_ptr<float>(), cur_stream()),
+             "dense_to_jagged");
+    return values;
+}
+
+struct JaggedToPaddedDenseFn : public torch::autograd::Function<JaggedToPaddedDenseFn> {
+    static Tensor forward(AutogradContext* ctx, const Tensor& values, const Tensor& offsets, int64_t max_lengths,
+                          double padding_value)
+    {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        ctx->save_for_backward({offsets});
+        ctx->saved_data["total_L"] = values.size(0);
+        return jagged_to_dense_impl(values, {offsets}, max_lengths, padding_value);
+    }
+    static variable_list backward(AutogradContext* ctx, variable_list grads)
+    {
+        const Tensor offsets = ctx->get_saved_variables()[0];
+        return {dense_to_jagged_impl(grads[0], {offsets}, ctx->saved_data["total_L"].toInt()), Tensor(), Tensor(), Tensor()};
+    }
+};
+
+struct DenseToJaggedFn : public torch::autograd::Function<DenseToJaggedFn> {
+    static Tensor forward(AutogradContext* ctx, const Tensor& dense, const Tensor& offsets, int64_t total_L)
+    {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        ctx->save_for_backward({offsets});
+        ctx->saved_data["L"] = dense.size(1);
+        return dense_to_jagged_impl(dense, {offsets}, total_L);
+    }
+    static variable_list backward(AutogradContext* ctx, variable_list grads)
+    {
+        const Tensor offsets = ctx->get_saved_variables()[0];
+        return {jagged_to_dense_impl(grads[0], {offsets}, ctx->saved_data["L"].toInt(), 0.0), Tensor(), Tensor()};
+    }
+};
+
+Tensor jagged_to_padded_dense_v1(const Tensor& values, std::vector<Tensor> offsets, int64_t max_lengths, double padding_value)
+{
+    TORCH_CHECK(offsets.size() == 1, "offsets must contain exactly 1 tensor, but got ", offsets.size(), " tensors");
+    return JaggedToPaddedDenseFn::apply(values, offsets[0], max_lengths, padding_value);
+}
+Tensor jagged_to_padded_dense_v2(const Tensor& values, std::vector<Tensor> offsets, at::IntArrayRef max_lengths,
+                                 double padding_value)
+{
+    TORCH_CHECK(max_lengths.size() == 1, "max_lengths must contain exactly one element, but got ", max_lengths.size());
+    return jagged_to_padded_dense_v1(values, std::move(offsets), max_lengths[0], padding_value);
+}
+std::tuple<Tensor, std::vector<Tensor>> dense_to_jagged(const Tensor& dense, std::vector<Tensor> offsets,
+                                                        std::optional<c10::SymInt> total_L)
+{
+    TORCH_CHECK(offsets.size() == 1, "offsets must contain exactly 1 tensor, but got ", offsets.size(), " tensors");
+    const int64_t tl = total_L.has_value() ? total_L->guard_int(__FILE__, __LINE__) : -1;
+    return {DenseToJaggedFn::apply(dense, offsets[0], tl), offsets};
+}
+
+// schema strings of the reference's TORCH_LIBRARY(mxrec) blocks, verbatim modulo whitespace
+void define_and_implement_kjt(torch::Library& m)
+{
+    m.def("permute_2D_sparse_data(Tensor permute, Tensor lengths, Tensor values, Tensor? weights=None, "
+          "SymInt? permuted_lengths_sum=None) -> (Tensor, Tensor, Tensor?)", &permute_2D_sparse_data);
+    m.def("permute_1D_sparse_data(Tensor permute, Tensor lengths, Tensor values, Tensor? weights=None, "
+          "SymInt? permuted_lengths_sum=None) -> (Tensor, Tensor, Tensor?)", &permute_1D_sparse_data);
+    m.def("asynchronous_complete_cumsum(Tensor offset) -> Tensor", &asynchronous_complete_cumsum);
+    m.def("jagged_to_padded_dense.v1(Tensor values, Tensor[] offsets, int max_lengths, float padding_value) -> Tensor",
+          &jagged_to_padded_dense_v1);
+    m.def("jagged_to_padded_dense.v2(Tensor values, Tensor[] offsets, int[] max_lengths, float padding_value) -> Tensor",
+          &jagged_to_padded_dense_v2);
+    m.def("dense_to_jagged(Tensor dense, Tensor[] offsets, SymInt? total_L=None) -> (Tensor, Tensor[])", &dense_to_jagged);
+}
+
 }  // namespace recsdk_torch
 
 #ifndef RECSDK_NO_FBGEMM_NS
-TORCH_LIBRARY_FRAGMENT(fbgemm, m) { recsdk_torch::define_and_implement(m); }
+TORCH_LIBRARY_FRAGMENT(fbgemm, m)
+{
+    recsdk_torch::define_and_implement(m);
+    recsdk_torch::define_and_implement_kjt(m);
+}
+#endif
+
+// the namespace the reference defines the jagged-batch utilities in
+#ifndef RECSDK_NO_MXREC_NS
+TORCH_LIBRARY(mxrec, m) { recsdk_torch::define_and_implement_kjt(m); }
 #endif
 
 TORCH_LIBRARY(recsdk, m)
@@ -545,6 +731,7 @@ TORCH_LIBRARY(recsdk, m)
         .def("size", &recsdk_torch::IdsMapper::size)
         .def_static("parallel_ids2indices_unique_out", &recsdk_torch::IdsMapper::ParallelUniqueHashOut);
     m.def("block_bucketize_sparse_features", &recsdk_torch::block_bucketize_sparse_features);
+    recsdk_torch::define_and_implement_kjt(m);
 }
 
 // The reference's own registration names (hybrid_torchrec/src/bind_torch_lib.cpp:9-19): callers that say

@@ -353,3 +353,103 @@ def bucketize(lengths, indices, num_features: int, world: int, do_unique: bool =
                                int(return_count), _ptr(new_lengths), _ptr(new_indices), _ptr(perm), _ptr(counts),
                                _ptr(num_out), _ptr(ws), ws.numel(), _stream()), "recsdk_bucketize")
     return new_lengths, new_indices, perm, counts, num_out
+
+
+# --------------------------------------------------------------------------- jagged-batch utilities
+def asynchronous_complete_cumsum(offset: torch.Tensor) -> torch.Tensor:
+    """[n] -> [n + 1]: 0 followed by the running sums (asynchronous_complete_cumsum.cpp:18-25)."""
+    lib = _lib.load()
+    x = offset.to(torch.int64).contiguous()
+    n = x.numel()
+    out = torch.empty(n + 1, dtype=torch.int64, device=x.device)
+    ws = _workspace(lib.recsdk_complete_cumsum_workspace_bytes(n), x.device)
+    check(lib.recsdk_complete_cumsum(_ptr(x), n, _ptr(out), _ptr(ws), ws.numel(), _stream()), "recsdk_complete_cumsum")
+    return out.to(offset.dtype)
+
+
+def permute_2D_sparse_data(permute: torch.Tensor, lengths: torch.Tensor, values: torch.Tensor,
+                           weights: Optional[torch.Tensor] = None, permuted_lengths_sum: Optional[int] = None):
+    """(permuted_lengths [T', B], permuted_values, permuted_weights or None) -- permute2d_sparse_data.cpp:21-48.
+    Without ``permuted_lengths_sum`` the output size is read back from the device (one synchronisation), as the
+    reference does."""
+    lib = _lib.load()
+    if lengths.dim() != 2:
+        raise RuntimeError("lengths must be 2-D [T, B]")
+    if values.element_size() not in (4, 8):
+        raise RuntimeError("values must have 4- or 8-byte elements")
+    dev = values.device
+    perm = permute.to(torch.int64).contiguous()
+    len64 = lengths.to(torch.int64).contiguous()
+    vals = values.contiguous()
+    T_in, B = len64.shape
+    T_out = perm.numel()
+    w = None
+    if weights is not None:
+        _chk(weights, torch.float32, "weights")
+        if weights.numel() != vals.numel():
+            raise RuntimeError(f"weights and values length mismatch: {weights.numel()} vs {vals.numel()}")
+        w = weights
+    out_len = torch.empty((T_out, B), dtype=torch.int64, device=dev)
+    status = new_status(dev)
+    ws = _workspace(lib.recsdk_permute_sparse_workspace_bytes(T_in, T_out), dev)
+    if permuted_lengths_sum is not None and permuted_lengths_sum > 0:
+        total = int(permuted_lengths_sum)
+    else:
+        total = int(len64.index_select(0, perm).sum().item()) if T_out and B else 0
+    out_vals = torch.empty(total, dtype=vals.dtype, device=dev)
+    out_w = torch.empty(total, dtype=torch.float32, device=dev) if w is not None else None
+    check(lib.recsdk_permute_2d_sparse_data(_ptr(perm), T_out, _ptr(len64), T_in, B, _ptr(vals), vals.element_size(),
+                                            _ptr(w), _ptr(out_len), _ptr(out_vals), _ptr(out_w), total, None,
+                                            _ptr(status), _ptr(ws), ws.numel(), _stream()),
+          "recsdk_permute_2d_sparse_data")
+    raise_on_status(status, "permute_2D_sparse_data")
+    return out_len.to(lengths.dtype), out_vals, out_w
+
+
+def permute_1D_sparse_data(permute: torch.Tensor, lengths: torch.Tensor, values: torch.Tensor,
+                           weights: Optional[torch.Tensor] = None, permuted_lengths_sum: Optional[int] = None):
+    """permute1d_sparse_data.cpp:57-93: the 2-D call on lengths viewed as [L, 1]."""
+    if permute.dim() != 1 or lengths.dim() != 1 or values.dim() != 1:
+        raise RuntimeError("permute, lengths and values must be 1-D")
+    if permuted_lengths_sum is not None and permuted_lengths_sum < 0:
+        raise RuntimeError(f"permuted_lengths_sum must be non-negative, got {permuted_lengths_sum}")
+    out_len, out_vals, out_w = permute_2D_sparse_data(permute, lengths.view(-1, 1), values, weights, permuted_lengths_sum)
+    return out_len.view(-1), out_vals, out_w
+
+
+def jagged_to_padded_dense(values: torch.Tensor, offsets, max_lengths, padding_value: float = 0.0) -> torch.Tensor:
+    """values [N, D], offsets = [tensor [B + 1]] -> [B, max_length, D] (jagged_to_padded_dense.cpp v1 / v2)."""
+    lib = _lib.load()
+    if not isinstance(offsets, (list, tuple)) or len(offsets) != 1:
+        raise RuntimeError(f"offsets must contain exactly 1 tensor, but got {len(offsets)} tensors")
+    if isinstance(max_lengths, (list, tuple)):
+        if len(max_lengths) != 1:
+            raise RuntimeError(f"max_lengths must contain exactly one element, but got {len(max_lengths)}")
+        max_lengths = max_lengths[0]
+    if max_lengths <= 0:
+        raise RuntimeError(f"max_lengths must be positive, but got {max_lengths}")
+    _chk(values, torch.float32, "values")
+    if values.dim() != 2:
+        raise RuntimeError("values must be 2-D")
+    offs = offsets[0].to(torch.int64).contiguous()
+    B, D = offs.numel() - 1, values.shape[1]
+    out = torch.empty((B, int(max_lengths), D), dtype=torch.float32, device=values.device)
+    check(lib.recsdk_jagged_to_padded_dense(_ptr(values), _ptr(offs), B, D, int(max_lengths), float(padding_value),
+                                            _ptr(out), _stream()), "recsdk_jagged_to_padded_dense")
+    return out
+
+
+def dense_to_jagged(dense: torch.Tensor, offsets, total_L: Optional[int] = None):
+    """dense [B, L, D], offsets = [tensor [B + 1]] -> (values [total_L, D], offsets) (dense_to_jagged.cpp); also the
+    backward of jagged_to_padded_dense."""
+    lib = _lib.load()
+    if not isinstance(offsets, (list, tuple)) or len(offsets) != 1:
+        raise RuntimeError(f"offsets must contain exactly 1 tensor, but got {len(offsets)} tensors")
+    _chk(dense, torch.float32, "dense")
+    offs = offsets[0].to(torch.int64).contiguous()
+    B, L, D = dense.shape
+    if total_L is None:
+        total_L = int(offs[-1].item())
+    values = torch.empty((total_L, D), dtype=torch.float32, device=dense.device)
+    check(lib.recsdk_dense_to_jagged(_ptr(dense), _ptr(offs), B, D, L, _ptr(values), _stream()), "recsdk_dense_to_jagged")
+    return values, offsets
