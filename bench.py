@@ -643,6 +643,26 @@ def run_ops(args):
     c = cpu_ms(lambda i: port.restore(uq_np, inv_np, np.array([0, u], np.int64), np.array([0, ids_np.size], np.int64)))
     entry("restore", ids_np.size, "ids", g, c, "port", ids_np.size * 24)
 
+    # ---- jagged-batch utilities on the configs[1] batch shape: 26 x 65536 lengths, 1.7 M values
+    kl = np.ones((N_TABLES, BATCH), np.int64)
+    kp = rng.permutation(N_TABLES).astype(np.int32)
+    d_kl, d_kp = torch.from_numpy(kl).to(dev), torch.from_numpy(kp).to(dev)
+    g = gpu_ms(lambda i: ops.permute_2D_sparse_data(d_kp, d_kl, ids, None, ids.numel()))
+    c = cpu_ms(lambda i: port.permute_2D_sparse_data(kp, kl, ids_np))
+    entry("permute_2D_sparse_data", ids_np.size, "values", g, c, "port", ids_np.size * 8 * 4)
+    flat_l = d_kl.view(-1)
+    g = gpu_ms(lambda i: ops.asynchronous_complete_cumsum(flat_l))
+    c = cpu_ms(lambda i: port.asynchronous_complete_cumsum(kl.reshape(-1)))
+    entry("asynchronous_complete_cumsum", kl.size, "lengths", g, c, "port", kl.size * 16)
+    jl = rng.integers(0, 101, 16384)
+    jo = np.concatenate([[0], np.cumsum(jl)]).astype(np.int64)
+    jv = torch.randn(int(jo[-1]), 64, device=dev)
+    d_jo = torch.from_numpy(jo).to(dev)
+    g = gpu_ms(lambda i: ops.jagged_to_padded_dense(jv, [d_jo], 100, 0.0))
+    jv_np = jv.cpu().numpy()
+    c = cpu_ms(lambda i: port.jagged_to_padded_dense(jv_np, jo, 100, 0.0))
+    entry("jagged_to_padded_dense", int(jo[-1]), "rows", g, c, "port", int(jo[-1]) * 256 + 16384 * 100 * 256)
+
     emit({"workload": "ops", "n_gpus": 1, "peak_gbs": peak, "peak_kind": peak_kind, "cores": os.cpu_count(),
           "data": "synthetic", "ops": res})
 
