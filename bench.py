@@ -394,7 +394,7 @@ def run_ours(args):
         upd_bytes = U * (4 * DIM * 2 * (1 + S) + 12) + (N - n_long) * (4 * DIM + 4) + n_chunks * 4 * DIM
         upd_ms_avg = sum(upd_ms) / len(upd_ms)
         achieved = upd_bytes / (upd_ms_avg * 1e-3) / 1e9
-        # whole step, SURVEY formula: dedup + fwd + bwd
+        # whole step: dedup (16N + 8U) + forward (N(8+4D) + 8(N+1) + 4D N) + backward (4D N + 8N + 8U + U 4D 2(1+S))
         step_bytes = (16 * N + 8 * U) + (N * (8 + 4 * DIM) + 8 * (N + 1) + 4 * DIM * N) + \
                      (4 * DIM * N + 8 * N + 8 * U + U * 4 * DIM * 2 * (1 + S))
         bits = module.total_hash_size_bits
