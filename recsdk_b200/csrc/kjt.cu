@@ -164,10 +164,11 @@ template <bool TO_DENSE>
 static __global__ void __launch_bounds__(256) jagged_dense_kernel(float* __restrict__ values,
                                                                   const int64_t* __restrict__ offsets, int64_t B,
                                                                   int32_t D, int64_t L, float padding,
-                                                                  float* __restrict__ dense, int vec)
+                                                                  float* __restrict__ dense, int vec, int lanes)
 {
-    const int lanes = 32;
-    const int lane = threadIdx.x & 31;
+    // `lanes` (a power of two <= 32) threads share one row: as many as it has 128-bit words, so narrow rows do
+    // not leave most of a warp idle
+    const int lane = threadIdx.x & (lanes - 1);
     const int64_t rows = B * L;
     for (int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / lanes; r < rows;
          r += static_cast<int64_t>(gridDim.x) * blockDim.x / lanes) {
@@ -188,7 +189,12 @@ static __global__ void __launch_bounds__(256) jagged_dense_kernel(float* __restr
                 }
             }
         } else if (TO_DENSE) {
-            for (int c = lane; c < D; c += lanes) drow[c] = padding;
+            if (vec) {
+                const float4 pad = make_float4(padding, padding, padding, padding);
+                for (int c = lane; c < (D >> 2); c += lanes) st_f4_stream(drow + 4 * c, pad);
+            } else {
+                for (int c = lane; c < D; c += lanes) drow[c] = padding;
+            }
         }
     }
 }
@@ -210,6 +216,14 @@ static __global__ void __launch_bounds__(256) jagged_tail_zero_kernel(float* __r
 }  // namespace recsdk
 
 using namespace recsdk;
+
+static int row_lanes(int32_t D, int vec)
+{
+    const int words = vec ? (D >> 2) : D;
+    int lanes = 1;
+    while (lanes < 32 && lanes < words) lanes <<= 1;
+    return lanes;
+}
 
 extern "C" size_t recsdk_complete_cumsum_workspace_bytes(int64_t n)
 {
@@ -284,8 +298,9 @@ extern "C" int recsdk_jagged_to_padded_dense(const float* values, const int64_t*
     if (B == 0) return RECSDK_OK;
     if (!offsets || !dense) return RECSDK_ERR_INVALID_ARG;
     const int vec = (aligned16(values) && aligned16(dense) && (D & 3) == 0) ? 1 : 0;
-    jagged_dense_kernel<true><<<grid_for(B * max_length, 8, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        const_cast<float*>(values), offsets, B, D, max_length, padding_value, dense, vec);
+    const int lanes = row_lanes(D, vec);
+    jagged_dense_kernel<true><<<grid_for(B * max_length, 256 / lanes, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        const_cast<float*>(values), offsets, B, D, max_length, padding_value, dense, vec, lanes);
     RECSDK_CUDA_CHECK_LAUNCH();
     return RECSDK_OK;
 }
@@ -298,8 +313,9 @@ extern "C" int recsdk_dense_to_jagged(const float* dense, const int64_t* offsets
     if (!offsets || !dense || !values) return RECSDK_ERR_INVALID_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int vec = (aligned16(values) && aligned16(dense) && (D & 3) == 0) ? 1 : 0;
-    jagged_dense_kernel<false><<<grid_for(B * max_length, 8, 8), 256, 0, st>>>(values, offsets, B, D, max_length, 0.f,
-                                                                              const_cast<float*>(dense), vec);
+    const int lanes = row_lanes(D, vec);
+    jagged_dense_kernel<false><<<grid_for(B * max_length, 256 / lanes, 8), 256, 0, st>>>(
+        values, offsets, B, D, max_length, 0.f, const_cast<float*>(dense), vec, lanes);
     jagged_tail_zero_kernel<<<grid_for(B, 8, 8), 256, 0, st>>>(values, offsets, B, D, max_length);
     RECSDK_CUDA_CHECK_LAUNCH();
     return RECSDK_OK;
