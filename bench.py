@@ -154,7 +154,8 @@ def run_ours(args):
 
     dedup = world > 1 and args.exchange == "dedup"
     opt_kw = dict(optimizer=EmbOptimType.ADAM, pooling_mode=PoolingMode.SUM, learning_rate=LR, eps=EPS, beta1=BETA1,
-                  beta2=BETA2, device=dev, weights_init=(-0.01, 0.01), seed=SEED + rank)
+                  beta2=BETA2, device=dev, weights_init=(-0.01, 0.01), seed=SEED + rank,
+                  plan_ahead=not args.no_plan_ahead)
     if dedup:
         # the sample owners fetch the DISTINCT rows their samples need and pool locally; gradients return summed
         # per distinct row: ids, rows and gradient rows cross in NCCL all-to-alls, ~5x fewer bytes than pooled rows
@@ -249,7 +250,7 @@ def run_ours(args):
             ev_pairs.append(evs)
             phase_marks.append(marks)
         if fused:
-            module.forward_into(idx, offs, out_shards=fx.out_shards)
+            module.forward_into(idx, offs, out_shards=fx.out_shards, plan_grad_shards=fx.grad_shards)
             mark()
             fx.fence()  # every owner's stores have landed: fx.pooled.local is complete; the dense part runs here
             fx.fence()  # ... and has written fx.grads.local on every rank
@@ -778,6 +779,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="step", choices=["step", "ops"],
                     help="step: the benchmark (default).  ops: per-operator measurements of the other entry points")
+    ap.add_argument("--no-plan-ahead", action="store_true",
+                    help="do not overlap the backward's index work (sort of the row keys, runs, per-row records) "
+                         "with the forward on a side stream")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--zipf-alpha", type=float, default=ALPHA,
                     help="1-GPU experiments only: skew of the ids (the benchmark's is 1.1; not the benchmark otherwise)")

@@ -169,6 +169,13 @@ RECSDK_API int recsdk_unique_sorted_static(const int64_t* ids, int64_t n, int ke
  * asynchronous copies (rows of 128..1024 floats, 16-byte aligned tables; other shapes ignore the flag).  Same
  * results bit for bit; measured slightly slower than the default on the benchmark workload, so it is opt-in. */
 #define RECSDK_BWD_STAGED_UPDATE 1
+/* PLAN_ONLY / APPLY_ONLY split one call in two.  The plan (position -> row key, sort, runs, per-row records) reads
+ * the indices and needs only the LAYOUT of the gradient (total_D / D_offsets or grad_shards), so it can be enqueued
+ * on another stream while the forward of the same batch runs; grad_output may be NULL in that call.  The apply call
+ * (chunk sums, row update) takes the same arguments plus the gradient and the same workspace, untouched in
+ * between, and must be ordered after the plan call (an event).  Neither flag: both phases, as before. */
+#define RECSDK_BWD_PLAN_ONLY 2
+#define RECSDK_BWD_APPLY_ONLY 4
 typedef struct {
     const float* grad_output; /* [B,total_D]  (NONE: [N,max_D]) */
     float* dev_weights;

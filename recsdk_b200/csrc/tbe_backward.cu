@@ -163,6 +163,17 @@ struct RunStartOut {
 };
 
 // ---------------------------------------------------------------------------- gradient rows
+// Where a gradient row lies, independent of the address of the gradient buffer (so that the plan can be made
+// before the gradient exists): element offset inside its buffer in the low 56 bits, shard number above.
+constexpr int kLocShardShift = 56;
+__device__ __forceinline__ int64_t grad_row_loc(const BwdParams& p, uint32_t v);
+__device__ __forceinline__ const float* grad_row_at(const BwdParams& p, int64_t loc)
+{
+    const int64_t off = loc & ((int64_t(1) << kLocShardShift) - 1);
+    if (p.sh.num_shards == 0) return p.grad + off;
+    return shard_base(p.sh, loc >> kLocShardShift) + off;
+}
+
 struct GradRow {
     const float* ptr;
     float scale;  // MEAN: 1/len
@@ -189,6 +200,17 @@ __device__ __forceinline__ GradRow grad_row_of(const BwdParams& p, uint32_t v)
         }
     }
     return g;
+}
+
+__device__ __forceinline__ int64_t grad_row_loc(const BwdParams& p, uint32_t v)
+{
+    if (p.mode == RECSDK_POOL_NONE) return static_cast<int64_t>(v) * p.max_D;
+    const uint32_t f = v >> p.bshift;
+    const uint32_t b = v & ((1u << p.bshift) - 1u);
+    if (p.sh.num_shards == 0) return static_cast<int64_t>(b) * p.total_D + p.dofs[f];
+    const int64_t s = static_cast<int64_t>(b) / p.sh.shard_B;
+    return (s << kLocShardShift) |
+           ((static_cast<int64_t>(b) - s * p.sh.shard_B) * p.sh.row_stride + p.sh.col_offsets[f]);
 }
 
 __device__ __forceinline__ float prep_grad(const BwdParams& p, float g, float scale)
@@ -399,7 +421,7 @@ __device__ __forceinline__ void opt_update_vec(const BwdParams& p, float g, floa
 // a single 32-byte read instead of a chain of five dependent loads.
 struct __align__(16) RunMeta {
     int64_t row_off;     // element offset of the row in dev_weights; -1: out of range, skip
-    int64_t g0_ptr;      // address of the run's first gradient row
+    int64_t g0_loc;      // location (grad_row_loc) of the run's first gradient row
     int32_t rs, len;     // sorted positions [rs, rs + len)
     int32_t D;           // row width in elements; kMetaVecBit set when the 128-bit path applies
     int32_t chunk_base;  // first slot of the run in the partial buffer (len > kChunk), else -1
@@ -432,7 +454,7 @@ __global__ void __launch_bounds__(256) run_meta_kernel(BwdParams p, const KeyT* 
             set_status(p.status, RECSDK_ERR_INDEX_RANGE, row, m.row_off);
             m.row_off = -1;
         }
-        m.g0_ptr = reinterpret_cast<int64_t>(grad_row_of(p, v0).ptr);
+        m.g0_loc = grad_row_loc(p, v0);
         m.rs = rs;
         m.len = len;
         m.D = D | (vec_ok_for(p, wofs, D, f) ? kMetaVecBit : 0);
@@ -506,6 +528,7 @@ __device__ __forceinline__ void update_body(const BwdParams& p, const RunMeta& m
     const int64_t row_off = m.row_off;
     // MEAN pooling scales every gradient row by its bag length: take the general path for all rows
     const bool first_direct = !chunked && p.mode != RECSDK_POOL_MEAN;
+    const float* g0_row = grad_row_at(p, m.g0_loc);
     for (int cb = 0; cb < nvec; cb += G * K) {
         typename V::T acc[K], w[K], m1[K], m2[K], g0[K];
         // all row loads of a short run are independent: issue them together
@@ -518,7 +541,7 @@ __device__ __forceinline__ void update_body(const BwdParams& p, const RunMeta& m
                 w[k] = V::ld(p.w + row_off + V::W * col);
                 if (OPT != RECSDK_OPT_SGD) m1[k] = V::ld(p.m1 + row_off + V::W * col);
                 if (OPT == RECSDK_OPT_ADAM) m2[k] = V::ld(p.m2 + row_off + V::W * col);
-                if (first_direct) g0[k] = V::ld_stream(reinterpret_cast<const float*>(m.g0_ptr) + V::W * col);
+                if (first_direct) g0[k] = V::ld_stream(g0_row + V::W * col);
             }
         }
         row_gradient<V, G, K>(p, m, cb, lane, nvec, first_direct, g0, acc);
@@ -582,7 +605,7 @@ __global__ void __launch_bounds__(256, 3) update_staged_kernel(BwdParams p, cons
     // producer side, run by lane `s` alone: publish the record of the row that stage s will hold and start its copies
     auto arm = [&](int s, int4 lo, int4 hi) {
         const int64_t row_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.y)) << 32) | static_cast<uint32_t>(lo.x);
-        const int64_t g0_ptr = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
+        const int64_t g0_loc = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
         const bool staged = row_off >= 0 && (hi.z & kMetaVecBit) != 0;
         if (staged) hi.z |= kMetaStagedBit;
         smeta[2 * s] = lo;
@@ -595,7 +618,7 @@ __global__ void __launch_bounds__(256, 3) update_staged_kernel(BwdParams p, cons
         bulk_g2s(st, p.w + row_off, rb, &bars[s]);
         if (OPT != RECSDK_OPT_SGD) bulk_g2s(st + row_bytes_max, p.m1 + row_off, rb, &bars[s]);
         if (OPT == RECSDK_OPT_ADAM) bulk_g2s(st + 2 * row_bytes_max, p.m2 + row_off, rb, &bars[s]);
-        if (direct) bulk_g2s(st + (NARR - 1) * row_bytes_max, reinterpret_cast<const float*>(g0_ptr), rb, &bars[s]);
+        if (direct) bulk_g2s(st + (NARR - 1) * row_bytes_max, grad_row_at(p, g0_loc), rb, &bars[s]);
     };
 
     // prologue: lane s fills stage s with the warp's s-th row
@@ -619,7 +642,7 @@ __global__ void __launch_bounds__(256, 3) update_staged_kernel(BwdParams p, cons
         const int4 lo = smeta[2 * s], hi = smeta[2 * s + 1];
         RunMeta m;
         m.row_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.y)) << 32) | static_cast<uint32_t>(lo.x);
-        m.g0_ptr = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
+        m.g0_loc = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
         m.rs = hi.x;
         m.len = hi.y;
         m.D = hi.z;
@@ -698,7 +721,7 @@ __global__ void __launch_bounds__(256) update_kernel(BwdParams p, const RunMeta*
         }
         RunMeta m;
         m.row_off = (static_cast<int64_t>(static_cast<uint32_t>(lo.y)) << 32) | static_cast<uint32_t>(lo.x);
-        m.g0_ptr = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
+        m.g0_loc = (static_cast<int64_t>(static_cast<uint32_t>(lo.w)) << 32) | static_cast<uint32_t>(lo.z);
         m.rs = hi.x;
         m.len = hi.y;
         m.D = hi.z;
@@ -846,27 +869,43 @@ static int run_backward(const recsdk_tbe_backward_args* a, BwdParams p, const Bw
     const int64_t N = a->N;
     KeyT* ka = static_cast<KeyT*>(ws.keys_a);
     KeyT* kb = static_cast<KeyT*>(ws.keys_b);
-    cudaMemsetAsync(ws.counters, 0, 8 * sizeof(int64_t), st);  // {U, chunks, indices in chunked runs, ...}
-    // 1. expand; it also fills the histogram of the first sort pass
-    const RadixFusedPlan plan = radix_fused_begin(N, key_bits, ws.sort_scratch, st);
-    if (a->pooling_mode == RECSDK_POOL_NONE)
-        expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, ka, ws.vals_a, plan.first);
-    else
-        expand_pooled_kernel<KeyT><<<grid_for(a->T * a->B, 8 * 32), 256, 0, st>>>(p, ka, ws.vals_a, plan.first);
-    // 2. sort: per pass a scan and a scatter that fills the next pass's histogram
-    const int which = radix_sort_pairs_fused<KeyT>(plan, ka, ws.vals_a, kb, ws.vals_b, N, ws.sort_scratch, st);
+    const bool do_plan = (a->flags & RECSDK_BWD_APPLY_ONLY) == 0;
+    const bool do_apply = (a->flags & RECSDK_BWD_PLAN_ONLY) == 0;
+    // where the sorted tags end up depends only on the number of passes
+    int passes, bits;
+    radix_plan(key_bits, &passes, &bits);
+    const int which = (N > 1 ? passes : 0) & 1;
     const KeyT* keys = which ? kb : ka;
     p.vals = which ? ws.vals_b : ws.vals_a;
-    // 3. runs
-    device_scan_fn<true>(HeadFlagIn<KeyT>{keys}, RunStartOut{ws.run_start, ws.counters, N}, N, ws.scan_scratch, nullptr,
-                         st);
     p.run_start = ws.run_start;
     p.counters = ws.counters;
-    const int vec_per_row = (a->max_D + 3) / 4;
-    // 4. per-run records (+ chunk descriptors of long runs), chunk sums
     p.chunk_desc = ws.desc;
     p.partial = ws.partial;
-    run_meta_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, keys, ws.counters, ws.meta, ws.desc);
+    const int vec_per_row = (a->max_D + 3) / 4;
+    if (do_plan) {
+        // The plan needs the indices and the LAYOUT of the gradient, not the gradient: it can run ahead, on
+        // another stream, while the forward of the same batch (or the dense part) runs.
+        cudaMemsetAsync(ws.counters, 0, 8 * sizeof(int64_t), st);  // {U, chunks, indices in chunked runs, ...}
+        // 1. expand; it also fills the histogram of the first sort pass
+        const RadixFusedPlan plan = radix_fused_begin(N, key_bits, ws.sort_scratch, st);
+        if (a->pooling_mode == RECSDK_POOL_NONE)
+            expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, ka, ws.vals_a, plan.first);
+        else
+            expand_pooled_kernel<KeyT><<<grid_for(a->T * a->B, 8 * 32), 256, 0, st>>>(p, ka, ws.vals_a, plan.first);
+        // 2. sort: per pass a scan and a scatter that fills the next pass's histogram
+        const int got = radix_sort_pairs_fused<KeyT>(plan, ka, ws.vals_a, kb, ws.vals_b, N, ws.sort_scratch, st);
+        if (got != which) return RECSDK_ERR_CUDA;  // cannot happen: both follow radix_plan
+        // 3. runs
+        device_scan_fn<true>(HeadFlagIn<KeyT>{keys}, RunStartOut{ws.run_start, ws.counters, N}, N, ws.scan_scratch,
+                             nullptr, st);
+        // 4. per-run records (+ chunk descriptors of long runs)
+        run_meta_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, keys, ws.counters, ws.meta, ws.desc);
+    }
+    if (!do_apply) {
+        RECSDK_CUDA_CHECK_LAUNCH();
+        return RECSDK_OK;
+    }
+    // 4b. chunk sums
     if (a->reduce_chunk > 0) {
 #define CALL_PARTIAL(G, K) launch_partial<G, K>(p, N, st)
         RECSDK_DISPATCH_GK(vec_per_row, CALL_PARTIAL);
@@ -914,8 +953,10 @@ extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stre
     if (!a->dev_weights || !a->weights_offsets || !a->D_offsets || !a->indices || !a->offsets)
         return RECSDK_ERR_INVALID_ARG;
     const recsdk_sample_shards& sh = a->grad_shards;
+    const bool plan_only = (a->flags & RECSDK_BWD_PLAN_ONLY) != 0;
+    if ((a->flags & RECSDK_BWD_PLAN_ONLY) && (a->flags & RECSDK_BWD_APPLY_ONLY)) return RECSDK_ERR_INVALID_ARG;
     if (sh.num_shards == 0) {
-        if (!a->grad_output) return RECSDK_ERR_INVALID_ARG;
+        if (!a->grad_output && !plan_only) return RECSDK_ERR_INVALID_ARG;
     } else {
         if (!sample_shards_valid(sh, a->B) || a->pooling_mode == RECSDK_POOL_NONE) return RECSDK_ERR_INVALID_ARG;
     }
@@ -967,7 +1008,9 @@ extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stre
     p.status = a->dev_status;
     bool grad_aligned = true;
     if (sh.num_shards == 0) {
-        grad_aligned = aligned16(a->grad_output);
+        // a plan made before the gradient exists assumes a 16-byte aligned gradient; the apply call checks it
+        grad_aligned = (plan_only && !a->grad_output) ? true : aligned16(a->grad_output);
+        if ((a->flags & RECSDK_BWD_APPLY_ONLY) && !grad_aligned) return RECSDK_ERR_INVALID_ARG;
     } else {
         for (int s = 0; s < sh.num_shards; ++s) grad_aligned = grad_aligned && aligned16(sh.ptrs[s]);
     }

@@ -86,56 +86,22 @@ __device__ __forceinline__ unsigned group_mask()
 
 constexpr int kFwdUnroll = 8;
 
-// Offsets of one group of G consecutive bags, one bag per lane.
-struct GroupHead {
-    int64_t start_l;  // first index position of this lane's bag (INT64_MAX past the last bag)
-    int64_t end_all;  // one past the last index position of the group
-};
-
-__device__ __forceinline__ GroupHead load_group_head(const FwdParams& p, int64_t bag0, int64_t num_bags, int gl, int G)
-{
-    GroupHead h;
-    h.start_l = INT64_MAX;
-    h.end_all = 0;
-    if (bag0 < num_bags) {
-        const int64_t rem = num_bags - bag0;
-        const int nb = static_cast<int>(rem < G ? rem : G);
-        if (gl < nb) h.start_l = __ldg(p.offs + bag0 + gl);
-        h.end_all = __ldg(p.offs + bag0 + nb);
-    }
-    return h;
-}
-
-// The kernel is a three-stage software pipeline over the groups a lane group owns: while the rows of group i
-// are gathered, the first G ids of group i+1 and the offsets of group i+2 are already in flight, so only the row
-// loads themselves (kFwdUnroll at a time) sit on the critical path.
 template <int G, int K>
 __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
 {
     const int gl = threadIdx.x % G;
     const unsigned gmask = group_mask<G>();
     const int64_t num_bags = p.T * p.B;
-    const int64_t bag_step = static_cast<int64_t>(gridDim.x) * blockDim.x;  // groups_total * G
+    const int64_t groups_total = static_cast<int64_t>(gridDim.x) * blockDim.x / G;
     const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / G;
     const int max_nvec = p.max_D >> 2;
 
-    int64_t bag0 = gid * G;
-    GroupHead hA = load_group_head(p, bag0, num_bags, gl, G);
-    GroupHead hB = load_group_head(p, bag0 + bag_step, num_bags, gl, G);
-    // ids of the first G positions of group A
-    int64_t id_next = 0;
-    {
-        const int64_t p0 = __shfl_sync(gmask, hA.start_l, 0, G);
-        if (bag0 < num_bags && p0 + gl < hA.end_all) id_next = __ldg(p.idx + p0 + gl);
-    }
-
-    for (; bag0 < num_bags; bag0 += bag_step) {
-        const GroupHead hC = load_group_head(p, bag0 + 2 * bag_step, num_bags, gl, G);
+    for (int64_t bag0 = gid * G; bag0 < num_bags; bag0 += groups_total * G) {
         const int nb = static_cast<int>((num_bags - bag0) < G ? (num_bags - bag0) : G);
         const bool valid = gl < nb;
         const int64_t my_bag = bag0 + gl;
-        const int64_t start_l = hA.start_l;
-        const int64_t end_all = hA.end_all;
+        const int64_t start_l = valid ? p.offs[my_bag] : INT64_MAX;
+        const int64_t end_all = p.offs[bag0 + nb];
         const int64_t t_l = valid ? my_bag / p.B : 0;
         const int64_t b_l = my_bag - t_l * p.B;
         const int32_t d0_l = p.dofs[t_l];
@@ -144,33 +110,20 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
         const int64_t optr_l = valid ? reinterpret_cast<int64_t>(out_row_ptr(p, t_l, b_l, d0_l)) : 0;
         const bool ok_l = !valid || ((((wofs_l | D_l) & 3) == 0) && ((optr_l & 15) == 0));
         const bool all_ok = __all_sync(gmask, ok_l) != 0;  // executed by every lane of the group
-        const int64_t p0 = __shfl_sync(gmask, start_l, 0, G);
-        const int64_t p0_B = __shfl_sync(gmask, hB.start_l, 0, G);
-        const bool have_B = bag0 + bag_step < num_bags;
-        // ids of the first chunk of the next group (used when this group's walk does not fetch them itself)
-        auto fetch_next_group = [&]() -> int64_t {
-            return (have_B && p0_B + gl < hB.end_all) ? __ldg(p.idx + p0_B + gl) : 0;
-        };
-
         if (!(p.base_aligned && all_ok)) {
             for (int j = 0; j < nb; ++j) forward_bag_scalar<G>(p, gl, bag0 + j);
-            id_next = fetch_next_group();
-            hA = hB;
-            hB = hC;
             continue;
         }
+        const int64_t p0 = __shfl_sync(gmask, start_l, 0, G);
 
         // flush bag j: write `acc` (scaled for MEAN) or zeros
         auto flush = [&](int j, const float4 (&acc)[K], bool has_rows, int cb) {
             float* optr = reinterpret_cast<float*>(__shfl_sync(gmask, optr_l, j, G));
             const int nvec = __shfl_sync(gmask, D_l, j, G) >> 2;
-            float mean = 1.0f;
-            if (p.mode == RECSDK_POOL_MEAN) {
-                const int64_t sj = __shfl_sync(gmask, start_l, j, G);
-                const int64_t nx = __shfl_sync(gmask, start_l, (j + 1) & (G - 1), G);
-                const int64_t ej = (j + 1 < nb) ? nx : end_all;
-                mean = __fdiv_rn(1.0f, static_cast<float>(ej - sj));
-            }
+            const int64_t sj = __shfl_sync(gmask, start_l, j, G);
+            const int64_t nx = __shfl_sync(gmask, start_l, (j + 1) & (G - 1), G);
+            const int64_t ej = (j + 1 < nb) ? nx : end_all;
+            const float mean = __fdiv_rn(1.0f, static_cast<float>(ej - sj));
 #pragma unroll
             for (int k = 0; k < K; ++k) {
                 const int c = cb + gl + k * G;
@@ -182,9 +135,7 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
             }
         };
 
-        bool next_fetched = false;  // id_next already holds the first chunk of the next group
         for (int cb = 0; cb < max_nvec; cb += G * K) {
-            const bool last_pass = cb + G * K >= max_nvec;
             int cur = 0;           // bag (0..nb) whose rows are being accumulated
             bool cur_has = false;  // accumulator holds at least one row
             float4 acc[K];
@@ -194,16 +145,7 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
             for (int64_t base = p0; base < end_all; base += G) {
                 const int64_t pos = base + gl;
                 const bool have = pos < end_all;
-                const int64_t id = id_next;
-                // the ids of the chunk that is walked after this one are requested now
-                if (base + G < end_all) {
-                    id_next = (pos + G < end_all) ? __ldg(p.idx + pos + G) : 0;
-                } else if (!last_pass) {
-                    id_next = (p0 + gl < end_all) ? __ldg(p.idx + p0 + gl) : 0;
-                } else {
-                    id_next = fetch_next_group();
-                    next_fetched = true;
-                }
+                const int64_t id = have ? p.idx[pos] : 0;
                 // bag of `pos`: the largest j with start_j <= pos (empty bags share a start; the last owns it)
                 int j_l = 0;
 #pragma unroll
@@ -216,7 +158,6 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
                 const int32_t D_j = __shfl_sync(gmask, D_l, j_l, G);
                 int64_t ro_l = wofs_j + id * D_j;
                 if (have && !row_ok(p, id, ro_l, D_j)) ro_l = -1;
-                const int jn_l = j_l | ((D_j >> 2) << 8);  // bag and row width (in float4) of this position
                 const int cnt = static_cast<int>((end_all - base) < G ? (end_all - base) : G);
 
                 constexpr int kUnroll = kFwdUnroll / K;  // independent row loads in flight per lane
@@ -228,9 +169,8 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
                         const int jj = jj0 + u;
                         const int src = jj < cnt ? jj : 0;
                         const int64_t ro = __shfl_sync(gmask, ro_l, src, G);
-                        const int jn = __shfl_sync(gmask, jn_l, src, G);
-                        bj[u] = jn & 0xff;
-                        const int nvec = jn >> 8;
+                        bj[u] = __shfl_sync(gmask, j_l, src, G);
+                        const int nvec = __shfl_sync(gmask, D_l, bj[u], G) >> 2;
 #pragma unroll
                         for (int k = 0; k < K; ++k) {
                             const int c = cb + gl + k * G;
@@ -263,9 +203,6 @@ __global__ void __launch_bounds__(256) tbe_forward_pooled_kernel(FwdParams p)
                 ++cur;
             }
         }
-        if (!next_fetched) id_next = fetch_next_group();  // a group of empty bags walks nothing
-        hA = hB;
-        hB = hC;
     }
 }
 

@@ -174,12 +174,17 @@ def tbe_backward(grad_output, dev_weights, momentum1, momentum2, weights_offsets
                  reduce_chunk: int = 64, gradient_clipping: bool = False, max_gradient: float = 0.0,
                  status: Optional[torch.Tensor] = None, bounds_check: bool = True,
                  workspace: Optional[torch.Tensor] = None, update_events=None,
-                 grad_shards: Optional[SampleShards] = None, staged_update: bool = False) -> None:
+                 grad_shards: Optional[SampleShards] = None, staged_update: bool = False,
+                 phase: str = "all") -> None:
     """``update_events``: optional (start, stop) torch.cuda.Event pair (created with enable_timing=True and
     recorded at least once before) that the library records around the row-update kernel.
-    ``grad_shards``: read the gradient rows from the sample owners' buffers (``grad_output`` is then None)."""
+    ``grad_shards``: read the gradient rows from the sample owners' buffers (``grad_output`` is then None).
+    ``phase``: "all", or "plan" (index work only; ``grad_output`` may be None; can run on another stream while the
+    forward runs) followed later by "apply" with the same arguments and workspace."""
     lib = _lib.load()
-    if grad_shards is None:
+    if phase not in ("all", "plan", "apply"):
+        raise ValueError(f"phase must be all / plan / apply, got {phase}")
+    if grad_shards is None and not (phase == "plan" and grad_output is None):
         _chk(grad_output, torch.float32, "grad_output")
     _chk(dev_weights, torch.float32, "dev_weights")
     if momentum1 is not None:
@@ -201,10 +206,13 @@ def tbe_backward(grad_output, dev_weights, momentum1, momentum2, weights_offsets
     B = (offsets.numel() - 1) // T
     N = indices.numel()
     wsz = lib.recsdk_tbe_backward_workspace_bytes(N, max_D)
+    if phase != "all" and (workspace is None or workspace.numel() < wsz):
+        raise RuntimeError("plan / apply calls need the caller's workspace (it carries the plan between them)")
     if workspace is None or workspace.numel() < wsz:
         workspace = _workspace(wsz, dev_weights.device)
     a = _lib.TbeBackwardArgs()
-    a.flags = 1 if staged_update else 0  # RECSDK_BWD_STAGED_UPDATE
+    # RECSDK_BWD_STAGED_UPDATE | RECSDK_BWD_PLAN_ONLY | RECSDK_BWD_APPLY_ONLY
+    a.flags = (1 if staged_update else 0) | {"all": 0, "plan": 2, "apply": 4}[phase]
     a.grad_output = _ptr(grad_output) if grad_shards is None else None
     if grad_shards is not None:
         grad_shards.fill(a.grad_shards)

@@ -87,7 +87,10 @@ class _LookupFunction(torch.autograd.Function):
                               unique_ids if unique_ids is not None else torch.empty(0),
                               unique_offsets if unique_offsets is not None else torch.empty(0),
                               unique_inverse if unique_inverse is not None else torch.empty(0))
-        return module._forward_impl(hash_indices if hash_indices is not None else indices, offsets)
+        use = hash_indices if hash_indices is not None else indices
+        if module.plan_ahead:  # the backward's index work overlaps this forward on a side stream
+            module.plan_backward_ahead(use, offsets, unique_ids, unique_offsets, unique_inverse)
+        return module._forward_impl(use, offsets)
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -125,9 +128,18 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         reduce_chunk: int = 64,
         bounds_check: bool = False,
         use_torch_ops: Optional[bool] = None,
+        plan_ahead: bool = False,
         **_ignored,
     ) -> None:
         super().__init__()
+        # plan_ahead: every forward also enqueues, on a side stream, the index work of the backward that will
+        # follow it (sort of the row keys, runs, per-row records); the backward then only sums and updates.
+        # Only for the forward -> backward alternation of training: a second forward before the backward
+        # overwrites the plan of the first.
+        self.plan_ahead = bool(plan_ahead)
+        self._plan_stream = None
+        self._plan_event = None
+        self._planned_for = None
         if weights_precision != SparseType.FP32 or output_dtype != SparseType.FP32:
             raise ValueError("only fp32 weights/output are supported")
         if not isinstance(optimizer, EmbOptimType):
@@ -219,13 +231,40 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
                                status=self._status if self.bounds_check else None, bounds_check=self.bounds_check,
                                out=out, out_shards=out_shards)
 
-    def _backward_impl(self, grad_output, indices, offsets, unique_ids, unique_offsets, unique_inverse, iteration,
-                       update_events=None, grad_shards=None) -> None:
-        a = self.optimizer_args
-        self._last_N = indices.numel()  # indices of the most recent backward (bandwidth accounting)
-        need = ops.tbe_backward_workspace_bytes(indices.numel(), self.max_D)
+    def _ensure_workspace(self, n_indices: int) -> None:
+        need = ops.tbe_backward_workspace_bytes(n_indices, self.max_D)
         if self._ws is None or self._ws.numel() < need:
             self._ws = torch.empty(need, dtype=torch.uint8, device=self.current_device)
+
+    def plan_backward_ahead(self, indices, offsets, unique_ids=None, unique_offsets=None, unique_inverse=None,
+                            grad_shards=None) -> None:
+        """Enqueue the index work of the next backward (for exactly these indices / offsets) on the module's side
+        stream, ordered after what is already enqueued on the current stream; the backward waits for it."""
+        self._ensure_workspace(indices.numel())
+        cur = torch.cuda.current_stream(self.current_device)
+        if self._plan_stream is None:
+            # high priority: the plan's many small kernels take SM slots as the forward's blocks retire instead of
+            # queueing behind them
+            self._plan_stream = torch.cuda.Stream(device=self.current_device, priority=-1)
+            self._plan_event = torch.cuda.Event()
+        self._plan_stream.wait_stream(cur)
+        with torch.cuda.stream(self._plan_stream):
+            self._backward_impl(None, indices, offsets, unique_ids, unique_offsets, unique_inverse, 1,
+                                grad_shards=grad_shards, phase="plan")
+            self._plan_event.record(self._plan_stream)
+        self._planned_for = (indices.data_ptr(), indices.numel(), offsets.data_ptr())
+
+    def _backward_impl(self, grad_output, indices, offsets, unique_ids, unique_offsets, unique_inverse, iteration,
+                       update_events=None, grad_shards=None, phase: str = "all") -> None:
+        a = self.optimizer_args
+        self._last_N = indices.numel()  # indices of the most recent backward (bandwidth accounting)
+        self._ensure_workspace(indices.numel())
+        if phase == "all" and self._planned_for is not None:
+            if self._planned_for != (indices.data_ptr(), indices.numel(), offsets.data_ptr()):
+                raise RuntimeError("the backward plan made ahead belongs to other indices / offsets")
+            torch.cuda.current_stream(self.current_device).wait_event(self._plan_event)
+            self._planned_for = None
+            phase = "apply"
         ops.tbe_backward(grad_output, self.weights_dev.data,
                          self.momentum1_dev if self._optim_num >= 1 else None,
                          self.momentum2_dev if self._optim_num >= 2 else None,
@@ -235,7 +274,7 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
                          total_hash_size_bits=self.total_hash_size_bits, reduce_chunk=self.reduce_chunk,
                          gradient_clipping=a.gradient_clipping, max_gradient=a.max_gradient,
                          status=self._status if self.bounds_check else None, bounds_check=self.bounds_check,
-                         workspace=self._ws, update_events=update_events, grad_shards=grad_shards)
+                         workspace=self._ws, update_events=update_events, grad_shards=grad_shards, phase=phase)
 
     # ------------------------------------------------------------------ reference interface
     def forward(self, indices: Tensor, offsets: Tensor, hash_indices: Optional[Tensor] = None,
@@ -335,9 +374,14 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         ops.raise_on_status(self._status, "HybridSplitTableBatchedEmbeddingBagsCodegen")
 
     # ------------------------------------------------------------------ allocation-free stepping (benchmarks, pipelines)
-    def forward_into(self, indices: Tensor, offsets: Tensor, out: Optional[Tensor] = None, out_shards=None):
+    def forward_into(self, indices: Tensor, offsets: Tensor, out: Optional[Tensor] = None, out_shards=None,
+                     plan_grad_shards=None):
         """Forward without autograd bookkeeping, writing into a caller-owned output, or (``out_shards``, an
-        ops.SampleShards) straight into the sample owners' peer-mapped buffers."""
+        ops.SampleShards) straight into the sample owners' peer-mapped buffers.  With ``plan_ahead`` the index work
+        of the following backward_from is enqueued on the side stream first (``plan_grad_shards``: the layout that
+        backward's gradient will have when it is sample-sharded)."""
+        if self.plan_ahead:
+            self.plan_backward_ahead(indices, offsets, grad_shards=plan_grad_shards)
         return self._forward_impl(indices, offsets, out=out, out_shards=out_shards)
 
     def backward_from(self, grad_output: Optional[Tensor], indices: Tensor, offsets: Tensor, unique_indices=None,

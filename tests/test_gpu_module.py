@@ -169,3 +169,34 @@ def test_bucketize_torch_op_matches_reference_golden(golden_dir, op):
         np.testing.assert_array_equal(res[1].cpu().numpy(), g[f"c{c}_new_indices"])
         np.testing.assert_array_equal(res[4].cpu().numpy(), g[f"c{c}_unbucketize_permute"])
         np.testing.assert_array_equal(res[6].cpu().numpy(), g[f"c{c}_ids_counts"])
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_module_plan_ahead_matches_plain_module(mode):
+    """plan_ahead=True (the backward's index work enqueued on a side stream by every forward) through autograd and
+    through forward_into / backward_from: same weights, bit for bit, as the module without it."""
+    from recsdk_b200.tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
+
+    specs = [(500, 128), (40, 128), (300, 64)]
+    mods = [HybridSplitTableBatchedEmbeddingBagsCodegen(specs, optimizer=EmbOptimType.ADAM, pooling_mode=PoolingMode(mode),
+                                                        learning_rate=0.05, device=DEV, weights_init=(-0.1, 0.1), seed=4,
+                                                        plan_ahead=pa) for pa in (False, True)]
+    rng = np.random.default_rng(mode)
+    B = 64
+    for step in range(4):
+        lens = rng.integers(0, 4, 3 * B)
+        offs = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)).to(DEV)
+        idx = torch.from_numpy(np.concatenate([rng.integers(0, specs[i // B][0] if i % 5 else 7, lens[i])
+                                               for i in range(3 * B)]).astype(np.int64)).to(DEV)
+        g = torch.randn(B, 128 + 128 + 64, device=DEV)
+        for m in mods:
+            if step % 2 == 0:
+                out = m(idx, offs)
+                out.backward(g)
+            else:
+                out = torch.empty(B, 320, device=DEV)
+                m.forward_into(idx, offs, out)
+                m.backward_from(g, idx, offs)
+    assert torch.equal(mods[0].weights_dev.data, mods[1].weights_dev.data)
+    assert torch.equal(mods[0].momentum1_dev, mods[1].momentum1_dev)
+    assert torch.equal(mods[0].momentum2_dev, mods[1].momentum2_dev)

@@ -226,6 +226,51 @@ def test_backward_staged_update_bit_exact(case, mode, opt):
         np.testing.assert_array_equal(dm2.cpu().numpy(), m2)
 
 
+@pytest.mark.parametrize("opt", [1, 2])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("case", [2, 3, 7, 8])
+def test_backward_plan_then_apply_bit_exact(case, mode, opt):
+    """RECSDK_BWD_PLAN_ONLY on a side stream (no gradient given), then RECSDK_BWD_APPLY_ONLY on the main stream
+    after an event: same bits as the single call, i.e. as the oracle."""
+    if mode == 2 and len(set(BWD_CASES[case]["dims"])) > 1:
+        pytest.skip("NONE pooling needs equal dims")
+    rng = np.random.default_rng(2600 + case)
+    c = make_case(rng, **BWD_CASES[case])
+    from recsdk_b200 import ops
+
+    N = c["indices"].size
+    gshape = (N, c["max_D"]) if mode == 2 else (c["B"], c["total_D"])
+    grad = rng.standard_normal(gshape).astype(np.float32)
+    w = c["w"].copy()
+    m1 = np.full_like(w, 0.1) if opt == 1 else rng.uniform(0, 0.01, w.size).astype(np.float32)
+    m2 = rng.uniform(0, 0.01, w.size).astype(np.float32)
+    dw, dm1, dm2 = _t(w), _t(m1), _t(m2)
+    st = ops.new_status(DEV)
+    bits = int(c["hs"][-1]).bit_length()
+    ws = torch.empty(ops.tbe_backward_workspace_bytes(N, c["max_D"]), dtype=torch.uint8, device=DEV)
+    side, ev = torch.cuda.Stream(), torch.cuda.Event()
+    d = dict(wo=_t(c["wo"]), do=_t(c["do"]), hs=_t(c["hs"]), idx=_t(c["indices"]), offs=_t(c["offsets"]), g=_t(grad))
+    for it in (1, 2):
+        port.tbe_backward(grad, w, m1, m2, c["wo"], c["do"], c["hs"], c["indices"], c["offsets"], c["T"], c["B"],
+                          c["total_D"], c["max_D"], mode, opt, 0.05, 1e-8, 0.9, 0.999, it, reduce_chunk=64)
+        args = (dw, dm1, dm2, d["wo"], d["do"], d["hs"], d["idx"], d["offs"], c["total_D"], c["max_D"], mode, opt, 0.05,
+                1e-8, 0.9, 0.999, it)
+        kw = dict(total_hash_size_bits=bits, reduce_chunk=64, status=st, workspace=ws)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ops.tbe_backward(None, *args, phase="plan", **kw)
+            ev.record(side)
+        torch.cuda.current_stream().wait_event(ev)
+        ops.tbe_backward(d["g"], *args, phase="apply", **kw)
+    ops.raise_on_status(st)
+    np.testing.assert_array_equal(dw.cpu().numpy(), w)
+    np.testing.assert_array_equal(dm1.cpu().numpy(), m1)
+    if opt == 2:
+        np.testing.assert_array_equal(dm2.cpu().numpy(), m2)
+    with pytest.raises(RuntimeError, match="workspace"):
+        ops.tbe_backward(None, *args, phase="plan", total_hash_size_bits=bits)
+
+
 def test_backward_gradient_clipping_and_64bit_keys():
     rng = np.random.default_rng(7)
     c = make_case(rng, rows=[300, 200], dims=[16, 16], B=40, max_len=5)
