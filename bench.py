@@ -163,6 +163,8 @@ def run_ours(args):
 
         bag = TableWiseDedupEmbeddingBag([rows_all[t] for t in sh.output_table_order], DIM,
                                          [sh.owner[t] for t in sh.output_table_order], world, rank, **opt_kw)
+        if not os.environ.get("RECSDK_DEDUP_NCCL_ROWS"):  # A/B switch: rows through NCCL all-to-alls instead
+            bag.enable_peer_pull(BATCH)
         module = bag.owner
     else:
         module = HybridSplitTableBatchedEmbeddingBagsCodegen([(r, DIM) for r in rows], **opt_kw)
@@ -490,6 +492,9 @@ def run_ours(args):
         dist.barrier()
         if fused:
             fx.close()
+            dist.barrier()
+        if dedup:
+            bag.close()
             dist.barrier()
         dist.destroy_process_group()
 

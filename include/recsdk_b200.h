@@ -437,6 +437,9 @@ RECSDK_API int recsdk_dense_to_jagged(const float* dense, const int64_t* offsets
 RECSDK_API int recsdk_peer_export(const void* dev_ptr, unsigned char* handle_out, int64_t* offset_out);
 RECSDK_API int recsdk_peer_import(const unsigned char* handle, int64_t offset, void** dev_ptr_out);
 RECSDK_API int recsdk_peer_release(void* imported_ptr, int64_t offset);
+/* Stream-ordered copy between device buffers of which either may be a peer mapping (a pull of rows from another
+ * rank's buffer, or a push into it). */
+RECSDK_API int recsdk_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -112,6 +112,7 @@ SIGNATURES = {
     "recsdk_peer_export": (C.c_int, [vp, vp, C.POINTER(C.c_int64)]),
     "recsdk_peer_import": (C.c_int, [vp, C.c_int64, C.POINTER(vp)]),
     "recsdk_peer_release": (C.c_int, [vp, C.c_int64]),
+    "recsdk_peer_copy": (C.c_int, [vp, vp, C.c_size_t, vp]),
     "recsdk_mapper_table_bytes": (C.c_size_t, [C.c_int64]),
     "recsdk_mapper_init": (C.c_int, [C.POINTER(MapperT), vp]),
     "recsdk_mapper_workspace_bytes": (C.c_size_t, [C.c_int64]),

@@ -62,3 +62,15 @@ extern "C" int recsdk_peer_release(void* imported_ptr, int64_t offset)
     }
     return RECSDK_OK;
 }
+
+extern "C" int recsdk_peer_copy(void* dst, const void* src, size_t bytes, void* stream)
+{
+    if (bytes == 0) return RECSDK_OK;
+    if (dst == nullptr || src == nullptr) return RECSDK_ERR_INVALID_ARG;
+    // either side may be a mapping returned by recsdk_peer_import: the copy engines move the bytes over NVLink
+    if (cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return RECSDK_ERR_CUDA;
+    }
+    return RECSDK_OK;
+}

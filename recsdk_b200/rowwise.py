@@ -30,6 +30,13 @@ from . import ops
 from .tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
 
 
+def _running(xs):
+    s = 0
+    for x in xs:
+        s += x
+        yield s
+
+
 def _a2a(out: torch.Tensor, inp: torch.Tensor, out_splits: List[int], in_splits: List[int], group) -> None:
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_to_all_single(out, inp, out_splits, in_splits, group=group)
@@ -178,6 +185,102 @@ class TableWiseDedupEmbeddingBag(_DedupExchangeLookup):
         self.owner = HybridSplitTableBatchedEmbeddingBagsCodegen(
             [(n_local, self.dim)], feature_table_map=[0] * world, optimizer=optimizer, pooling_mode=PoolingMode.NONE,
             device=self.device, **optimizer_kwargs)
+
+    # ------------------------------------------------------------------ peer-pull variant of the two row exchanges
+    def enable_peer_pull(self, max_ids_per_table_per_rank: int) -> None:
+        """Replace the all-to-alls of rows and of gradient rows by copies out of peer-mapped buffers: the owner
+        gathers the requested rows into a buffer every rank can address and each requester pulls its segment
+        (copy engines over NVLink); gradients travel the same way in the other direction.  Buffers are sized for
+        the worst case (every id of a rank's batch distinct: ``max_ids_per_table_per_rank`` is the largest number
+        of ids one rank's batch can hold for one table, the batch size for one id per bag); call once, on every
+        rank, after construction."""
+        from .peer import PeerMappedBuffer
+
+        W, D = self.world, self.dim
+        max_tables = max(sum(1 for o in self.owner_of if o == r) for r in range(W))
+        self._rows_stage = PeerMappedBuffer((max_tables * W * max_ids_per_table_per_rank, D), self.device, self.group)
+        self._grad_stage = PeerMappedBuffer((self.F * max_ids_per_table_per_rank, D), self.device, self.group)
+        self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._peer_pull = True
+
+    def _fence(self) -> None:
+        dist.all_reduce(self._token, group=self.group)  # stream-ordered barrier across the ranks
+
+    def _pull(self, dst: torch.Tensor, src_ptr: int, rows: int) -> None:
+        from . import _lib
+        from .ops import _stream, check
+
+        check(_lib.load().recsdk_peer_copy(dst.data_ptr(), src_ptr, rows * self.dim * 4, _stream()), "recsdk_peer_copy")
+
+    def forward(self, indices: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+        if not getattr(self, "_peer_pull", False):
+            return super().forward(indices, offsets)
+        F, D, W, dev, me = self.F, self.dim, self.world, self.device, self.rank
+        uniq_buf, perm, send_counts = self._partition(indices, offsets)
+        mat = torch.empty(W * W, dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(mat, send_counts.view(-1).contiguous(), group=self.group)
+        M = mat.view(W, W).tolist()  # M[q][r]: distinct rows rank q asks of rank r (the one host read of the forward)
+        send_splits, recv_splits = [int(x) for x in M[me]], [int(M[q][me]) for q in range(W)]
+        n_u, n_recv = sum(send_splits), sum(recv_splits)
+        # every rank sees the whole matrix, so a buffer that is too small is an error on all ranks at once
+        worst_owner = max(sum(int(M[q][r]) for q in range(W)) for r in range(W))
+        worst_asker = max(sum(int(x) for x in M[q]) for q in range(W))
+        if worst_owner > self._rows_stage.local.shape[0] or worst_asker > self._grad_stage.local.shape[0]:
+            raise RuntimeError(f"peer-pull buffers too small: {worst_owner} rows at an owner / {worst_asker} at a "
+                               f"requester, capacities {self._rows_stage.local.shape[0]} / "
+                               f"{self._grad_stage.local.shape[0]}")
+        recv_ids = torch.empty(n_recv, dtype=torch.int64, device=dev)
+        _a2a(recv_ids, uniq_buf[:n_u], recv_splits, send_splits, self.group)
+        local = self._owner_rows(recv_ids)
+        owner_offsets = torch.tensor([0] + list(_running(recv_splits)), dtype=torch.int64, device=dev)
+        stage = self._rows_stage.local[:max(n_recv, 1)]
+        if n_recv:
+            self.owner.forward_into(local, owner_offsets, stage[:n_recv])
+        self._fence()  # every owner's rows are in its buffer
+        fetched = torch.empty((n_u, D), dtype=torch.float32, device=dev)
+        seg = 0
+        for r in range(W):
+            n = send_splits[r]
+            if n:
+                start_in_r = sum(int(M[q][r]) for q in range(me))  # rows of lower ranks come first in r's buffer
+                self._pull(fetched[seg:seg + n], self._rows_stage.ptrs[r] + start_in_r * D * 4, n)
+            seg += n
+        out = ops.tbe_forward(fetched.view(-1), self._zeros_F, self._D_offsets, perm, offsets, F * D, D,
+                              int(self.pooling_mode), bounds_check=True)
+        self._ctx = (perm, offsets, n_u, send_splits, recv_splits, local, owner_offsets, n_recv, M)
+        return out
+
+    def backward(self, grad_output: torch.Tensor, update_events=None) -> None:
+        if not getattr(self, "_peer_pull", False):
+            return super().backward(grad_output, update_events)
+        perm, offsets, n_u, send_splits, recv_splits, local, owner_offsets, n_recv, M = self._ctx
+        F, D, W, dev, me = self.F, self.dim, self.world, self.device, self.rank
+        fetched_grad = self._grad_stage.local.view(-1)[:max(n_u, 1) * D]
+        fetched_grad.zero_()
+        hs = torch.zeros(F + 1, dtype=torch.int64, device=dev)
+        hs[F] = n_u
+        ops.tbe_backward(grad_output, fetched_grad, None, None, self._zeros_F, self._D_offsets, hs, perm, offsets,
+                         F * D, D, int(self.pooling_mode), ops.OPT_SGD, -1.0,
+                         total_hash_size_bits=max(1, int(n_u).bit_length()), bounds_check=True)
+        self._fence()  # every requester's per-row sums are in its buffer
+        recv_grad = torch.empty((n_recv, D), dtype=torch.float32, device=dev)
+        seg = 0
+        for q in range(W):
+            n = recv_splits[q]
+            if n:
+                start_in_q = sum(int(M[q][r]) for r in range(me))  # q's rows for lower owners come first in its buffer
+                self._pull(recv_grad[seg:seg + n], self._grad_stage.ptrs[q] + start_in_q * D * 4, n)
+            seg += n
+        if n_recv:
+            self.owner.backward_from(recv_grad, local, owner_offsets, update_events=update_events)
+        else:
+            self.owner.iter[0] += 1
+
+    def close(self) -> None:
+        if getattr(self, "_peer_pull", False):
+            self._rows_stage.close()
+            self._grad_stage.close()
+            self._peer_pull = False
 
     def _partition(self, indices, offsets):
         F, dev = self.F, self.device

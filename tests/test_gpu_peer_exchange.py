@@ -130,7 +130,7 @@ def test_fused_table_wise_exchange_two_gpus():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(300)
+        p.join(90)
     for p in procs:
         if p.is_alive():  # pragma: no cover
             p.terminate()

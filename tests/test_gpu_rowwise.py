@@ -62,6 +62,8 @@ def _worker(rank, world, port, errors, scheme="row"):
             shard_of = lambda a: a[rank::world]  # noqa: E731
         else:
             bag = TableWiseDedupEmbeddingBag(ROWS, D, owner, world, rank, **kw)
+            if scheme == "table_pull":  # rows and gradient rows pulled out of peer-mapped buffers instead of all-to-alls
+                bag.enable_peer_pull(B_LOCAL * MAX_L)
             mine_tables = [f for f in range(F) if owner[f] == rank]
             shard_of = lambda a: a  # noqa: E731
         for f in mine_tables:
@@ -103,13 +105,16 @@ def _worker(rank, world, port, errors, scheme="row"):
             got = results[0][f][:exp.shape[0]].cpu().numpy()
             np.testing.assert_allclose(got, exp, rtol=0, atol=1e-5)
         dist.barrier()
+        if scheme == "table_pull":
+            bag.close()
+            dist.barrier()
         dist.destroy_process_group()
     except Exception as e:  # pragma: no cover
         errors.put((rank, repr(e)))
         raise
 
 
-@pytest.mark.parametrize("scheme", ["row", "table"])
+@pytest.mark.parametrize("scheme", ["row", "table", "table_pull"])
 def test_dedup_exchange_lookup_two_gpus(scheme):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -123,7 +128,7 @@ def test_dedup_exchange_lookup_two_gpus(scheme):
     for p in procs:
         p.start()
     for p in procs:
-        p.join(300)
+        p.join(90)
     for p in procs:
         if p.is_alive():  # pragma: no cover
             p.terminate()
