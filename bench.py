@@ -163,7 +163,10 @@ def run_ours(args):
 
         bag = TableWiseDedupEmbeddingBag([rows_all[t] for t in sh.output_table_order], DIM,
                                          [sh.owner[t] for t in sh.output_table_order], world, rank, **opt_kw)
-        if not os.environ.get("RECSDK_DEDUP_NCCL_ROWS"):  # A/B switch: rows through NCCL all-to-alls instead
+        # rows pulled out of peer-mapped buffers instead of the two row all-to-alls: measured better at 2 GPUs
+        # (2.08 vs 2.32 ms/step), worse at 4 and 8 (2.63 vs 2.35, 3.24 vs 2.39: 2(W-1) small serial copies and two
+        # more fences per step), so it is off unless asked for
+        if os.environ.get("RECSDK_DEDUP_PEER_PULL"):
             bag.enable_peer_pull(BATCH)
         module = bag.owner
     else:
