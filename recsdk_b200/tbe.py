@@ -186,7 +186,8 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         from . import torch_ops
 
         if use_torch_ops is None:
-            use_torch_ops = torch_ops.available() and reduce_chunk == 64 and not bounds_check
+            # the registered operators run the whole backward in one call; planning ahead needs the split calls
+            use_torch_ops = torch_ops.available() and reduce_chunk == 64 and not bounds_check and not plan_ahead
         if use_torch_ops:
             torch_ops.load()
         self.use_torch_ops = bool(use_torch_ops)
