@@ -11,7 +11,11 @@
 // Also: class `recsdk::IdsMapper` with the methods of `hybrid::IdsMapper`
 // (hybrid_torchrec/src/bind_torch_lib.cpp:9-19) and `recsdk::block_bucketize_sparse_features`.
 #include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
+
+#include <atomic>
 #include <torch/csrc/autograd/custom_function.h>
 #include <torch/custom_class.h>
 #include <torch/library.h>
@@ -90,25 +94,30 @@ struct OptArgs {
     int64_t iter = 1;
 };
 
+// flags / ws / plan_total_D: the split form of the call (RECSDK_BWD_PLAN_ONLY without a gradient, then
+// RECSDK_BWD_APPLY_ONLY with the same workspace); 0 / undefined / 0 = the whole backward with its own workspace.
 static Tensor backward_exact(const Tensor& grad_output_in, const Tensor& dev_weights, const Tensor& weights_offsets,
                              const Tensor& D_offsets, int64_t max_D, const Tensor& hash_size_cumsum,
                              int64_t total_hash_size_bits, const Tensor& indices, const Tensor& offsets,
                              int64_t pooling_mode, const Tensor& momentum1, const Tensor& momentum2,
                              const Tensor& hash_indices, const Tensor& unique_ids, const Tensor& unique_offsets,
-                             const Tensor& unique_inverse, const OptArgs& o)
+                             const Tensor& unique_inverse, const OptArgs& o, int flags = 0, Tensor ws = Tensor(),
+                             int64_t plan_total_D = 0, void* stream = nullptr)
 {
     TORCH_CHECK(dev_weights.is_cuda(), "dev_weights must be a CUDA tensor (recsdk_b200 has no CPU path)");
     const c10::cuda::OptionalCUDAGuard guard(device_of(dev_weights));
     const int64_t T = weights_offsets.size(0);
     const Tensor& idx = pick(indices, hash_indices);
     if (T == 0 || idx.numel() == 0) return Tensor();
-    Tensor grad_output = grad_output_in.contiguous();
-    TORCH_CHECK(grad_output.scalar_type() == at::kFloat, "grad_output must be fp32");
+    const bool plan_only = (flags & RECSDK_BWD_PLAN_ONLY) != 0;
+    Tensor grad_output = plan_only ? Tensor() : grad_output_in.contiguous();
+    TORCH_CHECK(plan_only || grad_output.scalar_type() == at::kFloat, "grad_output must be fp32");
     check_i64(idx, "indices");
     check_i64(offsets, "offsets");
     const int64_t B = (offsets.size(0) - 1) / T;
     recsdk_tbe_backward_args b{};
-    b.grad_output = grad_output.data_ptr<float>();
+    b.grad_output = plan_only ? nullptr : grad_output.data_ptr<float>();
+    b.flags = flags;
     b.dev_weights = dev_weights.data_ptr<float>();
     if (o.optimizer != RECSDK_OPT_SGD) b.momentum1 = momentum1.data_ptr<float>();
     if (o.optimizer == RECSDK_OPT_ADAM) b.momentum2 = momentum2.data_ptr<float>();
@@ -130,7 +139,7 @@ static Tensor backward_exact(const Tensor& grad_output_in, const Tensor& dev_wei
     b.T = T;
     b.B = B;
     b.N = idx.numel();
-    b.total_D = static_cast<int32_t>(pooling_mode == RECSDK_POOL_NONE ? max_D : grad_output.size(1));
+    b.total_D = static_cast<int32_t>(pooling_mode == RECSDK_POOL_NONE ? max_D : (plan_only ? plan_total_D : grad_output.size(1)));
     b.max_D = static_cast<int32_t>(max_D);
     b.pooling_mode = static_cast<int32_t>(pooling_mode);
     b.optimizer = o.optimizer;
@@ -141,11 +150,12 @@ static Tensor backward_exact(const Tensor& grad_output_in, const Tensor& dev_wei
     b.beta1 = static_cast<float>(o.beta1);
     b.beta2 = static_cast<float>(o.beta2);
     b.iter = o.iter;
-    Tensor ws = at::empty({static_cast<int64_t>(recsdk_tbe_backward_workspace_bytes(b.N, b.max_D))},
-                          dev_weights.options().dtype(at::kByte));
+    if (!ws.defined())
+        ws = at::empty({static_cast<int64_t>(recsdk_tbe_backward_workspace_bytes(b.N, b.max_D))},
+                       dev_weights.options().dtype(at::kByte));
     b.workspace = ws.data_ptr();
     b.workspace_bytes = static_cast<size_t>(ws.numel());
-    check_rc(recsdk_tbe_backward(&b, cur_stream()), "split_embedding_backward_codegen_unweighted_exact_cuda");
+    check_rc(recsdk_tbe_backward(&b, stream ? stream : cur_stream()), "split_embedding_backward_codegen_unweighted_exact_cuda");
     return Tensor();  // like the reference: state is updated in place, no weight gradient is returned
 }
 
@@ -192,6 +202,13 @@ Tensor backward_sgd_cuda(const Tensor& grad_output, const Tensor& dev_weights, c
 }
 
 // ---------------------------------------------------------------------------- autograd lookup functions
+// Plan ahead (off by default; recsdk::set_plan_ahead(True)): the lookup functions enqueue the index work of their
+// own backward on a high-priority side stream while the forward runs, and the backward only sums and updates.
+// For the forward -> backward alternation of training.
+static std::atomic<bool> g_plan_ahead{false};
+void set_plan_ahead(bool on) { g_plan_ahead.store(on); }
+bool get_plan_ahead() { return g_plan_ahead.load(); }
+
 // One Function for the three optimizers (the reference has SplitLookupAdagrad / SplitLookupAdam / SplitLookupSgd,
 // e.g. backward_codegen_adam_unweighted_exact.cpp:65-284): forward = pooled gather, backward = optional clamp of
 // the incoming gradient + fused segment-sum / optimizer, no gradient for any input.
@@ -225,6 +242,27 @@ public:
         ctx->saved_data["beta1"] = beta1;
         ctx->saved_data["beta2"] = beta2;
         ctx->saved_data["iter"] = iter;
+        ctx->saved_data["planned"] = false;
+        const Tensor& plan_idx = pick(indices, hash_indices);
+        if (g_plan_ahead.load() && dev_weights.is_cuda() && plan_idx.numel() > 0) {
+            const c10::cuda::OptionalCUDAGuard guard(device_of(dev_weights));
+            Tensor ws = at::empty({static_cast<int64_t>(recsdk_tbe_backward_workspace_bytes(plan_idx.numel(), static_cast<int32_t>(max_D)))},
+                                  dev_weights.options().dtype(at::kByte));
+            auto side = at::cuda::getStreamFromPool(/*isHighPriority=*/true, dev_weights.device().index());
+            auto cur = at::cuda::getCurrentCUDAStream();
+            at::cuda::CUDAEvent ready;
+            ready.record(cur);
+            ready.block(side);  // the indices are complete before the plan reads them
+            c10::cuda::CUDACachingAllocator::recordStream(ws.storage().data_ptr(), side);
+            OptArgs o{static_cast<int>(optimizer), eps, lr, beta1, beta2, iter};
+            backward_exact(Tensor(), dev_weights, weights_offsets, D_offsets, max_D, hash_size_cumsum, total_hash_size_bits,
+                           indices, offsets, pooling_mode, momentum1, momentum2, hash_indices, unique_ids, unique_offsets,
+                           unique_inverse, o, RECSDK_BWD_PLAN_ONLY, ws, total_D, side.stream());
+            ctx->saved_data["planned"] = true;
+            ctx->saved_data["plan_ws"] = ws;
+            ctx->saved_data["plan_stream_id"] = static_cast<int64_t>(side.id());
+            ctx->saved_data["plan_device"] = static_cast<int64_t>(side.device_index());
+        }
         const Tensor none;
         return {forward_unweighted_cuda(dev_weights, none, none, none, weights_offsets, D_offsets, total_D, max_D, indices,
                                         offsets, pooling_mode, none, none, 0, false, hash_indices, none)};
@@ -242,8 +280,22 @@ public:
         OptArgs o{static_cast<int>(ctx->saved_data["optimizer"].toInt()), ctx->saved_data["eps"].toDouble(),
                   ctx->saved_data["lr"].toDouble(), ctx->saved_data["beta1"].toDouble(),
                   ctx->saved_data["beta2"].toDouble(), ctx->saved_data["iter"].toInt()};
+        int flags = 0;
+        Tensor ws;
+        if (ctx->saved_data["planned"].toBool()) {
+            // everything enqueued on the side stream so far (the plan) is ordered before the apply phase
+            const c10::cuda::OptionalCUDAGuard guard(device_of(s[0]));
+            const auto side = c10::cuda::CUDAStream(c10::Stream(
+                c10::Stream::UNSAFE, c10::Device(c10::DeviceType::CUDA, static_cast<c10::DeviceIndex>(ctx->saved_data["plan_device"].toInt())),
+                ctx->saved_data["plan_stream_id"].toInt()));
+            at::cuda::CUDAEvent done;
+            done.record(side);
+            done.block(at::cuda::getCurrentCUDAStream());
+            flags = RECSDK_BWD_APPLY_ONLY;
+            ws = ctx->saved_data["plan_ws"].toTensor();
+        }
         backward_exact(g, s[0], s[1], s[2], ctx->saved_data["max_D"].toInt(), s[3], ctx->saved_data["bits"].toInt(), s[4],
-                       s[5], ctx->saved_data["pooling_mode"].toInt(), s[6], s[7], s[8], s[9], s[10], s[11], o);
+                       s[5], ctx->saved_data["pooling_mode"].toInt(), s[6], s[7], s[8], s[9], s[10], s[11], o, flags, ws);
         return variable_list(25);  // no gradient for any of the 25 forward inputs
     }
 };
@@ -731,6 +783,8 @@ TORCH_LIBRARY(recsdk, m)
         .def("size", &recsdk_torch::IdsMapper::size)
         .def_static("parallel_ids2indices_unique_out", &recsdk_torch::IdsMapper::ParallelUniqueHashOut);
     m.def("block_bucketize_sparse_features", &recsdk_torch::block_bucketize_sparse_features);
+    m.def("set_plan_ahead(bool on) -> ()", &recsdk_torch::set_plan_ahead);
+    m.def("get_plan_ahead() -> bool", &recsdk_torch::get_plan_ahead);
     recsdk_torch::define_and_implement_kjt(m);
 }
 

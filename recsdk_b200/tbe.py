@@ -186,10 +186,15 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         from . import torch_ops
 
         if use_torch_ops is None:
-            # the registered operators run the whole backward in one call; planning ahead needs the split calls
+            # with plan_ahead the Python Function is the default route (measured 0.880 vs 0.907 ms per end-to-end step
+            # through the registered operators, which allocate their workspace per call); use_torch_ops=True
+            # selects the registered operators explicitly
             use_torch_ops = torch_ops.available() and reduce_chunk == 64 and not bounds_check and not plan_ahead
         if use_torch_ops:
             torch_ops.load()
+            if plan_ahead:
+                # process-wide switch of the registered lookup operators: they plan their own backward ahead
+                torch.ops.recsdk.set_plan_ahead(True)
         self.use_torch_ops = bool(use_torch_ops)
 
         total = table_wo[-1]

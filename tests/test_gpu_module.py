@@ -200,3 +200,40 @@ def test_module_plan_ahead_matches_plain_module(mode):
     assert torch.equal(mods[0].weights_dev.data, mods[1].weights_dev.data)
     assert torch.equal(mods[0].momentum1_dev, mods[1].momentum1_dev)
     assert torch.equal(mods[0].momentum2_dev, mods[1].momentum2_dev)
+
+
+def test_registered_ops_plan_ahead_same_bits():
+    """recsdk::set_plan_ahead(True): the registered lookup operators enqueue their backward's index work on a side
+    stream during the forward.  Same weights, bit for bit, as with the switch off."""
+    from recsdk_b200 import torch_ops
+    from recsdk_b200.tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
+
+    if not torch_ops.available():
+        pytest.skip("torch op library not built")
+    torch_ops.load()
+    specs = [(500, 128), (40, 128), (300, 64)]
+    rng = np.random.default_rng(12)
+    B = 64
+    steps = []
+    for _ in range(4):
+        lens = rng.integers(0, 4, 3 * B)
+        offs = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)).to(DEV)
+        idx = torch.from_numpy(np.concatenate([rng.integers(0, specs[i // B][0] if i % 5 else 7, lens[i])
+                                               for i in range(3 * B)]).astype(np.int64)).to(DEV)
+        steps.append((idx, offs, torch.randn(B, 320, device=DEV)))
+    results = []
+    try:
+        for on in (False, True):
+            torch.ops.recsdk.set_plan_ahead(on)
+            assert torch.ops.recsdk.get_plan_ahead() == on
+            m = HybridSplitTableBatchedEmbeddingBagsCodegen(specs, optimizer=EmbOptimType.ADAM, pooling_mode=PoolingMode.SUM,
+                                                            learning_rate=0.05, device=DEV, weights_init=(-0.1, 0.1), seed=4,
+                                                            use_torch_ops=True)
+            for idx, offs, g in steps:
+                m(idx, offs).backward(g)
+            torch.cuda.synchronize()
+            results.append((m.weights_dev.data.clone(), m.momentum1_dev.clone(), m.momentum2_dev.clone()))
+    finally:
+        torch.ops.recsdk.set_plan_ahead(False)
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
