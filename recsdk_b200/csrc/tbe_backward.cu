@@ -829,7 +829,8 @@ static void launch_update(const BwdParams& p, const RunMeta* meta, int64_t N, cu
 {
     if (G == 32 && launch_update_staged(p, meta, st)) return;
     const int groups_per_block = 256 / G;
-    const int grid = grid_for(N, groups_per_block, 8);
+    // as many blocks as are resident at once (64 registers: 4 per SM), each striding over the rows: no second wave
+    const int grid = grid_for(N, groups_per_block, 4);
     switch (p.opt) {
         case RECSDK_OPT_ADAGRAD: update_kernel<G, K, RECSDK_OPT_ADAGRAD><<<grid, 256, 0, st>>>(p, meta); break;
         case RECSDK_OPT_ADAM: update_kernel<G, K, RECSDK_OPT_ADAM><<<grid, 256, 0, st>>>(p, meta); break;
@@ -841,7 +842,8 @@ template <int G, int K>
 static void launch_partial(const BwdParams& p, int64_t N, cudaStream_t st)
 {
     const int groups_per_block = 256 / G;
-    const int grid = grid_for(2 * N / kChunk + 2, groups_per_block, 8);
+    // one resident wave (80 registers: 3 blocks per SM)
+    const int grid = grid_for(2 * N / kChunk + 2, groups_per_block, 3);
     partial_kernel<G, K><<<grid, 256, 0, st>>>(p);
 }
 
