@@ -92,6 +92,9 @@ typedef struct {
  * rest of the max_D-wide output row is zero.  `indices` is what the reference
  * calls hash_indices when those are given.  Every element of `out` is written.
  * ========================================================================= */
+/* flags of recsdk_tbe_forward_args.  LEAVE_ROOM: run the pooled gather with three instead of four resident blocks
+ * per SM so that kernels enqueued on other streams (the backward's plan) find SM slots beside it. */
+#define RECSDK_FWD_LEAVE_ROOM 1
 typedef struct {
     const float* dev_weights;       /* flat, all tables                         */
     const int64_t* weights_offsets; /* [T] element offset of each feature's table */
@@ -105,6 +108,7 @@ typedef struct {
     int64_t weights_numel; /* >0: rows are bounds-checked against it, violations -> status, row read as 0 */
     int64_t* dev_status;   /* optional */
     recsdk_sample_shards out_shards; /* optional (num_shards > 0): `out` is ignored */
+    int32_t flags;                   /* RECSDK_FWD_* */
 } recsdk_tbe_forward_args;
 RECSDK_API int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream);
 

@@ -41,7 +41,7 @@ class TbeForwardArgs(C.Structure):
         ("dev_weights", vp), ("weights_offsets", vp), ("D_offsets", vp), ("indices", vp), ("offsets", vp),
         ("out", vp), ("T", C.c_int64), ("B", C.c_int64), ("N", C.c_int64), ("total_D", C.c_int32),
         ("max_D", C.c_int32), ("pooling_mode", C.c_int32), ("weights_numel", C.c_int64), ("dev_status", vp),
-        ("out_shards", SampleShards),
+        ("out_shards", SampleShards), ("flags", C.c_int32),
     ]
 
 

@@ -244,6 +244,8 @@ __global__ void __launch_bounds__(256) tbe_forward_nobag_kernel(FwdParams p)
 }
 
 #ifndef RECSDK_EMULATE  // host side: not part of host-side SIMT emulation builds (tests/emu)
+static bool g_leave_room = false;  // set per call before launch_pooled (host-side, same thread)
+
 template <int G, int K>
 static void launch_pooled(const FwdParams& p, cudaStream_t st)
 {
@@ -252,7 +254,14 @@ static void launch_pooled(const FwdParams& p, cudaStream_t st)
     // beside this one on another stream, their blocks get SM slots as these retire (measured: 16 per SM 0.833 ms
     // per benchmark step, 8: 0.838, 2: 0.873; alone the grid size makes no difference)
     int grid = grid_for(ceil_div(p.T * p.B, G), groups_per_block, 16);
-    tbe_forward_pooled_kernel<G, K><<<grid, 256, 0, st>>>(p);
+    size_t smem = 0;
+    if (g_leave_room) {
+        // unused dynamic shared memory as an occupancy limit: 60 KB per block -> three blocks per SM
+        static bool attr_ok = cudaFuncSetAttribute(tbe_forward_pooled_kernel<G, K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   60 * 1024) == cudaSuccess;
+        if (attr_ok) smem = 60 * 1024; else (void)cudaGetLastError();
+    }
+    tbe_forward_pooled_kernel<G, K><<<grid, 256, smem, st>>>(p);
 }
 
 template <int G>
@@ -287,6 +296,7 @@ extern "C" int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream
                 aligned16(a->dev_weights) ? 1 : 0, sh};
     const int vec_per_row = (a->max_D + 3) / 4;
     const int G = group_lanes_for(vec_per_row);
+    g_leave_room = (a->flags & RECSDK_FWD_LEAVE_ROOM) != 0;
     if (a->pooling_mode == RECSDK_POOL_NONE) {
         if (a->N == 0) return RECSDK_OK;
         switch (G) {

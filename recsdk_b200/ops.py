@@ -90,7 +90,8 @@ class SampleShards:
 
 def tbe_forward(dev_weights, weights_offsets, D_offsets, indices, offsets, total_D: int, max_D: int,
                 pooling_mode: int, status: Optional[torch.Tensor] = None, bounds_check: bool = True,
-                out: Optional[torch.Tensor] = None, out_shards: Optional[SampleShards] = None):
+                out: Optional[torch.Tensor] = None, out_shards: Optional[SampleShards] = None,
+                leave_room: bool = False):
     """With ``out_shards`` the pooled rows are stored into the sample owners' buffers and None is returned."""
     lib = _lib.load()
     _chk(dev_weights, torch.float32, "dev_weights")
@@ -109,6 +110,7 @@ def tbe_forward(dev_weights, weights_offsets, D_offsets, indices, offsets, total
                                 _ptr(offsets), None, T, B, N, total_D, max_D, pooling_mode,
                                 dev_weights.numel() if bounds_check else 0, _ptr(status))
         out_shards.fill(a.out_shards)
+        a.flags = 1 if leave_room else 0  # RECSDK_FWD_LEAVE_ROOM
         check(lib.recsdk_tbe_forward(C.byref(a), _stream()), "recsdk_tbe_forward")
         return None
     if out is None:
@@ -119,6 +121,7 @@ def tbe_forward(dev_weights, weights_offsets, D_offsets, indices, offsets, total
     a = _lib.TbeForwardArgs(_ptr(dev_weights), _ptr(weights_offsets), _ptr(D_offsets), _ptr(indices), _ptr(offsets),
                             _ptr(out), T, B, N, total_D, max_D, pooling_mode,
                             dev_weights.numel() if bounds_check else 0, _ptr(status))
+    a.flags = 1 if leave_room else 0  # RECSDK_FWD_LEAVE_ROOM
     check(lib.recsdk_tbe_forward(C.byref(a), _stream()), "recsdk_tbe_forward")
     return out
 

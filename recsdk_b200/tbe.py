@@ -235,7 +235,8 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         return ops.tbe_forward(self.weights_dev.data, self.weights_offsets, self.D_offsets, indices, offsets,
                                self.total_D, self.max_D, int(self.pooling_mode),
                                status=self._status if self.bounds_check else None, bounds_check=self.bounds_check,
-                               out=out, out_shards=out_shards)
+                               out=out, out_shards=out_shards,
+                               leave_room=self.plan_ahead and self._planned_for is not None)
 
     def _ensure_workspace(self, n_indices: int) -> None:
         need = ops.tbe_backward_workspace_bytes(n_indices, self.max_D)
