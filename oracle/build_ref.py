@@ -13,9 +13,10 @@ Two artefacts are produced (both git-ignored; they travel with the work tree):
     utils/logger.cpp}`` unchanged, plus ``oracle/ref_embcache_harness.cpp`` (a
     flat C ABI over ``SwapManager`` / ``FeatureFilter``).
 
-No reference source is copied into this repository.  When the reference tree
-is not present (``RECSDK_REFERENCE_ROOT`` unset and the default location is
-missing) the recipe does nothing and whatever is already in ``oracle/_ref`` is
+No reference source is copied into this repository.  The reference tree is
+found through ``RECSDK_REFERENCE_ROOT`` or, when that is unset, as a checkout
+named ``reference`` beside this repository's own directory.  When neither
+exists the recipe does nothing and whatever is already in ``oracle/_ref`` is
 used as is.
 """
 from __future__ import annotations
@@ -27,11 +28,10 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-DEFAULT_REF = os.path.join(os.sep, "root", "reference")
 
 
 def reference_root() -> str | None:
-    root = os.environ.get("RECSDK_REFERENCE_ROOT", DEFAULT_REF)
+    root = os.environ.get("RECSDK_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     return root if os.path.isdir(os.path.join(root, "training", "torch_rec_v1")) else None
 
 

@@ -830,9 +830,13 @@ int orc_tbe_backward(const float* grad_output, float* weights, float* momentum1,
     } else {
 #pragma omp parallel for schedule(static)
         for (u = 0; u < U; u++) {
-            int64_t lin = own_uid[u], f = 0, r;
+            int64_t lin = own_uid[u], f = -1, r, ff;
             int32_t D;
-            while (f + 1 < T && hash_size_cumsum[f + 1] <= lin) f++;
+            /* the table that holds linear row `lin` starts at the largest hash_size_cumsum[f] <= lin; entries
+             * repeat (and are not monotonic in f) when features share tables, so look at all of them */
+            for (ff = 0; ff < T; ff++)
+                if (hash_size_cumsum[ff] <= lin && (f < 0 || hash_size_cumsum[ff] > hash_size_cumsum[f])) f = ff;
+            if (f < 0) continue;
             D = D_offsets[f + 1] - D_offsets[f];
             r = weights_offsets[f] + (lin - hash_size_cumsum[f]) * D;
             orc_update_row(optimizer, weights + r, momentum1 ? momentum1 + r : NULL, momentum2 ? momentum2 + r : NULL,

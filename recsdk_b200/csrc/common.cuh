@@ -12,9 +12,47 @@ namespace recsdk {
 constexpr int kWarp = 32;
 constexpr unsigned kFullMask = 0xffffffffu;
 
-// Number of SMs on a B200; grids of persistent / grid-stride kernels are sized
-// as a multiple of it.
-constexpr int kNumSMs = 148;
+// Number of SMs of the current device (148 on a B200); grids of persistent / grid-stride kernels are sized as a
+// multiple of it.  Queried once per device.
+constexpr int kMaxDevices = 64;
+#ifdef RECSDK_EMULATE
+static inline int num_sms() { return 148; }
+#else
+static inline int current_device_index()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+    return dev;
+}
+static inline int num_sms()
+{
+    static int cached[kMaxDevices] = {0};
+    const int dev = current_device_index();
+    int n = cached[dev];
+    if (n <= 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = 148;
+        }
+        cached[dev] = n;  // racing threads store the same value
+    }
+    return n;
+}
+// Opt-in to more than 48 KB of dynamic shared memory for `func`, once per device (the attribute is per device).
+// `done` is a per-kernel-instantiation table of kMaxDevices flags.
+template <typename F>
+static inline bool smem_optin(F func, int bytes, bool* done)
+{
+    const int dev = current_device_index();
+    if (done[dev]) return true;
+    if (cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    done[dev] = true;
+    return true;
+}
+#endif
 
 #define RECSDK_CUDA_CHECK_LAUNCH()                      \
     do {                                                \
@@ -67,7 +105,7 @@ __device__ __forceinline__ float* shard_base(const recsdk_sample_shards& sh, int
 static inline int grid_for(int64_t work, int64_t per_block, int max_blocks_per_sm = 16)
 {
     int64_t b = ceil_div(work, per_block);
-    int64_t cap = static_cast<int64_t>(kNumSMs) * max_blocks_per_sm;
+    int64_t cap = static_cast<int64_t>(num_sms()) * max_blocks_per_sm;
     if (b < 1) b = 1;
     return static_cast<int>(b < cap ? b : cap);
 }

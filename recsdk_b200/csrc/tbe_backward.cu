@@ -83,10 +83,26 @@ __device__ __forceinline__ int64_t feature_of_position(const int64_t* offs, int6
     return lo;
 }
 
+// Features that share a table put gradient rows of different column offsets into ONE run, so the 128-bit path
+// is taken only when the column offset of EVERY feature is a multiple of four floats.  Block 0 of the expand
+// kernel checks that and raises counters[3] (zeroed before the plan) when one is not.
+__device__ __forceinline__ void flag_unaligned_columns(const BwdParams& p, int64_t* counters_rw)
+{
+    if (blockIdx.x != 0) return;
+    bool bad = false;
+    for (int64_t t = threadIdx.x; t < p.T; t += blockDim.x) {
+        const int32_t c = p.sh.num_shards > 0 ? p.sh.col_offsets[t] : p.dofs[t];
+        bad = bad || ((c | (p.dofs[t + 1] - p.dofs[t])) & 3) != 0;
+    }
+    if (bad) atomicCAS(reinterpret_cast<unsigned long long*>(counters_rw + 3), 0ull, 1ull);
+}
+
 template <typename KeyT>
 __global__ void __launch_bounds__(256) expand_pooled_kernel(BwdParams p, KeyT* __restrict__ keys,
-                                                            uint32_t* __restrict__ vals, SortHistSink sink)
+                                                            uint32_t* __restrict__ vals, SortHistSink sink,
+                                                            int64_t* __restrict__ counters_rw)
 {
+    flag_unaligned_columns(p, counters_rw);
     const int lane = threadIdx.x & 31;
     const int64_t num_bags = p.T * p.B;
     const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
@@ -123,8 +139,10 @@ __global__ void __launch_bounds__(256) expand_pooled_kernel(BwdParams p, KeyT* _
 
 template <typename KeyT>
 __global__ void __launch_bounds__(256) expand_nobag_kernel(BwdParams p, KeyT* __restrict__ keys,
-                                                           uint32_t* __restrict__ vals, SortHistSink sink)
+                                                           uint32_t* __restrict__ vals, SortHistSink sink,
+                                                           int64_t* __restrict__ counters_rw)
 {
+    flag_unaligned_columns(p, counters_rw);
     // warp-uniform trip count: the histogram sink is a warp-wide call
     for (int64_t pos0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31); pos0 < p.N;
          pos0 += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -267,11 +285,15 @@ __device__ __forceinline__ void run_geometry(const BwdParams& p, uint32_t v0, in
     wofs = p.wofs[f];
 }
 
+// 128-bit path for a run of feature f's table: needs every address the run touches 16-byte aligned, i.e. the
+// table (wofs, D), the row pitch of the gradient, and the column offsets of ALL features (counters[3], see
+// flag_unaligned_columns: a run can hold gradient rows of several features that share the table).
 __device__ __forceinline__ bool vec_ok_for(const BwdParams& p, int64_t wofs, int32_t D, int64_t f)
 {
-    if (p.sh.num_shards > 0)
-        return p.base_aligned && (((wofs | D | p.sh.col_offsets[f] | p.sh.row_stride | p.max_D) & 3) == 0);
-    return p.base_aligned && (((wofs | D | p.dofs[f] | p.total_D | p.max_D) & 3) == 0);
+    (void)f;
+    if (!p.base_aligned || p.counters[3] != 0) return false;
+    if (p.sh.num_shards > 0) return ((wofs | D | p.sh.row_stride | p.max_D) & 3) == 0;
+    return ((wofs | D | p.total_D | p.max_D) & 3) == 0;
 }
 
 // ---------------------------------------------------------------------------- 4b. chunk sums
@@ -793,16 +815,9 @@ template <int OPT, int kStages>
 static bool launch_update_staged_impl(const BwdParams& p, const RunMeta* meta, int warps, cudaStream_t st)
 {
     const size_t smem = update_staged_smem_bytes(warps, kStages, StagedArrays<OPT>::kCount, p.max_D);
-    static bool attr_set = false;  // one attribute per instantiation; setting it again is harmless
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(update_staged_kernel<OPT, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024) !=
-            cudaSuccess) {
-            (void)cudaGetLastError();
-            return false;
-        }
-        attr_set = true;
-    }
-    update_staged_kernel<OPT, kStages><<<kNumSMs * 3, warps * 32, smem, st>>>(p, meta);
+    static bool optin_done[kMaxDevices] = {false};  // one table per instantiation
+    if (!smem_optin(update_staged_kernel<OPT, kStages>, 72 * 1024, optin_done)) return false;
+    update_staged_kernel<OPT, kStages><<<num_sms() * 3, warps * 32, smem, st>>>(p, meta);
     return true;
 }
 
@@ -887,13 +902,14 @@ static int run_backward(const recsdk_tbe_backward_args* a, BwdParams p, const Bw
     if (do_plan) {
         // The plan needs the indices and the LAYOUT of the gradient, not the gradient: it can run ahead, on
         // another stream, while the forward of the same batch (or the dense part) runs.
-        cudaMemsetAsync(ws.counters, 0, 8 * sizeof(int64_t), st);  // {U, chunks, indices in chunked runs, ...}
+        cudaMemsetAsync(ws.counters, 0, 8 * sizeof(int64_t), st);  // {U, chunks, indices in chunked runs, unaligned columns, ...}
         // 1. expand; it also fills the histogram of the first sort pass
         const RadixFusedPlan plan = radix_fused_begin(N, key_bits, ws.sort_scratch, st);
         if (a->pooling_mode == RECSDK_POOL_NONE)
-            expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, ka, ws.vals_a, plan.first);
+            expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(p, ka, ws.vals_a, plan.first, ws.counters);
         else
-            expand_pooled_kernel<KeyT><<<grid_for(a->T * a->B, 8 * 32), 256, 0, st>>>(p, ka, ws.vals_a, plan.first);
+            expand_pooled_kernel<KeyT><<<grid_for(a->T * a->B, 8 * 32), 256, 0, st>>>(p, ka, ws.vals_a, plan.first,
+                                                                                        ws.counters);
         // 2. sort: per pass a scan and a scatter that fills the next pass's histogram
         const int got = radix_sort_pairs_fused<KeyT>(plan, ka, ws.vals_a, kb, ws.vals_b, N, ws.sort_scratch, st);
         if (got != which) return RECSDK_ERR_CUDA;  // cannot happen: both follow radix_plan
@@ -915,11 +931,9 @@ static int run_backward(const recsdk_tbe_backward_args* a, BwdParams p, const Bw
     }
     // 5. update
     if (a->ev_update_start) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_update_start), st);
-#ifndef RECSDK_SKIP_UPDATE
 #define CALL_UPDATE(G, K) launch_update<G, K>(p, ws.meta, N, st)
     RECSDK_DISPATCH_GK(vec_per_row, CALL_UPDATE);
 #undef CALL_UPDATE
-#endif
     if (a->ev_update_stop) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_update_stop), st);
     RECSDK_CUDA_CHECK_LAUNCH();
     return RECSDK_OK;

@@ -244,10 +244,8 @@ __global__ void __launch_bounds__(256) tbe_forward_nobag_kernel(FwdParams p)
 }
 
 #ifndef RECSDK_EMULATE  // host side: not part of host-side SIMT emulation builds (tests/emu)
-static bool g_leave_room = false;  // set per call before launch_pooled (host-side, same thread)
-
 template <int G, int K>
-static void launch_pooled(const FwdParams& p, cudaStream_t st)
+static void launch_pooled(const FwdParams& p, bool leave_room, cudaStream_t st)
 {
     const int groups_per_block = 256 / G;
     // several waves of short-lived blocks rather than one resident wave: when the backward's index kernels run
@@ -255,11 +253,10 @@ static void launch_pooled(const FwdParams& p, cudaStream_t st)
     // per benchmark step, 8: 0.838, 2: 0.873; alone the grid size makes no difference)
     int grid = grid_for(ceil_div(p.T * p.B, G), groups_per_block, 16);
     size_t smem = 0;
-    if (g_leave_room) {
+    if (leave_room) {
         // unused dynamic shared memory as an occupancy limit: 60 KB per block -> three blocks per SM
-        static bool attr_ok = cudaFuncSetAttribute(tbe_forward_pooled_kernel<G, K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   60 * 1024) == cudaSuccess;
-        if (attr_ok) smem = 60 * 1024; else (void)cudaGetLastError();
+        static bool optin_done[kMaxDevices] = {false};
+        if (smem_optin(tbe_forward_pooled_kernel<G, K>, 60 * 1024, optin_done)) smem = 60 * 1024;
     }
     tbe_forward_pooled_kernel<G, K><<<grid, 256, smem, st>>>(p);
 }
@@ -296,7 +293,7 @@ extern "C" int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream
                 aligned16(a->dev_weights) ? 1 : 0, sh};
     const int vec_per_row = (a->max_D + 3) / 4;
     const int G = group_lanes_for(vec_per_row);
-    g_leave_room = (a->flags & RECSDK_FWD_LEAVE_ROOM) != 0;
+    const bool leave_room = (a->flags & RECSDK_FWD_LEAVE_ROOM) != 0;
     if (a->pooling_mode == RECSDK_POOL_NONE) {
         if (a->N == 0) return RECSDK_OK;
         switch (G) {
@@ -309,15 +306,15 @@ extern "C" int recsdk_tbe_forward(const recsdk_tbe_forward_args* a, void* stream
         }
     } else {
         switch (G) {
-            case 1: launch_pooled<1, 1>(p, st); break;
-            case 2: launch_pooled<2, 1>(p, st); break;
-            case 4: launch_pooled<4, 1>(p, st); break;
-            case 8: launch_pooled<8, 1>(p, st); break;
-            case 16: launch_pooled<16, 1>(p, st); break;
+            case 1: launch_pooled<1, 1>(p, leave_room, st); break;
+            case 2: launch_pooled<2, 1>(p, leave_room, st); break;
+            case 4: launch_pooled<4, 1>(p, leave_room, st); break;
+            case 8: launch_pooled<8, 1>(p, leave_room, st); break;
+            case 16: launch_pooled<16, 1>(p, leave_room, st); break;
             default:
-                if (vec_per_row <= 32) launch_pooled<32, 1>(p, st);
-                else if (vec_per_row <= 64) launch_pooled<32, 2>(p, st);
-                else launch_pooled<32, 4>(p, st);
+                if (vec_per_row <= 32) launch_pooled<32, 1>(p, leave_room, st);
+                else if (vec_per_row <= 64) launch_pooled<32, 2>(p, leave_room, st);
+                else launch_pooled<32, 4>(p, leave_room, st);
                 break;
         }
     }

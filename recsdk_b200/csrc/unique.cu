@@ -135,7 +135,6 @@ constexpr size_t kUniqueStaticBytes = size_t(8) << 20;  // >= carve_unique(kUniq
 
 static __device__ __align__(256) unsigned char g_unique_static_scratch[kUniqueStaticBytes];
 
-constexpr int kMaxDevices = 64;
 static std::mutex g_unique_static_mu;
 static void* g_unique_static_ptr[kMaxDevices] = {nullptr};
 

@@ -64,7 +64,8 @@ extern "C" int emu_tbe_backward(const float* grad, float* w, float* m1, float* m
                        reinterpret_cast<uintptr_t>(m2)) & 15) == 0;
     // 1. expand (emulated)
     std::vector<uint32_t> keys(N), vals(N);
-    run_grid(grid, block, [&] { expand_pooled_kernel<uint32_t>(p, keys.data(), vals.data(), SortHistSink{}); });
+    std::vector<int64_t> counters(8, 0);
+    run_grid(grid, block, [&] { expand_pooled_kernel<uint32_t>(p, keys.data(), vals.data(), SortHistSink{}, counters.data()); });
     // 2.-3. stable sort by key, run starts (host)
     std::vector<int> order(N);
     std::iota(order.begin(), order.end(), 0);
@@ -76,7 +77,6 @@ extern "C" int emu_tbe_backward(const float* grad, float* w, float* m1, float* m
         if (i == 0 || skeys[i] != skeys[i - 1]) run_start.push_back(static_cast<int>(i));
     const int64_t U = static_cast<int64_t>(run_start.size());
     run_start.push_back(static_cast<int>(N));
-    std::vector<int64_t> counters(8, 0);
     counters[0] = U;
     const size_t max_chunks = 2 * static_cast<size_t>(N) / kChunk + 2;
     std::vector<RunMeta> meta(U > 0 ? U : 1);

@@ -8,7 +8,8 @@ import re
 
 import torch
 
-REF = os.environ.get("RECSDK_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+_REPO = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REF = os.environ.get("RECSDK_REFERENCE_ROOT") or os.path.join(os.path.dirname(_REPO), "reference")
 SRC = os.path.join(REF, "cust_op", "framework", "torch_plugin", "torch_library", "2.6.0",
                    "split_embedding_codegen_forward_unweighted")
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "op_schemas.txt")

@@ -82,3 +82,41 @@ def test_emulated_backward_matches_oracle(emu, case, mode, opt):
         np.testing.assert_array_equal(m1, em1)
     if opt == 2:
         np.testing.assert_array_equal(m2, em2)
+
+
+@pytest.mark.parametrize("opt", [1, 2, 3])
+def test_emulated_backward_shared_table_unaligned_columns(emu, opt):
+    """Features [A, B, A, C] with dims 8, 6, 8, 2: table A's rows could be moved 128 bits at a time, but feature 2's
+    gradient columns start at 14, and a run of table A holds gradient rows of features 0 AND 2.  The kernels must
+    fall back to the scalar path for every run (a float4 load at column 14 is misaligned on the GPU)."""
+    rng = np.random.default_rng(77)
+    rows, dims, ftm, B = [30, 20, 10], [8, 6, 2], [0, 1, 0, 2], 19
+    T = len(ftm)
+    table_wo = np.concatenate([[0], np.cumsum([r * d for r, d in zip(rows, dims)])]).astype(np.int64)
+    table_hs = np.concatenate([[0], np.cumsum(rows)]).astype(np.int64)
+    wo = np.array([table_wo[t] for t in ftm], np.int64)
+    fd = [dims[t] for t in ftm]
+    do = np.concatenate([[0], np.cumsum(fd)]).astype(np.int32)
+    hs = np.array([table_hs[t] for t in ftm] + [table_hs[-1]], np.int64)
+    lens = rng.integers(0, 4, size=T * B)
+    idx = np.concatenate([rng.integers(0, min(6, rows[ftm[i // B]]), size=lens[i]) for i in range(T * B)]).astype(np.int64)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    total_D, max_D = int(do[-1]), max(fd)
+    grad = rng.standard_normal((B, total_D)).astype(np.float32)
+    w = rng.uniform(-1, 1, int(table_wo[-1])).astype(np.float32)
+    m1 = np.full_like(w, 0.1)
+    m2 = rng.uniform(0, 0.01, w.size).astype(np.float32)
+    ew, em1, em2 = w.copy(), m1.copy(), m2.copy()
+    status = np.zeros(4, np.int64)
+    port.tbe_backward(grad, ew, em1, em2, wo.copy(), do, hs, idx, offs, T, B, total_D, max_D, 0, opt, 0.05, 1e-8, 0.9,
+                      0.999, 1, reduce_chunk=64)
+    b2s = port.adam_beta2sqrt(0.9, 0.999, 1) if opt == 2 else 0.0
+    rc = emu.emu_tbe_backward(_ptr(grad), _ptr(w), _ptr(m1), _ptr(m2), _ptr(wo), _ptr(do), _ptr(hs), _ptr(idx),
+                              _ptr(offs), T, B, idx.size, total_D, max_D, 0, opt, 64, 0.05, 1e-8, 0.9, 0.999, b2s,
+                              w.size, _ptr(status), 2, 1, 2, 64)
+    assert rc == 0 and status[0] == 0
+    np.testing.assert_array_equal(w, ew)
+    if opt != 3:
+        np.testing.assert_array_equal(m1, em1)
+    if opt == 2:
+        np.testing.assert_array_equal(m2, em2)

@@ -149,6 +149,9 @@ BWD_CASES = [
     dict(rows=[90, 60], dims=[6, 10], B=11, max_len=4),
     dict(rows=[100, 200], dims=[16, 16], B=20, max_len=5, feature_table_map=[0, 0, 1]),
     dict(rows=[20, 100], dims=[256, 256], B=70, max_len=4),
+    # features 0 and 2 share table 0 (dim 8) but feature 2's gradient columns start at 14: one run holds gradient
+    # rows of both, so the whole call must take the scalar path
+    dict(rows=[60, 40, 30], dims=[8, 6, 2], B=25, max_len=4, feature_table_map=[0, 1, 0, 2]),
 ]
 
 
