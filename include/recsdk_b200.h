@@ -445,6 +445,76 @@ RECSDK_API int recsdk_peer_release(void* imported_ptr, int64_t offset);
  * rank's buffer, or a push into it). */
 RECSDK_API int recsdk_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
 
+/* =========================================================================
+ * Dedup exchange: the sharded lookup driven from the device over peer mappings.
+ * Replaces, for the tables sharded over the GPUs of one box, the reference's exchange steps around the lookup:
+ * the id / row / gradient all-to-alls of the table-wise and row-wise paths
+ * (hybrid_torchrec/hybrid_torchrec/distributed/sharding/hybrid_tw_sharding.py:43-82, hybrid_rw_sharding.py,
+ * embeddingbag.py:550-593) and the fused collectives they map to on the reference's hardware: GatherAll
+ * (cust_op/ascendc_op/ai_core_op/lccl/v220/op_kernel/gather_all.h) and AllUss = all-to-all + unsorted segment sum
+ * (all2all_uss.h:319-381; deterministic order all_uss_deterministic.h:102-121: contributions of one row are added
+ * in source-rank order, golden cust_op/test/lccl_op_test/tf/all2all_uss.py:213-216).
+ *
+ * Every rank keeps ONE flat table of its rows (equal dim D) and owns the linear rows
+ * [rank_base[r], rank_base[r+1]) of a global row numbering:
+ *   table-wise: linear row = part_base[f] + id            (part_base [F]; tables ordered by owner)
+ *   row-wise:   linear row = part_base[(id % W)*F + f] + id / W   (part_base [W*F]; bucketize.cpp:44-48)
+ * One step, per rank, no host read and no allocation anywhere:
+ *   forward         sort-dedup of this rank's ids on the linear row (grouped by owner) -> the distinct ids and their
+ *                   count are stored into each owner's inbox (peer stores) -> the distinct rows are read straight from
+ *                   the owners' tables (peer loads) -> pooled locally with the forward kernel.
+ *   backward_local  per distinct row the sum of the bag gradients that used it (the forward's sort is the plan), stored
+ *                   straight into the owner's gradient inbox (peer stores).
+ *   -- fence: every rank's stores have landed (a stream-ordered collective on the caller's side) --
+ *   backward_owner  reads the counts FROM DEVICE MEMORY, merges the lists of all source ranks (sort on the local row,
+ *                   contributions of one row in source-rank order), applies the optimizer once per row.
+ *   -- fence before the next forward reads the tables --
+ * No kernel waits on another GPU; loads and stores on peer mappings are plain ld/st (no multicast object).
+ * With world == 1 (or several logical ranks of one process whose "peer" pointers are local) the same code runs on
+ * one GPU.
+ * ========================================================================= */
+#define RECSDK_XCHG_TABLE_WISE 0
+#define RECSDK_XCHG_ROW_WISE 1
+typedef struct {
+    int32_t world, rank;
+    int32_t partition; /* RECSDK_XCHG_* */
+    int32_t D;         /* row width, multiple of 4 */
+    int64_t F, B;      /* features and samples of THIS rank's batch */
+    int64_t max_ids;   /* capacity: the largest number of ids one step of this rank holds */
+    int64_t inbox_cap; /* rows one source rank may ask of one owner per step (worst case: all its ids) */
+    int32_t key_bits;  /* bits of rank_base[world] */
+    int32_t reserved;
+    const int64_t* part_base;  /* device, see above */
+    const int64_t* rank_base;  /* device [world+1] */
+    const int64_t* table_rows; /* device [F] rows of table f (ids are checked against it), or NULL */
+    int64_t local_rows;        /* rows of this rank's flat table */
+    /* index r = rank r's buffer as addressed from THIS process (own buffers: plain pointers) */
+    const float* tables[RECSDK_MAX_SHARDS]; /* [local_rows_r * D] weights                           */
+    int64_t* inbox_ids[RECSDK_MAX_SHARDS];  /* [world * inbox_cap]  local row numbers, by source    */
+    int64_t* inbox_counts[RECSDK_MAX_SHARDS]; /* [world]                                            */
+    float* inbox_grads[RECSDK_MAX_SHARDS];  /* [world * inbox_cap * D] per-row gradient sums        */
+    void* workspace; /* local scratch, recsdk_xchg_workspace_bytes(); holds the plan between the calls of a step */
+    size_t workspace_bytes;
+    int64_t* dev_status; /* optional */
+} recsdk_xchg_t;
+RECSDK_API size_t recsdk_xchg_workspace_bytes(int64_t max_ids, int64_t inbox_cap, int32_t world, int32_t D, int64_t F);
+/* indices [N], offsets [F*B+1] feature-major, out [B, F*D] (NONE: [N, D]).  pooling_mode RECSDK_POOL_*. */
+RECSDK_API int recsdk_xchg_forward(const recsdk_xchg_t* x, const int64_t* indices, const int64_t* offsets, int64_t N,
+                                   int32_t pooling_mode, float* out, void* stream);
+/* grad_output [B, F*D] (NONE: [N, D]) of the batch of the preceding recsdk_xchg_forward (same offsets). */
+RECSDK_API int recsdk_xchg_backward_local(const recsdk_xchg_t* x, const float* grad_output, const int64_t* offsets,
+                                          int64_t N, int32_t pooling_mode, int32_t gradient_clipping,
+                                          float max_gradient, void* stream);
+/* Updates this rank's table in place from its inbox.  ev_update_*: optional cudaEvent_t recorded around the row-update
+ * kernel. */
+RECSDK_API int recsdk_xchg_backward_owner(const recsdk_xchg_t* x, float* weights, float* momentum1, float* momentum2,
+                                          int32_t optimizer, float learning_rate, float eps, float beta1, float beta2,
+                                          int64_t iter, void* ev_update_start, void* ev_update_stop, void* stream);
+/* Plan counters of the most recent step, copied to host memory: out[0] distinct rows this rank asked for, out[1] ids
+ * this rank received as an owner, out[2] distinct rows it updated, out[3] ids in chunked local runs.  Synchronises
+ * the stream. */
+RECSDK_API int recsdk_xchg_counters(const recsdk_xchg_t* x, int64_t* out4, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

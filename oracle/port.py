@@ -327,3 +327,129 @@ def dense_to_jagged(dense, offsets):
         n = min(int(offsets[b + 1] - offsets[b]), L)
         out[offsets[b]:offsets[b] + n] = dense[b, :n]
     return out
+
+
+# ----------------------------------------------------------------------------- sharded lookup with dedup exchange
+class ShardedDedupOracle:
+    """CPU restatement of one box's sharded lookup where each rank fetches the DISTINCT rows of its batch from
+    their owners and sends back ONE summed gradient row per distinct row (the reference's row-wise flow: local
+    unique, all2all of ids, gather on the owner, all2all of rows; backward: local segment-sum over the inverse,
+    all2all of the sums, owner-side segment-sum and optimizer = AllUss,
+    cust_op/ascendc_op/ai_core_op/lccl/v220/op_kernel/all2all_uss.h:319-381).
+
+    The order of float additions is the two-level one of the reference's deterministic mode: a rank sums the bag
+    gradients of one of its distinct rows in ascending index position (chunks of 64 for longer runs, as everywhere
+    in this oracle); the owner then adds the per-rank sums of one row in SOURCE-RANK order starting from 0.0f
+    (all_uss_deterministic.h:102-121; golden `expect_uss[value] += all2all[i]` over rank-major rows,
+    cust_op/test/lccl_op_test/tf/all2all_uss.py:213-216) and applies the optimizer once.
+
+    Placement: "table" = whole tables on ranks (`owner[f]`), "row" = row id on rank id % W at local row id // W
+    (hybrid_torchrec/src/ids_process/bucketize.cpp:44-48).  State is kept per rank as one flat array, tables in
+    (owner, table) order for "table", table after table for "row"."""
+
+    def __init__(self, rows, dim, world, partition, owner=None, optimizer=2, lr=0.01, eps=1e-8, beta1=0.9,
+                 beta2=0.999, initial_accumulator_value=0.0):
+        self.rows, self.D, self.W, self.partition = [int(r) for r in rows], int(dim), int(world), partition
+        self.F = len(self.rows)
+        self.opt, self.hp = optimizer, (lr, eps, beta1, beta2)
+        W, F = self.W, self.F
+        if partition == "table":
+            self.owner = [int(o) for o in owner]
+            order = sorted(range(F), key=lambda f: (self.owner[f], f))
+            self.base = [0] * F  # row 0 of table f inside its owner's flat table
+            n_local = [0] * W
+            for f in order:
+                self.base[f] = n_local[self.owner[f]]
+                n_local[self.owner[f]] += self.rows[f]
+        else:
+            self.local = [[max((self.rows[f] - r + W - 1) // W, 0) for f in range(F)] for r in range(W)]
+            self.base_rf = [[sum(self.local[r][:f]) for f in range(F)] for r in range(W)]
+            n_local = [sum(self.local[r]) for r in range(W)]
+        self.n_local = [max(n, 1) for n in n_local]
+        self.w = [np.zeros(n * self.D, np.float32) for n in self.n_local]
+        self.m1 = [np.full(n * self.D, initial_accumulator_value, np.float32) for n in self.n_local]
+        self.m2 = [np.zeros(n * self.D, np.float32) for n in self.n_local]
+        self.it = 0
+
+    def place(self, f, idx):
+        """(owner rank, local row) of row `idx` of table f."""
+        idx = _i64(idx)
+        if self.partition == "table":
+            return np.full(idx.shape, self.owner[f], np.int64), self.base[f] + idx
+        r = idx % self.W
+        return r, np.array([self.base_rf[int(rr)][f] for rr in r.reshape(-1)], np.int64).reshape(idx.shape) + idx // self.W
+
+    def load_table(self, f, weights):
+        """Distribute a whole table [rows_f, D] over the ranks' flat arrays."""
+        weights = np.ascontiguousarray(weights, np.float32).reshape(self.rows[f], self.D)
+        r, lrow = self.place(f, np.arange(self.rows[f]))
+        for rank in range(self.W):
+            sel = r == rank
+            self.w[rank].reshape(-1, self.D)[lrow[sel]] = weights[sel]
+
+    def _keys(self, indices, offsets, B):
+        """Per position: (owner, local row) and the feature."""
+        N = indices.size
+        feat = np.searchsorted(offsets[B::B], np.arange(N), side="right") if N else np.empty(0, np.int64)
+        own, lrow = np.empty(N, np.int64), np.empty(N, np.int64)
+        for f in range(self.F):
+            sel = feat == f
+            own[sel], lrow[sel] = self.place(f, indices[sel])
+        return own, lrow
+
+    def step(self, batches, grads, B, pooling_mode=0):
+        """batches[q] = (indices, offsets) of rank q's samples, grads[q] their upstream gradient.  Returns the pooled
+        outputs per rank; updates the state in place."""
+        W, F, D = self.W, self.F, self.D
+        lr, eps, b1, b2 = self.hp
+        zeros_F = np.zeros(F, np.int64)
+        do = (np.arange(F + 1) * D).astype(np.int32)
+        outs, sends = [], []
+        for q in range(W):
+            idx, offs = _i64(batches[q][0]), _i64(batches[q][1])
+            N = idx.size
+            own, lrow = self._keys(idx, offs, B)
+            rank_span = int(max(self.n_local)) + 1
+            lin = own * rank_span + lrow  # grouped by owner, ascending local row inside
+            uniq, inv = np.unique(lin, return_inverse=True)
+            U = uniq.size
+            u_own, u_lrow = uniq // rank_span, uniq % rank_span
+            fetched = np.zeros((max(U, 1), D), np.float32)
+            for r in range(W):
+                sel = u_own == r
+                fetched[:U][sel] = self.w[r].reshape(-1, D)[u_lrow[sel]]
+            # pooled locally over the fetched rows: same rows in the same order as a lookup in the whole tables
+            outs.append(tbe_forward(fetched.reshape(-1), zeros_F, do, inv, offs, F, B, F * D, D, pooling_mode))
+            # per distinct row: sum of its bag gradients in position order (chunks of 64); SGD with lr = -1 on zeros
+            # leaves 0 + g * 1 = the sum itself
+            gsum = np.zeros(max(U, 1) * D, np.float32)
+            if N:
+                tbe_backward(grads[q], gsum, None, None, zeros_F, do, np.array([0] * F + [U], np.int64), inv, offs, F, B,
+                             F * D, D, pooling_mode, 3, -1.0, reduce_chunk=64)
+            sends.append((u_own, u_lrow, gsum.reshape(-1, D)[:U]))
+        self.it += 1
+        for r in range(W):
+            # the owner sees the lists of all source ranks, rank-major; NONE pooling with one feature per source
+            # rank, all mapped to its one table: contributions of a row are summed in ascending position
+            ids_in = [sends[q][1][sends[q][0] == r] for q in range(W)]
+            g_in = [sends[q][2][sends[q][0] == r] for q in range(W)]
+            counts = np.array([a.size for a in ids_in], np.int64)
+            if counts.sum() == 0:
+                continue
+            idx_in = np.concatenate(ids_in)
+            grad_in = np.ascontiguousarray(np.concatenate(g_in), np.float32)
+            offs_in = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+            tbe_backward(grad_in, self.w[r], self.m1[r] if self.opt != 3 else None,
+                         self.m2[r] if self.opt == 2 else None, np.zeros(W, np.int64),
+                         (np.arange(W + 1) * D).astype(np.int32), np.array([0] * W + [self.n_local[r]], np.int64),
+                         idx_in, offs_in, W, 1, W * D, D, 2, self.opt, lr, eps, b1, b2, self.it, reduce_chunk=64)
+        return outs
+
+    def table(self, f):
+        """The whole table f gathered back from the ranks."""
+        r, lrow = self.place(f, np.arange(self.rows[f]))
+        out = np.empty((self.rows[f], self.D), np.float32)
+        for rank in range(self.W):
+            sel = r == rank
+            out[sel] = self.w[rank].reshape(-1, self.D)[lrow[sel]]
+        return out

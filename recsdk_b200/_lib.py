@@ -80,6 +80,19 @@ class FilterT(C.Structure):
     ]
 
 
+XCHG_TABLE_WISE, XCHG_ROW_WISE = 0, 1
+
+
+class XchgT(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("partition", C.c_int32), ("D", C.c_int32), ("F", C.c_int64),
+        ("B", C.c_int64), ("max_ids", C.c_int64), ("inbox_cap", C.c_int64), ("key_bits", C.c_int32),
+        ("reserved", C.c_int32), ("part_base", vp), ("rank_base", vp), ("table_rows", vp), ("local_rows", C.c_int64),
+        ("tables", vp * MAX_SHARDS), ("inbox_ids", vp * MAX_SHARDS), ("inbox_counts", vp * MAX_SHARDS),
+        ("inbox_grads", vp * MAX_SHARDS), ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
+    ]
+
+
 # symbol -> (restype, argtypes); every symbol include/recsdk_b200.h declares
 SIGNATURES = {
     "recsdk_status_clear": (C.c_int, [vp, vp]),
@@ -113,6 +126,12 @@ SIGNATURES = {
     "recsdk_peer_import": (C.c_int, [vp, C.c_int64, C.POINTER(vp)]),
     "recsdk_peer_release": (C.c_int, [vp, C.c_int64]),
     "recsdk_peer_copy": (C.c_int, [vp, vp, C.c_size_t, vp]),
+    "recsdk_xchg_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int64]),
+    "recsdk_xchg_forward": (C.c_int, [C.POINTER(XchgT), vp, vp, C.c_int64, C.c_int32, vp, vp]),
+    "recsdk_xchg_backward_local": (C.c_int, [C.POINTER(XchgT), vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_float, vp]),
+    "recsdk_xchg_backward_owner": (C.c_int, [C.POINTER(XchgT), vp, vp, vp, C.c_int32, C.c_float, C.c_float, C.c_float,
+                                             C.c_float, C.c_int64, vp, vp, vp]),
+    "recsdk_xchg_counters": (C.c_int, [C.POINTER(XchgT), C.POINTER(C.c_int64), vp]),
     "recsdk_mapper_table_bytes": (C.c_size_t, [C.c_int64]),
     "recsdk_mapper_init": (C.c_int, [C.POINTER(MapperT), vp]),
     "recsdk_mapper_workspace_bytes": (C.c_size_t, [C.c_int64]),

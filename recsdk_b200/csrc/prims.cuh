@@ -123,12 +123,23 @@ static inline void device_scan(const int* in, int* out, int64_t n, int* scratch,
 }
 
 // Functor form of the scan: the input is computed on the fly (`in(i)` -> int) and
-// the result is consumed on the fly (`out(i, item, prefix)`), so flag arrays and
+// the result is consumed on the fly (`out(i, item, prefix, n)`), so flag arrays and
 // the kernels that would write/read them disappear.
+// `n_dev` (optional, device): the number of items when only the device knows it; `n` is then the capacity the
+// grid was sized for and items at or past *n_dev do not exist.
+__device__ __forceinline__ int64_t effective_n(int64_t n, const int64_t* __restrict__ n_dev)
+{
+    if (n_dev == nullptr) return n;
+    const int64_t d = *n_dev;
+    return d < n ? (d < 0 ? 0 : d) : n;
+}
+
 template <typename InFn>
-__global__ void __launch_bounds__(kScanThreads) scan_reduce_fn_kernel(InFn in, int64_t n, int* __restrict__ tile_sums)
+__global__ void __launch_bounds__(kScanThreads) scan_reduce_fn_kernel(InFn in, int64_t n, int* __restrict__ tile_sums,
+                                                                      const int64_t* __restrict__ n_dev)
 {
     __shared__ int sm[33];
+    n = effective_n(n, n_dev);
     const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
     int s = 0;
 #pragma unroll
@@ -141,9 +152,11 @@ __global__ void __launch_bounds__(kScanThreads) scan_reduce_fn_kernel(InFn in, i
 
 template <bool INCLUSIVE, typename InFn, typename OutFn>
 __global__ void __launch_bounds__(kScanThreads) scan_apply_fn_kernel(InFn in, OutFn out, int64_t n,
-                                                                     const int* __restrict__ tile_sums)
+                                                                     const int* __restrict__ tile_sums,
+                                                                     const int64_t* __restrict__ n_dev)
 {
     __shared__ int sm[33];
+    n = effective_n(n, n_dev);
     const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
     int v[kScanItems];
     int s = 0;
@@ -157,22 +170,24 @@ __global__ void __launch_bounds__(kScanThreads) scan_apply_fn_kernel(InFn in, Ou
     int run = tile_sums[blockIdx.x] + inc - s;
 #pragma unroll
     for (int k = 0; k < kScanItems; ++k) {
-        if (base + k < n) out(base + k, v[k], INCLUSIVE ? run + v[k] : run);
+        if (base + k < n) out(base + k, v[k], INCLUSIVE ? run + v[k] : run, n);
         run += v[k];
     }
 }
 
 template <bool INCLUSIVE, typename InFn, typename OutFn>
-static inline void device_scan_fn(InFn in, OutFn out, int64_t n, int* scratch, int64_t* total_out, cudaStream_t st)
+static inline void device_scan_fn(InFn in, OutFn out, int64_t n, int* scratch, int64_t* total_out, cudaStream_t st,
+                                  const int64_t* n_dev = nullptr)
 {
     if (n <= 0) {
         if (total_out) cudaMemsetAsync(total_out, 0, sizeof(int64_t), st);
         return;
     }
     const int64_t tiles = scan_num_tiles(n);
-    scan_reduce_fn_kernel<InFn><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, n, scratch);
+    scan_reduce_fn_kernel<InFn><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, n, scratch, n_dev);
     scan_tile_sums_kernel<<<1, 1024, 0, st>>>(scratch, tiles, total_out);
-    scan_apply_fn_kernel<INCLUSIVE, InFn, OutFn><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, out, n, scratch);
+    scan_apply_fn_kernel<INCLUSIVE, InFn, OutFn><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, out, n, scratch,
+                                                                                                       n_dev);
 }
 
 // ----------------------------------------------------------------------------
@@ -268,10 +283,13 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
                                                                     uint32_t* __restrict__ vals_out, int64_t n,
                                                                     int shift, const uint32_t* __restrict__ hist,
                                                                     const uint32_t* __restrict__ totals,
-                                                                    int64_t tiles, SortHistSink next)
+                                                                    int64_t tiles, SortHistSink next,
+                                                                    const int64_t* __restrict__ n_dev)
 {
     constexpr int RADIX = 1 << BITS;
     constexpr int PER = RADIX / kSortThreads;  // digits per thread in the block-wide steps
+    n = effective_n(n, n_dev);
+    if (static_cast<int64_t>(blockIdx.x) * kSortTile >= n) return;  // block-uniform: a tile past the end has no items
     __shared__ uint32_t warp_cnt[kSortThreads / 32][RADIX];
     __shared__ int sm[33];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -353,20 +371,21 @@ static inline void radix_sort_pass(const KeyT* kin, const uint32_t* vin, KeyT* k
     sort_hist_kernel<KeyT, BITS><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, n, shift, hist, tiles);
     sort_scan_kernel<<<RADIX, 256, 0, st>>>(hist, tiles, totals);
     sort_scatter_kernel<KeyT, BITS><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(
-        kin, vin, kout, vout, n, shift, hist, totals, tiles, SortHistSink{nullptr, 0, 0, 0u});
+        kin, vin, kout, vout, n, shift, hist, totals, tiles, SortHistSink{nullptr, 0, 0, 0u}, nullptr);
 }
 
 // One pass of the fused mode: the histogram of this pass already exists (its producer filled it); the scatter
 // fills the histogram of the next pass (`next`) while it writes that pass's input.
 template <typename KeyT, int BITS>
 static inline void radix_sort_pass_fused(const KeyT* kin, const uint32_t* vin, KeyT* kout, uint32_t* vout, int64_t n,
-                                         int shift, uint32_t* hist, uint32_t* totals, SortHistSink next, cudaStream_t st)
+                                         int shift, uint32_t* hist, uint32_t* totals, SortHistSink next, cudaStream_t st,
+                                         const int64_t* n_dev)
 {
     constexpr int RADIX = 1 << BITS;
     const int64_t tiles = sort_num_tiles(n);
     sort_scan_kernel<<<RADIX, 256, 0, st>>>(hist, tiles, totals);
     sort_scatter_kernel<KeyT, BITS><<<static_cast<unsigned>(tiles), kSortThreads, 0, st>>>(kin, vin, kout, vout, n, shift,
-                                                                                          hist, totals, tiles, next);
+                                                                                          hist, totals, tiles, next, n_dev);
 }
 
 // Number of passes and bits per pass for keys of `key_bits` significant bits.
@@ -423,9 +442,12 @@ static inline RadixFusedPlan radix_fused_begin(int64_t n, int key_bits, uint32_t
 }
 template <typename KeyT>
 static inline int radix_sort_pairs_fused(const RadixFusedPlan& pl, KeyT* keys_a, uint32_t* vals_a, KeyT* keys_b,
-                                         uint32_t* vals_b, int64_t n, uint32_t* scratch, cudaStream_t st)
+                                         uint32_t* vals_b, int64_t n, uint32_t* scratch, cudaStream_t st,
+                                         const int64_t* n_dev = nullptr)
 {
-    if (n <= 1) return 0;
+    // with a device-side count the passes always run (the count is unknown here), so the result's buffer depends
+    // on the capacity only
+    if (n <= 1 && n_dev == nullptr) return 0;
     const size_t per_pass = static_cast<size_t>(pl.tiles) * (size_t(1) << pl.bits);
     uint32_t* totals = scratch + static_cast<size_t>(pl.tiles) * kMaxRadix * kMaxSortPasses;
     int cur = 0;
@@ -438,9 +460,9 @@ static inline int radix_sort_pairs_fused(const RadixFusedPlan& pl, KeyT* keys_a,
         SortHistSink next{nullptr, 0, 0, 0u};
         if (p + 1 < pl.passes) next = SortHistSink{scratch + per_pass * (p + 1), pl.tiles, (p + 1) * pl.bits, (1u << pl.bits) - 1u};
         if (pl.bits == 9)
-            radix_sort_pass_fused<KeyT, 9>(kin, vin, kout, vout, n, p * 9, hist, totals, next, st);
+            radix_sort_pass_fused<KeyT, 9>(kin, vin, kout, vout, n, p * 9, hist, totals, next, st, n_dev);
         else
-            radix_sort_pass_fused<KeyT, 8>(kin, vin, kout, vout, n, p * 8, hist, totals, next, st);
+            radix_sort_pass_fused<KeyT, 8>(kin, vin, kout, vout, n, p * 8, hist, totals, next, st, n_dev);
         cur ^= 1;
     }
     return cur;

@@ -13,8 +13,7 @@ struct SortHistSink {
     void add_warp(bool, KeyT, int64_t) const {}
 };
 }  // namespace recsdk
-#include "../../recsdk_b200/csrc/tbe_backward.cu"
-}  // namespace recsdk: the kernel file leaves it open when its host side is compiled out
+#include "../../recsdk_b200/csrc/tbe_backward.cuh"
 
 using namespace recsdk;
 

@@ -19,7 +19,7 @@ OUT = os.path.join(HERE, "emu", "build", "libemu_backward.so")
 @pytest.fixture(scope="module")
 def emu():
     os.makedirs(os.path.dirname(OUT), exist_ok=True)
-    deps = [SRC, os.path.join(HERE, "emu", "simt_emu.h"), os.path.join(ROOT, "recsdk_b200", "csrc", "tbe_backward.cu"),
+    deps = [SRC, os.path.join(HERE, "emu", "simt_emu.h"), os.path.join(ROOT, "recsdk_b200", "csrc", "tbe_backward.cuh"),
             os.path.join(ROOT, "recsdk_b200", "csrc", "common.cuh"), os.path.join(ROOT, "include", "recsdk_b200.h")]
     if not os.path.exists(OUT) or any(os.path.getmtime(d) > os.path.getmtime(OUT) for d in deps):
         subprocess.check_call(["g++", "-O1", "-std=c++17", "-pthread", "-fPIC", "-shared", "-w", "-ffp-contract=off",
