@@ -475,6 +475,10 @@ RECSDK_API int recsdk_peer_copy(void* dst, const void* src, size_t bytes, void* 
  * ========================================================================= */
 #define RECSDK_XCHG_TABLE_WISE 0
 #define RECSDK_XCHG_ROW_WISE 1
+/* flags.  ONE_HOT: the caller states that every bag holds exactly one id (checked on the device: a violation is
+ * RECSDK_ERR_INVALID_ARG in the status block).  With SUM / MEAN pooling the forward then loads every distinct row once
+ * from its owner and stores it to all bags that use it, with no intermediate copy of the fetched rows. */
+#define RECSDK_XCHG_ONE_HOT 1
 typedef struct {
     int32_t world, rank;
     int32_t partition; /* RECSDK_XCHG_* */
@@ -483,7 +487,7 @@ typedef struct {
     int64_t max_ids;   /* capacity: the largest number of ids one step of this rank holds */
     int64_t inbox_cap; /* rows one source rank may ask of one owner per step (worst case: all its ids) */
     int32_t key_bits;  /* bits of rank_base[world] */
-    int32_t reserved;
+    int32_t flags;     /* RECSDK_XCHG_ONE_HOT */
     const int64_t* part_base;  /* device, see above */
     const int64_t* rank_base;  /* device [world+1] */
     const int64_t* table_rows; /* device [F] rows of table f (ids are checked against it), or NULL */

@@ -87,7 +87,7 @@ class XchgT(C.Structure):
     _fields_ = [
         ("world", C.c_int32), ("rank", C.c_int32), ("partition", C.c_int32), ("D", C.c_int32), ("F", C.c_int64),
         ("B", C.c_int64), ("max_ids", C.c_int64), ("inbox_cap", C.c_int64), ("key_bits", C.c_int32),
-        ("reserved", C.c_int32), ("part_base", vp), ("rank_base", vp), ("table_rows", vp), ("local_rows", C.c_int64),
+        ("flags", C.c_int32), ("part_base", vp), ("rank_base", vp), ("table_rows", vp), ("local_rows", C.c_int64),
         ("tables", vp * MAX_SHARDS), ("inbox_ids", vp * MAX_SHARDS), ("inbox_counts", vp * MAX_SHARDS),
         ("inbox_grads", vp * MAX_SHARDS), ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
     ]

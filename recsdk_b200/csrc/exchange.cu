@@ -40,6 +40,7 @@ struct XchgParams {
     const int64_t* __restrict__ table_rows;
     int64_t* status;
     int32_t mode, bshift;
+    int32_t one_hot;  // the caller states that every bag holds exactly one id (checked by the expand kernel)
 };
 
 __device__ __forceinline__ int64_t xchg_key(const XchgParams& x, int64_t f, int64_t id)
@@ -80,6 +81,8 @@ __global__ void __launch_bounds__(256) xchg_expand_pooled_kernel(XchgParams x, c
         const int64_t p0 = offs[bag0], p1 = offs[last_bag];
         const uint32_t f_l = bag < num_bags ? static_cast<uint32_t>(bag / x.B) : 0u;
         const uint32_t b_l = bag < num_bags ? static_cast<uint32_t>(bag - static_cast<int64_t>(f_l) * x.B) : 0u;
+        if (x.one_hot && bag < num_bags && offs[bag + 1] - start != 1)
+            set_status(x.status, RECSDK_ERR_INVALID_ARG, bag, offs[bag + 1] - start);  // not one id per bag
         for (int64_t base = p0; base < p1; base += 32) {
             const int64_t pos = base + lane;
             int j = 0;  // largest j with start_j <= pos (empty bags share a start; the last one owns pos)
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(256) xchg_expand_pooled_kernel(XchgParams x, c
                 key = xchg_key(x, f, idx[pos]);
                 keys[pos] = static_cast<KeyT>(key);
                 vals[pos] = static_cast<uint32_t>(pos);
-                tag_of_pos[pos] = (f << x.bshift) | b;
+                if (!x.one_hot) tag_of_pos[pos] = (f << x.bshift) | b;
             }
             sink.add_warp(pos < p1, static_cast<KeyT>(key), pos);
         }
@@ -141,6 +144,8 @@ struct XchgRunOut {
     int64_t* __restrict__ inverse;
     uint32_t* __restrict__ tags_sorted;
     int64_t* __restrict__ counters;
+    int64_t one_hot_B;  // > 0: one id per bag, position p is bag (p / B, p % B); no inverse is needed
+    int32_t bshift;
     __device__ __forceinline__ void operator()(int64_t i, int flag, int incl, int64_t n) const
     {
         const int u = incl - 1;
@@ -149,8 +154,13 @@ struct XchgRunOut {
             run_start[u] = static_cast<int>(i);
             uniq[u] = static_cast<int64_t>(keys[i]);
         }
-        inverse[pos] = u;
-        tags_sorted[i] = tag_of_pos != nullptr ? tag_of_pos[pos] : pos;
+        if (one_hot_B > 0) {
+            const uint32_t f = static_cast<uint32_t>(pos / one_hot_B);
+            tags_sorted[i] = (f << bshift) | static_cast<uint32_t>(pos - f * one_hot_B);
+        } else {
+            inverse[pos] = u;
+            tags_sorted[i] = tag_of_pos != nullptr ? tag_of_pos[pos] : pos;
+        }
         if (i == n - 1) {
             run_start[incl] = static_cast<int>(n);
             counters[0] = incl;
@@ -178,17 +188,57 @@ __device__ __forceinline__ int owner_of(const int64_t* seg, int W, int64_t u)
     return r;
 }
 
-// The sorted distinct keys are grouped by owner.  Every block finds the segment bounds itself (W+1 binary
-// searches); block 0 publishes them and stores this rank's counts into the owners' inboxes.  Then G lanes per
-// distinct row: lane 0 stores the local row number into the owner's inbox, all lanes copy the row from the owner's
-// table into `fetched`, kRows rows in flight per group.
+// The sorted distinct keys are grouped by owner.  One warp finds the segment bounds (W+1 binary searches),
+// publishes them and stores this rank's counts into the owners' inboxes.
+__global__ void __launch_bounds__(32) xchg_seg_kernel(XchgParams x, const int64_t* __restrict__ uniq,
+                                                      const int64_t* __restrict__ counters,
+                                                      int64_t* __restrict__ seg_out, PeerTable<int64_t*> inbox_counts)
+{
+    __shared__ int64_t seg[RECSDK_MAX_SHARDS + 1];
+    const int64_t U = counters[0];
+    const int t = threadIdx.x;
+    if (t <= x.W) seg[t] = t == x.W ? U : lower_bound_i64(uniq, U, x.rank_base[t]);
+    __syncwarp();
+    if (t <= x.W) seg_out[t] = seg[t];
+    if (t < x.W) {
+        int64_t cnt = seg[t + 1] - seg[t];
+        if (cnt > x.cap) {
+            set_status(x.status, RECSDK_ERR_TOO_LARGE, cnt, x.cap);
+            cnt = x.cap;
+        }
+        pick(inbox_counts, t)[x.me] = cnt;
+    }
+}
+
+// Where distinct row u comes from: owner, row address in the owner's table; lane 0 of the group also stores the
+// local row number into the owner's inbox.
+struct PullSrc {
+    const float* ptr;
+};
+__device__ __forceinline__ PullSrc xchg_resolve(const XchgParams& x, const int64_t* seg, const int64_t* rbase,
+                                                const int64_t* __restrict__ uniq, int64_t u, bool store_id,
+                                                const PeerTable<const float*>& tables,
+                                                const PeerTable<int64_t*>& inbox_ids)
+{
+    PullSrc r;
+    const int o = owner_of(seg, x.W, u);
+    const int64_t lrow = uniq[u] - rbase[o];
+    const int64_t slot = u - seg[o];
+    r.ptr = nullptr;
+    if (slot < x.cap) {
+        if (store_id) pick(inbox_ids, o)[static_cast<int64_t>(x.me) * x.cap + slot] = lrow;
+        r.ptr = pick(tables, o) + lrow * x.D;
+    }
+    return r;
+}
+
+// General lookups: G lanes per distinct row copy it from the owner's table into `fetched` (the pooled gather
+// then runs over `fetched`), kRows rows in flight per group.
 template <int G>
-__global__ void __launch_bounds__(256) xchg_route_pull_kernel(XchgParams x, const int64_t* __restrict__ uniq,
-                                                              const int64_t* __restrict__ counters,
-                                                              int64_t* __restrict__ seg_out,
-                                                              float* __restrict__ fetched, PeerTable<const float*> tables,
-                                                              PeerTable<int64_t*> inbox_ids,
-                                                              PeerTable<int64_t*> inbox_counts)
+__global__ void __launch_bounds__(256) xchg_pull_kernel(XchgParams x, const int64_t* __restrict__ uniq,
+                                                        const int64_t* __restrict__ counters,
+                                                        const int64_t* __restrict__ seg_g, float* __restrict__ fetched,
+                                                        PeerTable<const float*> tables, PeerTable<int64_t*> inbox_ids)
 {
     constexpr int kRows = 4;
     __shared__ int64_t seg[RECSDK_MAX_SHARDS + 1];
@@ -196,20 +246,9 @@ __global__ void __launch_bounds__(256) xchg_route_pull_kernel(XchgParams x, cons
     const int64_t U = counters[0];
     if (threadIdx.x <= x.W) {
         rbase[threadIdx.x] = x.rank_base[threadIdx.x];
-        seg[threadIdx.x] = threadIdx.x == x.W ? U : lower_bound_i64(uniq, U, x.rank_base[threadIdx.x]);
+        seg[threadIdx.x] = seg_g[threadIdx.x];
     }
     __syncthreads();
-    if (blockIdx.x == 0 && threadIdx.x <= x.W) {
-        seg_out[threadIdx.x] = seg[threadIdx.x];
-        if (threadIdx.x < x.W) {
-            int64_t cnt = seg[threadIdx.x + 1] - seg[threadIdx.x];
-            if (cnt > x.cap) {
-                set_status(x.status, RECSDK_ERR_TOO_LARGE, cnt, x.cap);
-                cnt = x.cap;
-            }
-            pick(inbox_counts, threadIdx.x)[x.me] = cnt;
-        }
-    }
     const int lane = threadIdx.x % G;
     const int nvec = x.D >> 2;
     const int64_t groups_total = static_cast<int64_t>(gridDim.x) * (blockDim.x / G);
@@ -217,19 +256,8 @@ __global__ void __launch_bounds__(256) xchg_route_pull_kernel(XchgParams x, cons
     for (int64_t u0 = gid * kRows; u0 < U; u0 += groups_total * kRows) {
         const float* src[kRows];
 #pragma unroll
-        for (int j = 0; j < kRows; ++j) {
-            const int64_t u = u0 + j;
-            src[j] = nullptr;
-            if (u < U) {
-                const int r = owner_of(seg, x.W, u);
-                const int64_t lrow = uniq[u] - rbase[r];
-                const int64_t slot = u - seg[r];
-                if (slot < x.cap) {
-                    if (lane == 0) pick(inbox_ids, r)[static_cast<int64_t>(x.me) * x.cap + slot] = lrow;
-                    src[j] = pick(tables, r) + lrow * x.D;
-                }
-            }
-        }
+        for (int j = 0; j < kRows; ++j)
+            src[j] = u0 + j < U ? xchg_resolve(x, seg, rbase, uniq, u0 + j, lane == 0, tables, inbox_ids).ptr : nullptr;
         for (int c = lane; c < nvec; c += G) {
             float4 v[kRows];
 #pragma unroll
@@ -241,13 +269,81 @@ __global__ void __launch_bounds__(256) xchg_route_pull_kernel(XchgParams x, cons
     }
 }
 
+// One id per bag (SUM or MEAN pooling): the pooled row of a bag IS the row of its id, so each distinct row is
+// loaded once from its owner and stored to every bag of its run -- no intermediate copy, no second pass over the
+// rows.  Work items: the distinct rows with runs of at most kDirectMax positions (G lanes each, kRows rows in flight),
+// then the chunks of the longer runs (their row is loaded once per chunk).  A bag's row is written as 0.0f + x, the
+// value a sum over the bag's single row gives.
+template <int G>
+__global__ void __launch_bounds__(256) xchg_pull_scatter_kernel(XchgParams x, const int64_t* __restrict__ uniq,
+                                                                const int64_t* __restrict__ counters,
+                                                                const int64_t* __restrict__ seg_g,
+                                                                const RunMeta* __restrict__ meta,
+                                                                const int2* __restrict__ desc,
+                                                                const int* __restrict__ chunk_row,
+                                                                const uint32_t* __restrict__ tags,
+                                                                float* __restrict__ out, PeerTable<const float*> tables,
+                                                                PeerTable<int64_t*> inbox_ids)
+{
+    constexpr int kRows = 4;
+    __shared__ int64_t seg[RECSDK_MAX_SHARDS + 1];
+    __shared__ int64_t rbase[RECSDK_MAX_SHARDS + 1];
+    const int64_t U = counters[0];
+    const int64_t n_chunks = counters[1];
+    if (threadIdx.x <= x.W) {
+        rbase[threadIdx.x] = x.rank_base[threadIdx.x];
+        seg[threadIdx.x] = seg_g[threadIdx.x];
+    }
+    __syncthreads();
+    const int lane = threadIdx.x % G;
+    const int nvec = x.D >> 2;
+    const int64_t total_D = x.F * x.D;
+    const uint32_t bmask = (1u << x.bshift) - 1u;
+    const int64_t groups_total = static_cast<int64_t>(gridDim.x) * (blockDim.x / G);
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * (blockDim.x / G) + threadIdx.x / G;
+    auto out_row = [&](uint32_t tag) { return out + static_cast<int64_t>(tag & bmask) * total_D + static_cast<int64_t>(tag >> x.bshift) * x.D; };
+    for (int64_t u0 = gid * kRows; u0 < U; u0 += groups_total * kRows) {
+        const float* src[kRows];
+        int rs[kRows], len[kRows];
+#pragma unroll
+        for (int j = 0; j < kRows; ++j) {
+            src[j] = nullptr;
+            rs[j] = len[j] = 0;
+            if (u0 + j < U) {
+                src[j] = xchg_resolve(x, seg, rbase, uniq, u0 + j, lane == 0, tables, inbox_ids).ptr;
+                const int4 hi = __ldg(reinterpret_cast<const int4*>(meta + u0 + j) + 1);
+                rs[j] = hi.x;
+                len[j] = hi.w >= 0 ? 0 : hi.y;  // chunked runs are written by the chunk items below
+            }
+        }
+        for (int c = lane; c < nvec; c += G) {
+            float4 v[kRows];
+#pragma unroll
+            for (int j = 0; j < kRows; ++j) v[j] = src[j] != nullptr ? ld_f4(src[j] + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kRows; ++j) {
+                const float4 r = add4(make_float4(0.f, 0.f, 0.f, 0.f), v[j]);
+                for (int i = 0; i < len[j]; ++i) st_f4_stream(out_row(__ldg(tags + rs[j] + i)) + 4 * c, r);
+            }
+        }
+    }
+    for (int64_t ch = gid; ch < n_chunks; ch += groups_total) {
+        const int2 be = desc[ch];
+        const float* src = xchg_resolve(x, seg, rbase, uniq, chunk_row[ch], false, tables, inbox_ids).ptr;
+        for (int c = lane; c < nvec; c += G) {
+            const float4 r = add4(make_float4(0.f, 0.f, 0.f, 0.f), src != nullptr ? ld_f4(src + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f));
+            for (int i = be.x; i < be.y; ++i) st_f4_stream(out_row(__ldg(tags + i)) + 4 * c, r);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------- backward (local) records
 // One thread per distinct row: where its sum goes (the owner's gradient inbox, slot = position inside the owner's
-// segment), its first gradient row, its run; runs longer than kChunk reserve chunk slots exactly as the fused
+// segment), its first gradient row, its run; runs longer than kDirectMax reserve chunk slots exactly as the fused
 // backward's records do.
 __global__ void __launch_bounds__(256) xchg_local_meta_kernel(BwdParams p, XchgParams x, const int64_t* __restrict__ seg_g,
                                                               int64_t* __restrict__ counters, RunMeta* __restrict__ meta,
-                                                              int2* __restrict__ desc)
+                                                              int2* __restrict__ desc, int* __restrict__ chunk_row)
 {
     __shared__ int64_t seg[RECSDK_MAX_SHARDS + 1];
     if (threadIdx.x <= x.W) seg[threadIdx.x] = seg_g[threadIdx.x];
@@ -269,8 +365,8 @@ __global__ void __launch_bounds__(256) xchg_local_meta_kernel(BwdParams p, XchgP
         m.len = len;
         m.D = x.D | (vec ? kMetaVecBit : 0);
         m.chunk_base = -1;
-        if (len > kChunk) {
-            const int c = (len + kChunk - 1) / kChunk;
+        if (len > p.direct_max) {
+            const int c = chunks_of_run(len, kChunk);
             const int base = static_cast<int>(atomicAdd(reinterpret_cast<unsigned long long*>(counters + 1),
                                                         static_cast<unsigned long long>(c)));
             atomicAdd(reinterpret_cast<unsigned long long*>(counters + 2), static_cast<unsigned long long>(len));
@@ -278,6 +374,7 @@ __global__ void __launch_bounds__(256) xchg_local_meta_kernel(BwdParams p, XchgP
             for (int k = 0; k < c; ++k) {
                 const int b0 = rs + k * kChunk;
                 desc[base + k] = make_int2(b0, b0 + kChunk < re ? b0 + kChunk : re);
+                chunk_row[base + k] = static_cast<int>(u);
             }
         }
         meta[u] = m;
@@ -344,6 +441,7 @@ struct XchgWorkspace {
     int32_t* dofs;
     RunMeta* meta;
     int2* desc;
+    int* chunk_row;
     float *partial, *fetched;
     // owner plan
     int64_t* oc;  // [8] {U, chunks, -, unaligned, ids received, ...}
@@ -363,7 +461,7 @@ static XchgWorkspace carve_xchg(void* base, int64_t max_ids, int64_t inbox_cap, 
     WorkspaceCarver c(base);
     XchgWorkspace w;
     const size_t n = static_cast<size_t>(max_ids > 0 ? max_ids : 1);
-    const size_t chunks = 2 * n / kChunk + 2;
+    const size_t chunks = chunk_slots_cap(max_ids);
     w.lc = c.take<int64_t>(8);
     w.seg = c.take<int64_t>(RECSDK_MAX_SHARDS + 1);
     w.keys_a = c.take<uint64_t>(n);
@@ -381,11 +479,12 @@ static XchgWorkspace carve_xchg(void* base, int64_t max_ids, int64_t inbox_cap, 
     w.dofs = c.take<int32_t>(static_cast<size_t>(F + 1));
     w.meta = c.take<RunMeta>(n);
     w.desc = c.take<int2>(chunks);
+    w.chunk_row = c.take<int>(chunks);
     w.partial = c.take<float>(chunks * static_cast<size_t>(D));
     w.fetched = c.take<float>(n * static_cast<size_t>(D));
     const int64_t in_cap = static_cast<int64_t>(world) * inbox_cap;
     const size_t m = static_cast<size_t>(in_cap > 0 ? in_cap : 1);
-    const size_t ochunks = 2 * m / kChunk + 2;
+    const size_t ochunks = chunk_slots_cap(in_cap);
     w.oc = c.take<int64_t>(8);
     w.lay_i64 = c.take<int64_t>(4);
     w.lay_i32 = c.take<int32_t>(4);
@@ -447,7 +546,41 @@ static XchgParams xchg_params(const recsdk_xchg_t* x, int64_t N, int32_t mode)
     q.status = x->dev_status;
     q.mode = mode;
     q.bshift = xchg_bits_for(x->B - 1 > 0 ? x->B - 1 : 1);
+    q.one_hot = (x->flags & RECSDK_XCHG_ONE_HOT) ? 1 : 0;
     return q;
+}
+
+// Parameters of the local backward phase (records, chunk sums, per-row sums).  `grad` may be NULL while only the
+// records are made (forward); the gradient must then be 16-byte aligned when it arrives, which backward_local checks.
+static BwdParams xchg_local_params(const recsdk_xchg_t* x, const XchgWorkspace& ws, const XchgParams& q, const float* grad,
+                                   const int64_t* offsets, int64_t N, int32_t mode, int32_t clip, float max_grad)
+{
+    BwdParams p{};
+    p.grad = grad;
+    p.wofs = ws.zeros_F;  // read by the chunk-sum kernel's geometry; the sums are not table rows
+    p.dofs = ws.dofs;
+    p.offs = offsets;
+    p.T = x->F;
+    p.B = x->B;
+    p.N = N;
+    p.total_D = static_cast<int32_t>(x->F * x->D);
+    p.max_D = x->D;
+    p.mode = mode;
+    p.opt = kOptStore;
+    p.bshift = q.bshift;
+    p.chunk = kChunk;
+    p.direct_max = kDirectMax;
+    p.max_grad = max_grad;
+    p.clip = clip;
+    p.status = x->dev_status;
+    p.base_aligned = aligned16(ws.partial) ? 1 : 0;
+    p.vals = ws.tags_sorted;
+    p.run_start = ws.run_start;
+    p.chunk_desc = ws.desc;
+    p.partial = ws.partial;
+    p.counters = ws.lc;
+    for (int r = 0; r < RECSDK_MAX_SHARDS; ++r) p.dst_ptrs[r] = x->inbox_grads[r < x->world ? r : 0];
+    return p;
 }
 
 template <typename KeyT>
@@ -470,7 +603,8 @@ static int xchg_forward_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, co
     const uint32_t* pos_sorted = which ? ws.vals_b : ws.vals_a;
     device_scan_fn<true>(HeadFlagIn<KeyT>{keys},
                          XchgRunOut<KeyT>{keys, pos_sorted, mode == RECSDK_POOL_NONE ? nullptr : ws.tag_of_pos,
-                                          ws.run_start, ws.uniq, ws.inverse, ws.tags_sorted, ws.lc},
+                                          ws.run_start, ws.uniq, ws.inverse, ws.tags_sorted, ws.lc,
+                                          (q.one_hot && mode != RECSDK_POOL_NONE) ? x->B : 0, q.bshift},
                          N, ws.scan_scratch, nullptr, st);
     PeerTable<const float*> tables;
     PeerTable<int64_t*> in_ids, in_counts;
@@ -480,18 +614,41 @@ static int xchg_forward_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, co
         in_ids.ptrs[r] = x->inbox_ids[s];
         in_counts.ptrs[r] = x->inbox_counts[s];
     }
+    xchg_seg_kernel<<<1, 32, 0, st>>>(q, ws.uniq, ws.lc, ws.seg, in_counts);
+    // the records of the local backward phase depend on the batch and on the LAYOUT of the gradient only: made here,
+    // they also tell the one-id-per-bag forward which runs are chunked
+    const BwdParams lp = xchg_local_params(x, ws, q, nullptr, offsets, N, mode, 0, 0.f);
+    xchg_local_meta_kernel<<<grid_for(N, 256), 256, 0, st>>>(lp, q, ws.seg, ws.lc, ws.meta, ws.desc, ws.chunk_row);
     const int G = group_lanes_for(x->D >> 2);
     // kRows rows per group and pass; several resident blocks per SM keep many peer loads in flight
     const int grid = grid_for(ceil_div(N, 4), 256 / G, 8);
+    if (q.one_hot && mode != RECSDK_POOL_NONE) {
+        switch (G) {
+#define RECSDK_PULL(GG)                                                                                                  \
+    case GG:                                                                                                             \
+        xchg_pull_scatter_kernel<GG><<<grid, 256, 0, st>>>(q, ws.uniq, ws.lc, ws.seg, ws.meta, ws.desc, ws.chunk_row,       \
+                                                           ws.tags_sorted, out, tables, in_ids);                          \
+        break
+            RECSDK_PULL(1);
+            RECSDK_PULL(2);
+            RECSDK_PULL(4);
+            RECSDK_PULL(8);
+            RECSDK_PULL(16);
+            default: RECSDK_PULL(32);
+#undef RECSDK_PULL
+        }
+        RECSDK_CUDA_CHECK_LAUNCH();
+        return RECSDK_OK;
+    }
     switch (G) {
 #define RECSDK_PULL(GG) \
-    case GG: xchg_route_pull_kernel<GG><<<grid, 256, 0, st>>>(q, ws.uniq, ws.lc, ws.seg, ws.fetched, tables, in_ids, in_counts); break
+    case GG: xchg_pull_kernel<GG><<<grid, 256, 0, st>>>(q, ws.uniq, ws.lc, ws.seg, ws.fetched, tables, in_ids); break
         RECSDK_PULL(1);
         RECSDK_PULL(2);
         RECSDK_PULL(4);
         RECSDK_PULL(8);
         RECSDK_PULL(16);
-        default: xchg_route_pull_kernel<32><<<grid, 256, 0, st>>>(q, ws.uniq, ws.lc, ws.seg, ws.fetched, tables, in_ids, in_counts); break;
+        default: RECSDK_PULL(32);
 #undef RECSDK_PULL
     }
     RECSDK_CUDA_CHECK_LAUNCH();
@@ -534,7 +691,7 @@ static int xchg_forward_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, co
 template <int G, int K>
 static void xchg_launch_partial(const BwdParams& p, int64_t n, cudaStream_t st)
 {
-    partial_kernel<G, K><<<grid_for(2 * n / kChunk + 2, 256 / G, 3), 256, 0, st>>>(p);
+    partial_kernel<G, K><<<grid_for(static_cast<int64_t>(chunk_slots_cap(n)), 256 / G, 3), 256, 0, st>>>(p);
 }
 
 template <int G, int K>
@@ -542,7 +699,8 @@ static void xchg_launch_update(const BwdParams& p, const RunMeta* meta, int64_t 
 {
     const int grid = grid_for(n, 256 / G, 4);
     switch (opt) {
-        case kOptStore: update_kernel<G, K, kOptStore><<<grid, 256, 0, st>>>(p, meta); break;
+        // the store variant needs 40 registers: six resident blocks per SM keep more gradient rows in flight
+        case kOptStore: update_kernel<G, K, kOptStore><<<grid_for(n, 256 / G, 6), 256, 0, st>>>(p, meta); break;
         case RECSDK_OPT_ADAGRAD: update_kernel<G, K, RECSDK_OPT_ADAGRAD><<<grid, 256, 0, st>>>(p, meta); break;
         case RECSDK_OPT_ADAM: update_kernel<G, K, RECSDK_OPT_ADAM><<<grid, 256, 0, st>>>(p, meta); break;
         default: update_kernel<G, K, RECSDK_OPT_SGD><<<grid, 256, 0, st>>>(p, meta); break;
@@ -575,7 +733,7 @@ static int xchg_owner_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, BwdP
                          n_dev);
     run_meta_kernel<KeyT><<<grid_for(n_cap, 256), 256, 0, st>>>(p, keys, ws.oc, ws.ometa, ws.odesc);
     const int vec_per_row = x->D >> 2;
-    if (x->world > kChunk) {  // a row has at most one contribution per source rank: chunk sums only beyond kChunk ranks
+    if (x->world > p.direct_max) {  // a row has at most one contribution per source rank: no run is longer than `world`
 #define CALL_PARTIAL(G, K) xchg_launch_partial<G, K>(p, n_cap, st)
         RECSDK_XCHG_DISPATCH_GK(vec_per_row, CALL_PARTIAL);
 #undef CALL_PARTIAL
@@ -607,6 +765,8 @@ extern "C" int recsdk_xchg_forward(const recsdk_xchg_t* x, const int64_t* indice
     if (!offsets || !out || (N > 0 && !indices)) return RECSDK_ERR_INVALID_ARG;
     if (pooling_mode != RECSDK_POOL_NONE && xchg_bits_for(x->B - 1 > 0 ? x->B - 1 : 1) + xchg_bits_for(x->F) > 32)
         return RECSDK_ERR_TOO_LARGE;
+    if ((x->flags & RECSDK_XCHG_ONE_HOT) && pooling_mode != RECSDK_POOL_NONE && N != x->F * x->B)
+        return RECSDK_ERR_INVALID_ARG;  // one id per bag was promised
     const XchgWorkspace ws = carve_xchg(x->workspace, x->max_ids, x->inbox_cap, x->world, x->D, x->F);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (x->key_bits <= 32) return xchg_forward_impl<uint32_t>(x, ws, indices, offsets, N, pooling_mode, out, st);
@@ -623,32 +783,9 @@ extern "C" int recsdk_xchg_backward_local(const recsdk_xchg_t* x, const float* g
     if (!grad_output || !offsets) return RECSDK_ERR_INVALID_ARG;
     const XchgWorkspace ws = carve_xchg(x->workspace, x->max_ids, x->inbox_cap, x->world, x->D, x->F);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!aligned16(grad_output)) return RECSDK_ERR_INVALID_ARG;  // the records made by the forward assume it
     const XchgParams q = xchg_params(x, N, pooling_mode);
-    BwdParams p{};
-    p.grad = grad_output;
-    p.wofs = ws.zeros_F;  // read by the chunk-sum kernel's geometry; the sums are not table rows
-    p.dofs = ws.dofs;
-    p.offs = offsets;
-    p.T = x->F;
-    p.B = x->B;
-    p.N = N;
-    p.total_D = static_cast<int32_t>(x->F * x->D);
-    p.max_D = x->D;
-    p.mode = pooling_mode;
-    p.opt = kOptStore;
-    p.bshift = q.bshift;
-    p.chunk = kChunk;
-    p.max_grad = max_gradient;
-    p.clip = gradient_clipping;
-    p.status = x->dev_status;
-    p.base_aligned = (aligned16(grad_output) && aligned16(ws.partial)) ? 1 : 0;
-    p.vals = ws.tags_sorted;
-    p.run_start = ws.run_start;
-    p.chunk_desc = ws.desc;
-    p.partial = ws.partial;
-    p.counters = ws.lc;
-    for (int r = 0; r < RECSDK_MAX_SHARDS; ++r) p.dst_ptrs[r] = x->inbox_grads[r < x->world ? r : 0];
-    xchg_local_meta_kernel<<<grid_for(N, 256), 256, 0, st>>>(p, q, ws.seg, ws.lc, ws.meta, ws.desc);
+    const BwdParams p = xchg_local_params(x, ws, q, grad_output, offsets, N, pooling_mode, gradient_clipping, max_gradient);
     const int vec_per_row = x->D >> 2;
 #define CALL_PARTIAL(G, K) xchg_launch_partial<G, K>(p, N, st)
     RECSDK_XCHG_DISPATCH_GK(vec_per_row, CALL_PARTIAL);
@@ -688,6 +825,7 @@ extern "C" int recsdk_xchg_backward_owner(const recsdk_xchg_t* x, float* weights
     p.mode = RECSDK_POOL_NONE;
     p.opt = optimizer;
     p.chunk = kChunk;
+    p.direct_max = kDirectMax;
     p.lr = learning_rate;
     p.eps = eps;
     p.beta1 = beta1;

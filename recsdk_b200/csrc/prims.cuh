@@ -191,8 +191,9 @@ static inline void device_scan_fn(InFn in, OutFn out, int64_t n, int* scratch, i
 }
 
 // ----------------------------------------------------------------------------
-// Stable LSD radix sort of (key, uint32 value) pairs, 8 or 9 bits per pass
-// (9 when that saves a pass, e.g. 27-bit keys: 3 passes instead of 4).
+// Stable LSD radix sort of (key, uint32 value) pairs, 8, 9 or 10 bits per pass
+// (the smallest digit that gives the fewest passes, e.g. 27-bit keys: 3 passes of
+// 9 bits instead of 4 of 8; 28..30-bit keys: 3 passes of 10 bits).
 // Per pass: tile histograms -> per-digit scan across tiles -> stable scatter
 // (warp match-any ranking).  Tile = 256 threads x 8 items; warp w owns the
 // contiguous 256 items [w*256, (w+1)*256) of the tile, taken 32 at a time, so
@@ -201,7 +202,7 @@ static inline void device_scan_fn(InFn in, OutFn out, int64_t n, int* scratch, i
 constexpr int kSortThreads = 256;
 constexpr int kSortRounds = 8;
 constexpr int kSortTile = kSortThreads * kSortRounds;  // 2048
-constexpr int kMaxRadix = 512;
+constexpr int kMaxRadix = 1024;
 
 static inline int64_t sort_num_tiles(int64_t n) { return ceil_div(n > 0 ? n : 1, kSortTile); }
 // uint32 scratch needed: histogram [radix][tiles] + digit totals [radix]
@@ -391,9 +392,17 @@ static inline void radix_sort_pass_fused(const KeyT* kin, const uint32_t* vin, K
 // Number of passes and bits per pass for keys of `key_bits` significant bits.
 static inline void radix_plan(int key_bits, int* passes, int* bits)
 {
-    const int p8 = (key_bits + 7) / 8, p9 = (key_bits + 8) / 9;
-    *bits = p9 < p8 ? 9 : 8;
-    *passes = p9 < p8 ? p9 : p8;
+    const int p8 = (key_bits + 7) / 8, p9 = (key_bits + 8) / 9, p10 = (key_bits + 9) / 10;
+    *bits = 8;
+    *passes = p8;
+    if (p9 < *passes) {
+        *bits = 9;
+        *passes = p9;
+    }
+    if (p10 < *passes) {
+        *bits = 10;
+        *passes = p10;
+    }
 }
 
 // Sorts n pairs by the key bits [0, key_bits).  Data ping-pongs between
@@ -412,7 +421,9 @@ static inline int radix_sort_pairs(KeyT* keys_a, uint32_t* vals_a, KeyT* keys_b,
         uint32_t* vin = cur ? vals_b : vals_a;
         KeyT* kout = cur ? keys_a : keys_b;
         uint32_t* vout = cur ? vals_a : vals_b;
-        if (bits == 9)
+        if (bits == 10)
+            radix_sort_pass<KeyT, 10>(kin, vin, kout, vout, n, p * 10, scratch, st);
+        else if (bits == 9)
             radix_sort_pass<KeyT, 9>(kin, vin, kout, vout, n, p * 9, scratch, st);
         else
             radix_sort_pass<KeyT, 8>(kin, vin, kout, vout, n, p * 8, scratch, st);
@@ -459,7 +470,9 @@ static inline int radix_sort_pairs_fused(const RadixFusedPlan& pl, KeyT* keys_a,
         uint32_t* hist = scratch + per_pass * p;
         SortHistSink next{nullptr, 0, 0, 0u};
         if (p + 1 < pl.passes) next = SortHistSink{scratch + per_pass * (p + 1), pl.tiles, (p + 1) * pl.bits, (1u << pl.bits) - 1u};
-        if (pl.bits == 9)
+        if (pl.bits == 10)
+            radix_sort_pass_fused<KeyT, 10>(kin, vin, kout, vout, n, p * 10, hist, totals, next, st, n_dev);
+        else if (pl.bits == 9)
             radix_sort_pass_fused<KeyT, 9>(kin, vin, kout, vout, n, p * 9, hist, totals, next, st, n_dev);
         else
             radix_sort_pass_fused<KeyT, 8>(kin, vin, kout, vout, n, p * 8, hist, totals, next, st, n_dev);

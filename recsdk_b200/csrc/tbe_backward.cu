@@ -44,7 +44,7 @@ static BwdWorkspace carve_bwd(void* base, int64_t N, int32_t max_D)
     WorkspaceCarver c(base);
     BwdWorkspace w;
     const size_t n = static_cast<size_t>(N > 0 ? N : 1);
-    const size_t max_chunks = 2 * n / kChunk + 2;
+    const size_t max_chunks = chunk_slots_cap(N);
     w.counters = c.take<int64_t>(8);
     w.keys_a = c.take<uint64_t>(n);
     w.keys_b = c.take<uint64_t>(n);
@@ -116,7 +116,7 @@ static void launch_partial(const BwdParams& p, int64_t N, cudaStream_t st)
 {
     const int groups_per_block = 256 / G;
     // one resident wave (80 registers: 3 blocks per SM)
-    const int grid = grid_for(2 * N / kChunk + 2, groups_per_block, 3);
+    const int grid = grid_for(static_cast<int64_t>(chunk_slots_cap(N)), groups_per_block, 3);
     partial_kernel<G, K><<<grid, 256, 0, st>>>(p);
 }
 
@@ -182,7 +182,7 @@ static int run_backward(const recsdk_tbe_backward_args* a, BwdParams p, const Bw
         return RECSDK_OK;
     }
     // 4b. chunk sums
-    if (a->reduce_chunk > 0) {
+    {
 #define CALL_PARTIAL(G, K) launch_partial<G, K>(p, N, st)
         RECSDK_DISPATCH_GK(vec_per_row, CALL_PARTIAL);
 #undef CALL_PARTIAL
@@ -270,6 +270,7 @@ extern "C" int recsdk_tbe_backward(const recsdk_tbe_backward_args* a, void* stre
     p.opt = a->optimizer;
     p.bshift = bshift;
     p.chunk = a->reduce_chunk;
+    p.direct_max = kDirectMax;
     p.lr = a->learning_rate;
     p.eps = a->eps;
     p.beta1 = a->beta1;

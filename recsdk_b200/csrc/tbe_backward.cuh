@@ -40,6 +40,21 @@
 namespace recsdk {
 
 constexpr int kChunk = 64;  // the only non-zero reduce_chunk supported
+// Runs of more than kDirectMax positions are summed by the chunk-sum kernel (lanes resolve the gradient rows of a
+// chunk in parallel and keep eight row loads in flight), the row-update kernel then reads one partial row per
+// chunk; shorter runs are summed inside the row-update kernel.  This routing does not touch the arithmetic: a run
+// of at most reduce_chunk positions is ONE chunk, and 0.0f + (its sequential sum) is that sum bit for bit (with
+// reduce_chunk 0 a longer run is one chunk as a whole).  Measured on the benchmark step with thresholds 8, 16, 32
+// and 64: within 2 % of each other, so the threshold is the chunk length.
+constexpr int kDirectMax = kChunk;
+// Slots of the partial buffer / chunk descriptors that n index positions can need.
+static inline size_t chunk_slots_cap(int64_t n)
+{
+    const size_t m = static_cast<size_t>(n > 0 ? n : 1);
+    return m / kChunk + m / (kDirectMax + 1) + 2;
+}
+// Chunks of a run of `len` positions that went through the chunk-sum kernel.
+__host__ __device__ __forceinline__ int chunks_of_run(int len, int chunk) { return chunk > 0 ? (len + chunk - 1) / chunk : 1; }
 
 struct BwdParams {
     const float* __restrict__ grad;
@@ -75,6 +90,7 @@ struct BwdParams {
     // kOptStore only (the dedup exchange's local phase): where the per-row sums go.  A record's row_off is then
     // (buffer number << kLocShardShift) | element offset inside that buffer; the buffers may be peer mappings.
     float* dst_ptrs[RECSDK_MAX_SHARDS];
+    int32_t direct_max;  // runs longer than this go through the chunk-sum kernel (>= kDirectMax)
 };
 
 // Internal "optimizer" of the row-update kernels: no table is read, the summed gradient of the row is stored.
@@ -468,7 +484,8 @@ struct __align__(16) RunMeta {
 };
 constexpr int32_t kMetaVecBit = 1 << 30;
 
-// A run longer than kChunk also reserves ceil(len/kChunk) slots of the partial buffer (atomic
+// A run longer than kDirectMax also reserves its chunk slots in the partial buffer -- ceil(len/reduce_chunk), or one
+// for the whole run when reduce_chunk is 0 -- (atomic
 // counter; slot numbers differ from launch to launch but a slot's content and the order in which
 // a run's slots are summed do not) and describes each chunk as [begin, end) in sorted positions.
 // counters[2] collects how many indices live in chunked runs (bandwidth accounting only).
@@ -499,15 +516,16 @@ __global__ void __launch_bounds__(256) run_meta_kernel(BwdParams p, const KeyT* 
         m.len = len;
         m.D = D | (vec_ok_for(p, wofs, D, f) ? kMetaVecBit : 0);
         m.chunk_base = -1;
-        if (p.chunk > 0 && len > kChunk) {
-            const int c = (len + kChunk - 1) / kChunk;
+        if (len > p.direct_max) {
+            const int c = chunks_of_run(len, p.chunk);
+            const int step = p.chunk > 0 ? p.chunk : len;
             const int base = static_cast<int>(atomicAdd(reinterpret_cast<unsigned long long*>(counters + 1),
                                                         static_cast<unsigned long long>(c)));
             atomicAdd(reinterpret_cast<unsigned long long*>(counters + 2), static_cast<unsigned long long>(len));
             m.chunk_base = base;
             for (int k = 0; k < c; ++k) {
-                const int b0 = rs + k * kChunk;
-                desc[base + k] = make_int2(b0, b0 + kChunk < re ? b0 + kChunk : re);
+                const int b0 = rs + k * step;
+                desc[base + k] = make_int2(b0, b0 + step < re ? b0 + step : re);
             }
         }
         meta[r] = m;
@@ -525,7 +543,7 @@ __device__ __forceinline__ void row_gradient(const BwdParams& p, const RunMeta& 
     const int rs = m.rs, re = m.rs + m.len;
     const bool chunked = m.chunk_base >= 0;
     if (chunked) {
-        const int nc = (m.len + kChunk - 1) / kChunk;
+        const int nc = chunks_of_run(m.len, p.chunk);
         int c = 0;
         for (; c + 4 <= nc; c += 4) {
             typename V::T v[4][K];

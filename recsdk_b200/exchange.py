@@ -78,7 +78,7 @@ class DedupExchange:
                  pooling_mode: PoolingMode = PoolingMode.SUM, device="cuda", learning_rate: float = 0.01,
                  eps: float = 1e-8, beta1: float = 0.9, beta2: float = 0.999, gradient_clipping: bool = False,
                  max_gradient: float = 1.0, initial_accumulator_value: float = 0.0,
-                 weights_init: Optional[tuple] = None, seed: int = 0, **_ignored):
+                 weights_init: Optional[tuple] = None, seed: int = 0, one_hot: bool = False, **_ignored):
         if not 1 <= world <= _lib.MAX_SHARDS:
             raise ValueError(f"1..{_lib.MAX_SHARDS} ranks supported")
         if dim <= 0 or dim % 4:
@@ -145,6 +145,9 @@ class DedupExchange:
         x = self._x
         x.world, x.rank, x.partition, x.D = world, rank, self._part_code, self.dim
         x.F, x.B, x.max_ids, x.inbox_cap, x.key_bits = self.F, self.B, self.max_ids, self.inbox_cap, self.key_bits
+        # one id per bag, promised by the caller and checked on the device: the forward then stores each fetched row
+        # straight to the bags that use it
+        x.flags = 1 if one_hot else 0
         x.part_base, x.rank_base, x.table_rows = (self.part_base.data_ptr(), self.rank_base.data_ptr(),
                                                    self.table_rows.data_ptr())
         x.local_rows = self.local_rows

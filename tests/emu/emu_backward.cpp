@@ -37,7 +37,7 @@ static void run_grid(int grid, int block, F kernel)
 template <int G, int K>
 static void run_partial_update(const BwdParams& p, const RunMeta* meta, int grid, int block)
 {
-    if (p.chunk > 0) run_grid(grid, block, [&] { partial_kernel<G, K>(p); });
+    run_grid(grid, block, [&] { partial_kernel<G, K>(p); });
     switch (p.opt) {
         case RECSDK_OPT_ADAGRAD: run_grid(grid, block, [&] { update_kernel<G, K, RECSDK_OPT_ADAGRAD>(p, meta); }); break;
         case RECSDK_OPT_ADAM: run_grid(grid, block, [&] { update_kernel<G, K, RECSDK_OPT_ADAM>(p, meta); }); break;
@@ -54,7 +54,7 @@ extern "C" int emu_tbe_backward(const float* grad, float* w, float* m1, float* m
     BwdParams p{};
     p.grad = grad; p.w = w; p.m1 = m1; p.m2 = m2; p.wofs = wofs; p.dofs = dofs; p.cumsum = cumsum;
     p.idx = idx; p.offs = offs; p.T = T; p.B = B; p.N = N; p.total_D = total_D; p.max_D = max_D;
-    p.mode = mode; p.opt = opt; p.chunk = chunk; p.lr = lr; p.eps = eps; p.beta1 = beta1; p.beta2 = beta2;
+    p.mode = mode; p.opt = opt; p.chunk = chunk; p.direct_max = kDirectMax; p.lr = lr; p.eps = eps; p.beta1 = beta1; p.beta2 = beta2;
     p.beta2sqrt = beta2sqrt; p.w_numel = w_numel; p.status = status;
     int bshift = 1;
     while ((int64_t(1) << bshift) <= (B - 1 > 0 ? B - 1 : 1)) ++bshift;
@@ -77,7 +77,7 @@ extern "C" int emu_tbe_backward(const float* grad, float* w, float* m1, float* m
     const int64_t U = static_cast<int64_t>(run_start.size());
     run_start.push_back(static_cast<int>(N));
     counters[0] = U;
-    const size_t max_chunks = 2 * static_cast<size_t>(N) / kChunk + 2;
+    const size_t max_chunks = chunk_slots_cap(N);
     std::vector<RunMeta> meta(U > 0 ? U : 1);
     std::vector<int2> desc(max_chunks);
     float* partial = static_cast<float*>(aligned_alloc(64, max_chunks * static_cast<size_t>(max_D) * sizeof(float)));

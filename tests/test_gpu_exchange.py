@@ -95,6 +95,43 @@ def test_exchange_loopback_bit_exact(partition, world, mode, opt):
     _run_and_compare(ranks, orc, batches, grads, B, mode)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("partition", ["row", "table"])
+def test_exchange_one_id_per_bag_path_bit_exact(partition, world, mode):
+    """The caller states one id per bag: every fetched row is stored straight to the bags of its run (short runs and
+    chunks of long runs).  Hot rows give runs far beyond the chunk length."""
+    rng = np.random.default_rng(400 + world)
+    rows, D, B = [300, 2000, 17], 64, 500
+    F = len(rows)
+    owner = [f % world for f in range(F)] if partition == "table" else None
+    ranks = _make_ranks(rows, D, world, partition, owner, B, F * B, 2, mode, inbox_cap=F * B, one_hot=True)
+    orc = port.ShardedDedupOracle(rows, D, world, partition, owner, optimizer=2, lr=0.05)
+    _load(ranks, orc, [rng.uniform(-0.1, 0.1, (r, D)).astype(np.float32) for r in rows])
+    batches = _batches(rng, rows, world, B, 1, hot=2, one_hot=True)
+    grads = [rng.standard_normal((B, F * D)).astype(np.float32) for _ in batches]
+    _run_and_compare(ranks, orc, batches, grads, B, mode)
+    assert ranks[0].counters()[3] > 0
+
+
+def test_exchange_one_id_per_bag_promise_is_checked():
+    rng = np.random.default_rng(3)
+    rows, D, B = [100], 8, 16
+    ranks = _make_ranks(rows, D, 1, "row", None, B, 3 * B, 3, 0, inbox_cap=3 * B, one_hot=True)
+    lens = np.full(B, 1, np.int64)
+    lens[5], lens[9] = 2, 0  # still B ids in total, but not one per bag: only the device can see it
+    idx = torch.from_numpy(rng.integers(0, 100, int(lens.sum())).astype(np.int64)).to(DEV)
+    offs = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)).to(DEV)
+    ranks[0].forward(idx, offs)
+    with pytest.raises(RuntimeError):
+        ranks[0].raise_if_error()
+    lens[9] = 1  # one id too many: rejected on the host
+    idx = torch.from_numpy(rng.integers(0, 100, int(lens.sum())).astype(np.int64)).to(DEV)
+    offs = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)).to(DEV)
+    with pytest.raises(RuntimeError):
+        ranks[0].forward(idx, offs)
+
+
 def test_exchange_hot_rows_long_runs_and_wide_rows():
     """Runs far longer than the chunk length on the requesting ranks (chunk sums) and rows of 128 floats."""
     rng = np.random.default_rng(5)
