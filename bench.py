@@ -47,9 +47,12 @@ HBM_BUDGET_BYTES = 150e9
 
 
 def seeded_rows():
-    from recsdk_b200.synthetic import table_rows_log_uniform
+    """The 26 row counts of configs[1]: log-uniform in [1e3, 4e7] from the seed (the same draw as
+    recsdk_b200.synthetic.table_rows_log_uniform, restated here so that the CPU arm imports nothing of the package)."""
+    import numpy as np
 
-    return table_rows_log_uniform(SEED, N_TABLES, 1e3, 4e7)
+    rng = np.random.default_rng(SEED)
+    return [int(r) for r in np.round(10 ** rng.uniform(math.log10(1e3), math.log10(4e7), N_TABLES)).astype(np.int64)]
 
 
 def measured_peak_gbs():
@@ -152,32 +155,17 @@ def run_ours(args):
     T = len(rows)
     B = BATCH * world  # a table owner sees the samples of every rank (weak scaling: BATCH per GPU)
 
-    dedup = world > 1 and args.exchange == "dedup"
     opt_kw = dict(optimizer=EmbOptimType.ADAM, pooling_mode=PoolingMode.SUM, learning_rate=LR, eps=EPS, beta1=BETA1,
                   beta2=BETA2, device=dev, weights_init=(-0.01, 0.01), seed=SEED + rank,
                   plan_ahead=not args.no_plan_ahead)
-    if dedup:
-        # the sample owners fetch the DISTINCT rows their samples need and pool locally; gradients return summed
-        # per distinct row: ids, rows and gradient rows cross in NCCL all-to-alls, ~5x fewer bytes than pooled rows
-        from recsdk_b200.rowwise import TableWiseDedupEmbeddingBag
-
-        bag = TableWiseDedupEmbeddingBag([rows_all[t] for t in sh.output_table_order], DIM,
-                                         [sh.owner[t] for t in sh.output_table_order], world, rank, **opt_kw)
-        # rows pulled out of peer-mapped buffers instead of the two row all-to-alls: measured better at 2 GPUs
-        # (2.08 vs 2.32 ms/step), worse at 4 and 8 (2.63 vs 2.35, 3.24 vs 2.39: 2(W-1) small serial copies and two
-        # more fences per step), so it is off unless asked for
-        if os.environ.get("RECSDK_DEDUP_PEER_PULL"):
-            bag.enable_peer_pull(BATCH)
-        module = bag.owner
-    else:
-        module = HybridSplitTableBatchedEmbeddingBagsCodegen([(r, DIM) for r in rows], **opt_kw)
+    module = HybridSplitTableBatchedEmbeddingBagsCodegen([(r, DIM) for r in rows], **opt_kw)
     gen = torch.Generator(device=dev)
     gen.manual_seed(SEED + 17 * rank)
     n_batches = 4  # rotate distinct batches so consecutive steps touch different rows
     ids_per_step_rank = T * B
     out = torch.empty((B, T * DIM), device=dev, dtype=torch.float32)
     if world == 1:
-        batches = [one_hot_batch(gen, rows, B, args.zipf_alpha, dev) for _ in range(n_batches)]
+        batches = [one_hot_batch(gen, rows, B, ALPHA, dev) for _ in range(n_batches)]
         grad = torch.randn((B, T * DIM), generator=gen, device=dev, dtype=torch.float32)
     else:
         # every rank holds the ids of ITS 65536 samples for all 26 fields and the upstream gradient of its
@@ -188,11 +176,7 @@ def run_ours(args):
         batches = [torch.stack([zipf_ids(gen, BATCH, rows_all[t], ALPHA, dev) for t in sh.output_table_order])
                    .view(N_TABLES, BATCH, 1) for _ in range(n_batches)]
         owner_offsets = torch.arange(T * B + 1, dtype=torch.int64, device=dev)
-        if dedup:
-            del out
-            grad = torch.randn((BATCH, N_TABLES * DIM), generator=gen, device=dev, dtype=torch.float32)
-            local_offsets = torch.arange(N_TABLES * BATCH + 1, dtype=torch.int64, device=dev)
-        elif args.exchange == "fused":
+        if args.exchange == "fused":
             # pooled rows and gradients of this rank's samples live in peer-mapped buffers: the owners' forward
             # kernels store into them and their backward kernels read from them over NVLink
             from recsdk_b200.peer import FusedTableWiseExchange
@@ -229,22 +213,6 @@ def run_ours(args):
                 marks.append(e)
 
         mark()
-        if dedup:
-            ids_local = batches[i % n_batches] if idx_offs is None else idx_offs[0]
-            mark()
-            evs = None
-            if timed:
-                evs = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                for e in evs:
-                    e.record()
-                ev_pairs.append(evs)
-                phase_marks.append(marks)
-            last_out[0] = bag.forward(ids_local.view(-1), local_offsets)
-            mark()
-            mark()
-            bag.backward(grad, update_events=evs)
-            mark()
-            return
         idx, offs, g = owner_view(i) if idx_offs is None else (*idx_offs, grad)
         mark()
         evs = None
@@ -345,9 +313,6 @@ def run_ours(args):
                 o = module(d_idx, d_offs)  # autograd-tracked lookup; backward runs the fused optimizer
                 o.backward(grad)
                 res = o
-        elif dedup:
-            step_resident(i, idx_offs=(d_idx.long(), None))
-            res = last_out[0]
         elif fused:
             idx, offs, _ = owner_view(i, ids_local=d_idx.long())
             step_resident(i, idx_offs=(idx, offs))
@@ -417,8 +382,6 @@ def run_ours(args):
         peak, peak_kind = measured_peak_gbs()
         S = 2  # Adam state slots
         N = ids_per_step_rank
-        if dedup:
-            N = module._last_N  # the owner's update runs over the distinct rows the ranks asked for
         # algorithmic bytes of one row-update launch: per unique row read+write of w, m, v and three 4-byte
         # plan entries; per index that it reduces itself (runs of <= 64) the gradient row and its 4-byte
         # (feature, sample) tag; per chunk sum of a longer run one row of the partial buffer.  The gradient
@@ -433,10 +396,6 @@ def run_ours(args):
         passes = min(math.ceil(bits / 8), math.ceil(bits / 9))  # the sort takes 9-bit digits when that saves a pass
         # forward + expand, (scan + scatter) per sort pass, 3 run-scan kernels, records, partial sums, update
         launches_per_step = 1 + (1 + 2 * passes + 3 + 1 + 1 + 1)
-        if dedup:
-            # + sorted unique of the local ids (load, 3 launches per pass of 4, flag scan 3, write), the owner's
-            # gather, the local pooling, and a second fused backward (local per-row sums, then the owner's update)
-            launches_per_step += (1 + 3 * 4 + 3 + 1) + 1 + (1 + 2 * passes + 3 + 1 + 1 + 1)
         line = {
             "metric": "embedding ids/sec (fwd+bwd+sparse Adam)",
             "value": value,
@@ -452,8 +411,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {
                 "workload": ("configs[1]: 26 tables dim 128 fp32, batch 65536 per GPU one-hot Zipf(1.1), sparse Adam, "
-                             "table-wise sharding") if (args.profile_tables == 0 and args.zipf_alpha == ALPHA) else
-                            f"EXPERIMENT, not the benchmark: Zipf alpha {args.zipf_alpha}" if args.profile_tables == 0 else
+                             "table-wise sharding") if args.profile_tables == 0 else
                             (f"REDUCED profiling case, not the benchmark: the {T} largest tables of configs[1] with rows "
                              f"capped at {row_cap}, batch 65536, sparse Adam"),
                 "tables_this_rank": T, "rows_this_rank": sum(rows), "row_cap": row_cap,
@@ -465,9 +423,7 @@ def run_ours(args):
                 "reduce_chunk": 64,
                 "exchange": ("none (1 GPU)" if world == 1 else
                              "ids: NCCL all-to-all; pooled rows and gradients: peer stores / loads inside the "
-                             "forward / backward kernels" if fused else
-                             "distinct rows fetched by the sample owners: NCCL all-to-alls of unique ids, rows and "
-                             "per-row gradient sums" if dedup else "NCCL all-to-all x3"),
+                             "forward / backward kernels" if fused else "NCCL all-to-all x3"),
             },
             "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
             "step_hbm_frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
@@ -496,11 +452,283 @@ def run_ours(args):
         if fused:
             fx.close()
             dist.barrier()
-        if dedup:
-            bag.close()
-            dist.barrier()
         dist.destroy_process_group()
 
+
+
+
+# ============================================================================ N > 1: device-driven dedup exchange
+def exchange_parity_check(world, rank, dev):
+    """A small seeded twin of the sharded step (same kernels, same process group, same peer mappings) compared bit
+    for bit with the CPU oracle of the sharded lookup before anything is timed.  Returns "bit-exact" or a reason."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from oracle import port
+    from recsdk_b200.rowwise import TableWiseDedupEmbeddingBag
+    from recsdk_b200.tbe import EmbOptimType
+
+    rows, D, B = [3000, 500, 40, 9000, 77], 128, 256
+    F = len(rows)
+    owner = [f % world for f in range(F)]
+    rng = np.random.default_rng(77)
+    weights = [rng.uniform(-0.01, 0.01, (r, D)).astype(np.float32) for r in rows]
+    batches, grads = [], []
+    for q in range(world):
+        ids = np.concatenate([np.minimum((rng.pareto(1.1, B) * 3).astype(np.int64), rows[f] - 1) for f in range(F)])
+        batches.append((ids.astype(np.int64), np.arange(F * B + 1, dtype=np.int64)))
+        grads.append(rng.standard_normal((B, F * D)).astype(np.float32))
+    bag = TableWiseDedupEmbeddingBag(rows, D, owner, world, rank, batch_size=B, optimizer=EmbOptimType.ADAM, device=dev,
+                                     learning_rate=LR, eps=EPS, beta1=BETA1, beta2=BETA2, one_hot=True)
+    orc = port.ShardedDedupOracle(rows, D, world, "table", owner=owner, optimizer=2, lr=LR, eps=EPS, beta1=BETA1,
+                                  beta2=BETA2)
+    for f, w in enumerate(weights):
+        orc.load_table(f, w)
+    bag.weights_dev.copy_(torch.from_numpy(orc.w[rank][:bag.weights_dev.numel()]))
+    idx, offs = (torch.from_numpy(a).to(dev) for a in batches[rank])
+    g = torch.from_numpy(grads[rank]).to(dev)
+    torch.cuda.synchronize()
+    dist.barrier()
+    ok = True
+    for _ in range(2):
+        exp = orc.step(batches, grads, B, 0)
+        out = bag.forward(idx, offs)
+        bag.backward(g)
+        ok = ok and np.array_equal(out.cpu().numpy(), exp[rank])
+    n = bag.weights_dev.numel()
+    ok = ok and np.array_equal(bag.weights_dev.cpu().numpy(), orc.w[rank][:n])
+    ok = ok and np.array_equal(bag.momentum1_dev.cpu().numpy(), orc.m1[rank][:n])
+    ok = ok and np.array_equal(bag.momentum2_dev.cpu().numpy(), orc.m2[rank][:n])
+    try:
+        bag.raise_if_error()
+    except RuntimeError:
+        ok = False
+    flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.barrier()
+    bag.close()
+    dist.barrier()
+    return "bit-exact" if flag.item() == 1.0 else "MISMATCH against the oracle of the sharded lookup"
+
+
+def run_dedup_multi(args):
+    """configs[1] on N > 1 GPUs: whole tables on ranks, every rank looks up the 26 fields of ITS samples through the
+    device-driven dedup exchange (distinct rows pulled from the owners, per-row gradient sums pushed back)."""
+    import torch
+    import torch.distributed as dist
+
+    from recsdk_b200.rowwise import TableWiseDedupEmbeddingBag
+    from recsdk_b200.sharding import greedy_table_placement
+    from recsdk_b200.synthetic import zipf_ids
+    from recsdk_b200.tbe import EmbOptimType
+
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ["RANK"])
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    parity = exchange_parity_check(world, rank, dev)
+
+    rows_all = seeded_rows()
+    F = len(rows_all)
+    owner = greedy_table_placement(rows_all, [DIM] * F, world)
+    bag = TableWiseDedupEmbeddingBag(rows_all, DIM, owner, world, rank, batch_size=BATCH, optimizer=EmbOptimType.ADAM,
+                                     device=dev, learning_rate=LR, eps=EPS, beta1=BETA1, beta2=BETA2,
+                                     weights_init=(-0.01, 0.01), seed=SEED + rank, one_hot=True)
+    state_bytes = bag.local_rows * DIM * 4 * 3
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 17 * rank)
+    n_batches = 4
+    main_stream = torch.cuda.current_stream()
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def measure(B):
+        """One scaling mode: B samples per rank.  Returns a dict of timings."""
+        bag.set_batch_size(B)
+        batches = [torch.stack([zipf_ids(gen, B, rows_all[t], ALPHA, dev) for t in range(F)]).view(-1)
+                   for _ in range(n_batches)]
+        offsets = torch.arange(F * B + 1, dtype=torch.int64, device=dev)
+        grad = torch.randn((B, F * DIM), generator=gen, device=dev, dtype=torch.float32)
+        out = torch.empty((B, F * DIM), device=dev, dtype=torch.float32)
+        ev_pairs, marks_all = [], []
+
+        def step(i, timed=False, ids=None):
+            marks = []
+
+            def mark():
+                if timed:
+                    e = torch.cuda.Event(enable_timing=True)
+                    e.record()
+                    marks.append(e)
+
+            evs = None
+            if timed:
+                evs = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                for e in evs:
+                    e.record()
+                ev_pairs.append(evs)
+                marks_all.append(marks)
+            mark()
+            bag.forward(batches[i % n_batches] if ids is None else ids, offsets, out=out)
+            mark()
+            bag.backward_local(grad)
+            mark()
+            bag.fence()
+            mark()
+            bag.backward_owner(evs)
+            mark()
+            bag.fence()
+            mark()
+
+        for i in range(args.warmup):
+            step(i)
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(args.steps):
+            step(args.warmup + i, timed=True)
+        t1.record()
+        barrier()
+        ms_total = t0.elapsed_time(t1)
+        names = ("forward", "backward_local", "fence", "backward_owner", "fence2")
+        phases = {n: sum(m[k].elapsed_time(m[k + 1]) for m in marks_all) / len(marks_all) for k, n in enumerate(names)}
+        upd_ms = sum(a.elapsed_time(b) for a, b in ev_pairs) / len(ev_pairs)
+        counters = bag.counters()
+        bag.raise_if_error()
+
+        # end to end: ids of every step cross PCIe from pinned host memory (int32, widened on the device) on a copy
+        # stream, double-buffered; 16 KB of the result are read back
+        host = [b.to(torch.int32).cpu().pin_memory() for b in batches]
+        d_bufs = [torch.empty_like(batches[0], dtype=torch.int32) for _ in range(2)]
+        copy_stream = torch.cuda.Stream(device=dev)
+        copied = [torch.cuda.Event(), torch.cuda.Event()]
+        consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        result_host = torch.empty(4096, dtype=torch.float32).pin_memory()
+
+        def prefetch(i):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[i % 2])
+                d_bufs[i % 2].copy_(host[i % n_batches], non_blocking=True)
+                copied[i % 2].record(copy_stream)
+
+        def run_e2e(n):
+            for e in consumed:
+                e.record(main_stream)
+            prefetch(0)
+            for i in range(n):
+                if i + 1 < n:
+                    prefetch(i + 1)
+                main_stream.wait_event(copied[i % 2])
+                step(i, ids=d_bufs[i % 2].long())
+                consumed[i % 2].record(main_stream)
+                result_host.copy_(out.reshape(-1)[:4096], non_blocking=True)
+
+        run_e2e(max(args.warmup, 3))
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        t_issue = time.perf_counter()
+        run_e2e(args.steps)
+        issue_ms = (time.perf_counter() - t_issue) * 1e3 / args.steps
+        e1.record()
+        barrier()
+        tt = torch.tensor([ms_total, e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        cc = torch.tensor([counters[0] - counters[4]], device=dev, dtype=torch.float64)  # distinct rows that crossed
+        dist.all_reduce(cc, op=dist.ReduceOp.MAX)
+        return dict(ms_step=tt[0].item() / args.steps, e2e_ms_step=tt[1].item() / args.steps, phases=phases,
+                    upd_ms=upd_ms, counters=counters, issue_ms=issue_ms, h2d=int(host[0].numel() * 4),
+                    remote_rows_max=int(cc.item()), B=B)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    weak = measure(BATCH)
+    clocks = sampler.stop() if rank == 0 else None
+    strong = measure(BATCH // world)  # the config as written: a global batch of 65536 split over the ranks
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        S = 2
+        U_req, n_recv, U_own, n_long, U_self, n_chunks = weak["counters"]
+        ids_per_step = F * BATCH * world
+        # row update on the owner: per distinct row read+write of w, m, v and its 32-byte record; per received id
+        # one gradient row of the inbox and its 4-byte slot number
+        upd_bytes = U_own * (4 * DIM * 2 * (1 + S) + 32) + n_recv * (4 * DIM + 4)
+        achieved = upd_bytes / (weak["upd_ms"] * 1e-3) / 1e9
+        # this rank's HBM traffic by the step formula: its own N ids looked up (dedup, rows written to the pooled output,
+        # gradients read once), plus the update of the rows it owns
+        N = F * BATCH
+        step_bytes = (16 * N + 8 * U_req) + (U_req * 4 * DIM + 8 * (N + 1) + 4 * DIM * N) + \
+                     (4 * DIM * N + 8 * N + U_req * 4 * DIM) + (n_recv * (8 + 4 * DIM) + U_own * 4 * DIM * 2 * (1 + S))
+        # bytes that cross NVLink per step and GPU, each direction: one row per distinct remote row pulled in the
+        # forward, one summed gradient row per distinct remote row pushed in the backward (+ 8 bytes of id)
+        remote = weak["remote_rows_max"]
+        nv_in, nv_out = remote * DIM * 4, remote * (DIM * 4 + 8)
+        ph = weak["phases"]
+        nv_in_gbs = nv_in / (ph["forward"] * 1e-3) / 1e9
+        nv_out_gbs = nv_out / (ph["backward_local"] * 1e-3) / 1e9
+        passes = min(math.ceil(bag.key_bits / b) for b in (8, 9, 10))
+        passes_o = min(math.ceil(max(1, int(bag.local_rows).bit_length()) / b) for b in (8, 9, 10))
+        launches_per_step = (1 + 2 * passes + 3 + 3) + 2 + (1 + 2 * passes_o + 3 + 2)
+
+        def scal(m, label):
+            ids = F * m["B"] * world
+            return {"scaling": label, "batch_per_gpu": m["B"], "ids_per_step": ids, "ms_per_step": m["ms_step"],
+                    "value": ids / (m["ms_step"] * 1e-3), "e2e_value": ids / (m["e2e_ms_step"] * 1e-3),
+                    "phases_ms_rank0": m["phases"]}
+
+        line = {
+            "metric": "embedding ids/sec (fwd+bwd+sparse Adam)", "value": ids_per_step / (weak["ms_step"] * 1e-3),
+            "unit": "ids/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": weak["ms_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": "configs[1]: 26 tables dim 128 fp32, batch 65536 per GPU one-hot Zipf(1.1), sparse Adam, "
+                            "table-wise sharding",
+                "tables_this_rank": owner.count(rank), "rows_this_rank": bag.local_rows, "row_cap": None,
+                "table_state_gb_this_rank": round(state_bytes / 1e9, 1), "ids_per_step": ids_per_step,
+                "distinct_rows_requested_rank0": U_req, "ids_received_as_owner_rank0": n_recv,
+                "distinct_rows_updated_rank0": U_own,
+                "l2": "inputs larger than L2: 872 MB output + 872 MB gradient + touched rows per step; "
+                      f"{n_batches} distinct batches rotate",
+                "reduce_chunk": 64,
+                "exchange": "device-driven dedup exchange over peer mappings: distinct ids and counts stored into the "
+                            "owners' inboxes, distinct rows loaded from the owners' tables, per-row gradient sums stored "
+                            "into the owners' inboxes, counts read on the device; two one-element NCCL all-reduces per "
+                            "step as fences",
+            },
+            "parity_check": parity,
+            "step_hbm_gbs_rank0": step_bytes / (weak["ms_step"] * 1e-3) / 1e9,
+            "step_hbm_frac_of_measured_peak": step_bytes / (weak["ms_step"] * 1e-3) / 1e9 / peak,
+            "roofline": {"kernel": "update_kernel<Adam> (owner phase)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "bytes_per_launch": upd_bytes,
+                         "ms_per_launch": weak["upd_ms"], "traffic": None},
+            "nvlink": {"bytes_per_step_per_gpu": {"in": nv_in, "out": nv_out},
+                       "gbs": {"in_over_forward_phase": nv_in_gbs, "out_over_backward_local_phase": nv_out_gbs},
+                       "frac_of_900": max(nv_in_gbs, nv_out_gbs) / 900.0,
+                       "frac_of_measured_770": max(nv_in_gbs, nv_out_gbs) / 770.0,
+                       "note": "per direction; the phases also hold the sort / pooling work, so these are lower bounds "
+                               "of the link rate while rows move"},
+            "e2e": {"value": ids_per_step / (weak["e2e_ms_step"] * 1e-3), "unit": "ids/s",
+                    "ms_per_step": weak["e2e_ms_step"], "host_enqueue_ms_per_step": weak["issue_ms"],
+                    "h2d_bytes_per_step": weak["h2d"], "d2h_bytes_per_step": 4096 * 4},
+            "phases_ms_rank0": weak["phases"],
+            "strong_scaling": scal(strong, "strong: global batch 65536 split over the ranks"),
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        emit(line)
+    dist.barrier()
+    bag.close()
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 # ============================================================================ per-operator measurements
@@ -747,7 +975,7 @@ def _cpu_step(port, c, it):
 def cpu_baseline_sample(budget_s: float = 15.0):
     port, c = _cpu_sample_setup()
     cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    port.set_num_threads(cores)  # explicit: a launcher's OMP_NUM_THREADS=1 must not decide the baseline
     _cpu_step(port, c, 1)
     t0 = time.perf_counter()
     n = 0
@@ -769,7 +997,7 @@ def run_reference(args):
         return
     port, c = _cpu_sample_setup()
     cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    port.set_num_threads(cores)  # explicit: torchrun exports OMP_NUM_THREADS=1 to its workers
     for i in range(args.warmup):
         _cpu_step(port, c, i + 1)
     t0 = time.perf_counter()
@@ -820,20 +1048,18 @@ def main():
                     help="do not overlap the backward's index work (sort of the row keys, runs, per-row records) "
                          "with the forward on a side stream")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--zipf-alpha", type=float, default=ALPHA,
-                    help="1-GPU experiments only: skew of the ids (the benchmark's is 1.1; not the benchmark otherwise)")
     ap.add_argument("--profile-tables", type=int, default=0,
                     help="reduced case for profiler captures: keep only the K largest tables (1 GPU, no e2e loop)")
     ap.add_argument("--profile-row-cap", type=int, default=524288, help="row cap of the reduced case")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl", "dedup"],
-                    help="N>1: pooled rows / gradients move inside the kernels over peer mappings (fused), through "
-                         "NCCL all-to-alls (nccl, the reference's scheme), or the sample owners fetch distinct rows "
-                         "and pool locally (dedup).  auto: fused at 2 GPUs, dedup from 3 GPUs on (measured: 1.92 vs "
-                         "2.25 ms/step at 2 GPUs, 4.08 vs 2.40 at 8)")
+                    help="N>1: dedup (default) = the device-driven dedup exchange: the sample owners fetch the distinct "
+                         "rows they need from the table owners and pool locally.  Kept as baselines: pooled rows / "
+                         "gradients through NCCL all-to-alls (nccl, the reference's scheme) or stored / loaded inside "
+                         "the owners' kernels over peer mappings (fused)")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
     if args.exchange == "auto":
-        args.exchange = "fused" if int(os.environ.get("WORLD_SIZE", "1")) <= 2 else "dedup"
+        args.exchange = "dedup"
     if args.workload == "ops":
         run_ops(args)
     elif args.impl == "reference":
@@ -841,7 +1067,10 @@ def main():
     else:
         if args.warmup < 3:
             args.warmup = 3
-        run_ours(args)
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1 and args.exchange == "dedup":
+            run_dedup_multi(args)
+        else:
+            run_ours(args)
 
 
 if __name__ == "__main__":

@@ -514,10 +514,11 @@ RECSDK_API int recsdk_xchg_backward_local(const recsdk_xchg_t* x, const float* g
 RECSDK_API int recsdk_xchg_backward_owner(const recsdk_xchg_t* x, float* weights, float* momentum1, float* momentum2,
                                           int32_t optimizer, float learning_rate, float eps, float beta1, float beta2,
                                           int64_t iter, void* ev_update_start, void* ev_update_stop, void* stream);
-/* Plan counters of the most recent step, copied to host memory: out[0] distinct rows this rank asked for, out[1] ids
- * this rank received as an owner, out[2] distinct rows it updated, out[3] ids in chunked local runs.  Synchronises
- * the stream. */
-RECSDK_API int recsdk_xchg_counters(const recsdk_xchg_t* x, int64_t* out4, void* stream);
+/* Plan counters of the most recent step, copied to host memory (6 words): [0] distinct rows this rank asked for,
+ * [1] ids this rank received as an owner, [2] distinct rows it updated, [3] ids in chunked local runs, [4] how many
+ * of [0] this rank owns itself (the others crossed the links), [5] chunk sums of the local phase.  Synchronises the
+ * stream. */
+RECSDK_API int recsdk_xchg_counters(const recsdk_xchg_t* x, int64_t* out6, void* stream);
 
 #ifdef __cplusplus
 }

@@ -28,6 +28,19 @@
 #include <string.h>
 
 #define ORC_OK 0
+
+/* Threads of the OpenMP loops below, set explicitly by the timing harness (a launcher that exports
+ * OMP_NUM_THREADS=1 to its workers must not decide a multi-core baseline).  Returns the count in effect. */
+int orc_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
 #define ORC_ERR_NEGATIVE_KEY 1
 #define ORC_ERR_TABLE_FULL 2
 #define ORC_ERR_CACHE_TOO_SMALL 3

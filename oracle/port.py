@@ -41,6 +41,11 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def set_num_threads(n: int) -> int:
+    """OpenMP threads of the C restatement from now on; returns the count in effect."""
+    return int(lib().orc_set_num_threads(C.c_int(int(n))))
+
+
 def _i64(a):
     a = np.ascontiguousarray(a, dtype=np.int64)
     return a

@@ -845,9 +845,9 @@ extern "C" int recsdk_xchg_backward_owner(const recsdk_xchg_t* x, float* weights
     return xchg_owner_impl<uint64_t>(x, ws, p, ev_update_start, ev_update_stop, st);
 }
 
-extern "C" int recsdk_xchg_counters(const recsdk_xchg_t* x, int64_t* out4, void* stream)
+extern "C" int recsdk_xchg_counters(const recsdk_xchg_t* x, int64_t* out6, void* stream)
 {
-    if (x == nullptr || out4 == nullptr || x->workspace == nullptr) return RECSDK_ERR_INVALID_ARG;
+    if (x == nullptr || out6 == nullptr || x->workspace == nullptr) return RECSDK_ERR_INVALID_ARG;
     const XchgWorkspace ws = carve_xchg(x->workspace, x->max_ids, x->inbox_cap, x->world, x->D, x->F);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int64_t lc[8], oc[8];
@@ -857,9 +857,17 @@ extern "C" int recsdk_xchg_counters(const recsdk_xchg_t* x, int64_t* out4, void*
         (void)cudaGetLastError();
         return RECSDK_ERR_CUDA;
     }
-    out4[0] = lc[0];
-    out4[1] = oc[4];
-    out4[2] = oc[0];
-    out4[3] = lc[2];
+    int64_t seg[RECSDK_MAX_SHARDS + 1];
+    if (cudaMemcpyAsync(seg, ws.seg, sizeof(seg), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return RECSDK_ERR_CUDA;
+    }
+    out6[0] = lc[0];
+    out6[1] = oc[4];
+    out6[2] = oc[0];
+    out6[3] = lc[2];
+    out6[4] = seg[x->rank + 1] - seg[x->rank];
+    out6[5] = lc[1];
     return RECSDK_OK;
 }

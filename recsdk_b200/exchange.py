@@ -214,6 +214,14 @@ class DedupExchange:
             check(lib.recsdk_peer_release(base, 0), "recsdk_peer_release")
         self._imports = []
 
+    def set_batch_size(self, batch_size: int) -> None:
+        """Samples per step of this rank from now on (the buffers were sized at construction: F * batch_size ids must
+        fit ``max_ids``)."""
+        if self.F * int(batch_size) > self.max_ids and self.pooling_mode != PoolingMode.NONE:
+            raise ValueError("batch does not fit the buffers this object was built with")
+        self.B = int(batch_size)
+        self._x.B = self.B
+
     # ------------------------------------------------------------------ the step
     def forward(self, indices: torch.Tensor, offsets: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """indices [N] int64 (row ids inside their tables), offsets [F*B+1] feature-major.  Returns the pooled
@@ -257,9 +265,9 @@ class DedupExchange:
         self.fence()
 
     def counters(self):
-        """(distinct rows asked for, ids received as owner, distinct rows updated, ids in chunked local runs) of the
-        most recent step; synchronises."""
-        out = (C.c_int64 * 4)()
+        """(distinct rows asked for, ids received as owner, distinct rows updated, ids in chunked local runs, distinct
+        rows asked of this rank itself, chunk sums of the local phase) of the most recent step; synchronises."""
+        out = (C.c_int64 * 6)()
         check(_lib.load().recsdk_xchg_counters(C.byref(self._x), out, _stream()), "recsdk_xchg_counters")
         return tuple(int(v) for v in out)
 
