@@ -520,6 +520,35 @@ RECSDK_API int recsdk_xchg_backward_owner(const recsdk_xchg_t* x, float* weights
  * stream. */
 RECSDK_API int recsdk_xchg_counters(const recsdk_xchg_t* x, int64_t* out6, void* stream);
 
+/* =========================================================================
+ * Host (DRAM) tier of the hybrid cache: key -> AoS row [w | m | v] store for the rows that are not held in the HBM
+ * cache.  Replaces Embcache::EmbTable (torchrec_embcache/csrc/emb_table/emb_table.h:32-372: FindOrInsert :54-116,
+ * InsertOrAssign :118-179, RemoveEmbedding, ForEachKey :300-330) and its initializers
+ * (emb_table/initializer.h:36-75).  HOST pointers throughout; these calls touch no GPU.  The device side of a swap
+ * is recsdk_gather_rows / recsdk_scatter_rows plus asynchronous copies of pinned staging buffers.
+ *   find_or_insert    a missing key gets a new row (weights from the initializer, optimizer state zero); the rows are
+ *                     copied OUT into one [n, emb_dim] block per array (optim blocks as many as optim_num)
+ *   insert_or_assign  creates missing rows (no initializer) and overwrites them from the blocks
+ *   export            ForEachKey: every key with its row, in the table's iteration order (unspecified, as the
+ *                     reference's); keys_out == NULL only counts.  Returns the number of rows, -1 on error.
+ * Thread-safe (one mutex per table).  INT64_MIN and INT64_MIN+1 are not valid keys.
+ * ========================================================================= */
+enum { RECSDK_HOST_INIT_LINEAR = 0, RECSDK_HOST_INIT_TRUNCATED_NORMAL = 1, RECSDK_HOST_INIT_UNIFORM = 2 };
+typedef struct recsdk_host_table recsdk_host_table;
+RECSDK_API recsdk_host_table* recsdk_host_table_create(int32_t emb_dim, int32_t optim_num, int32_t initializer_type,
+                                                       float weight_init_min, float weight_init_max,
+                                                       float weight_init_mean, float weight_init_stddev, int64_t seed,
+                                                       int64_t reserve_rows);
+RECSDK_API void recsdk_host_table_destroy(recsdk_host_table* t);
+RECSDK_API int64_t recsdk_host_table_size(recsdk_host_table* t);
+RECSDK_API int recsdk_host_table_find_or_insert(recsdk_host_table* t, const int64_t* keys, int64_t n, float* out_embs,
+                                                float* out_optim1, float* out_optim2);
+RECSDK_API int recsdk_host_table_insert_or_assign(recsdk_host_table* t, const int64_t* keys, int64_t n,
+                                                  const float* in_embs, const float* in_optim1, const float* in_optim2);
+RECSDK_API int recsdk_host_table_remove(recsdk_host_table* t, const int64_t* keys, int64_t n);
+RECSDK_API int64_t recsdk_host_table_export(recsdk_host_table* t, int64_t* keys_out, float* embs_out, float* optim1_out,
+                                            float* optim2_out, int64_t capacity);
+
 #ifdef __cplusplus
 }
 #endif

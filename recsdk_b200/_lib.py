@@ -132,6 +132,14 @@ SIGNATURES = {
     "recsdk_xchg_backward_owner": (C.c_int, [C.POINTER(XchgT), vp, vp, vp, C.c_int32, C.c_float, C.c_float, C.c_float,
                                              C.c_float, C.c_int64, vp, vp, vp]),
     "recsdk_xchg_counters": (C.c_int, [C.POINTER(XchgT), C.POINTER(C.c_int64), vp]),
+    "recsdk_host_table_create": (vp, [C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float, C.c_float, C.c_float,
+                                      C.c_int64, C.c_int64]),
+    "recsdk_host_table_destroy": (None, [vp]),
+    "recsdk_host_table_size": (C.c_int64, [vp]),
+    "recsdk_host_table_find_or_insert": (C.c_int, [vp, vp, C.c_int64, vp, vp, vp]),
+    "recsdk_host_table_insert_or_assign": (C.c_int, [vp, vp, C.c_int64, vp, vp, vp]),
+    "recsdk_host_table_remove": (C.c_int, [vp, vp, C.c_int64]),
+    "recsdk_host_table_export": (C.c_int64, [vp, vp, vp, vp, vp, C.c_int64]),
     "recsdk_mapper_table_bytes": (C.c_size_t, [C.c_int64]),
     "recsdk_mapper_init": (C.c_int, [C.POINTER(MapperT), vp]),
     "recsdk_mapper_workspace_bytes": (C.c_size_t, [C.c_int64]),

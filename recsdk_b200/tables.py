@@ -187,6 +187,11 @@ class SwapManager:
     def GetMemStartOffset(self) -> int:
         return self.memStartOffset
 
+    def slot_keys(self) -> torch.Tensor:
+        """Key of every slot up to the occupied count (cache_[off].key, swap_manager.h:41-54); slots freed by
+        RemoveKeys keep the key they last held, as in the reference."""
+        return self._slot_key[: self.GetOccupiedNum()]
+
     def GetKey(self, off: int) -> int:
         occ = self.GetOccupiedNum()
         if not (0 <= off < occ):
@@ -265,6 +270,34 @@ class FeatureFilter:
 
     def ClearEvictInfo(self) -> None:
         _lib.check(self._lib.recsdk_filter_clear_evict(C.byref(self._c), _stream()), "ClearEvictInfo")
+
+    def timestamp_records(self):
+        """(keys, timestamps) of every key in the timestamp map (GetFeatureTimestampMap, feature_filter.h), read
+        back from the table; order unspecified.  Synchronises."""
+        t = self._table.view(-1, 4).cpu()
+        sel = (t[:, 0] >= 0) & (t[:, 2] != torch.iinfo(torch.int64).min)
+        return t[sel, 0].contiguous(), t[sel, 2].contiguous()
+
+    def load_feature_records(self, keys: torch.Tensor, counts: torch.Tensor) -> None:
+        """LoadFeatureRecords (feature_filter.cpp:92-100) on a fresh filter: count[key] = counts[i].  Keys saved
+        with -1 (not in the count map when the checkpoint was written) stay absent."""
+        keep = counts >= 0
+        if bool(keep.any()):
+            self.StatisticsKeyCount(keys[keep].contiguous(), counts[keep].contiguous())
+
+    def load_timestamp_records(self, keys: torch.Tensor, timestamps: torch.Tensor) -> None:
+        """LoadTimestampRecords (feature_filter.cpp:102-110): timestamp[key] = ts; the latest-timestamp and
+        batch counters stay as they are, as in the reference."""
+        if keys.numel() == 0:
+            return
+        before = self._counters[:2].clone()
+        saved_interval = self._c.evict_step_interval
+        self._c.evict_step_interval = 0  # no evict scan while loading
+        try:
+            self.RecordTimestamp(keys, timestamps)
+        finally:
+            self._c.evict_step_interval = saved_interval
+        self._counters[:2].copy_(before)
 
     def GetCounts(self, keys: torch.Tensor) -> torch.Tensor:
         """count of each key, -1 where the key is not in the count map."""
