@@ -13,6 +13,11 @@ Two artefacts are produced (both git-ignored; they travel with the work tree):
     utils/logger.cpp}`` unchanged, plus ``oracle/ref_embcache_harness.cpp`` (a
     flat C ABI over ``SwapManager`` / ``FeatureFilter``).
 
+``oracle/_ref/libref_manager.so``
+    the whole ``EmbcacheManager`` (host store, ``Save`` / ``Load``) plus
+    ``oracle/ref_manager_harness.cpp``; used to write and read checkpoints with the
+    reference's own code.
+
 No reference source is copied into this repository.  The reference tree is
 found through ``RECSDK_REFERENCE_ROOT`` or, when that is unset, as a checkout
 named ``reference`` beside this repository's own directory.  When neither
@@ -87,6 +92,31 @@ def build_embcache(ref: str) -> str:
     return out
 
 
+def build_manager(ref: str) -> str:
+    """The reference's whole EmbcacheManager (host store, Save / Load) behind oracle/ref_manager_harness.cpp.  Its
+    sources include a bounds-checked C library header that is not in the tree: oracle/ref_shims/securec.h stands in
+    (memcpy_s / memset_s only)."""
+    src = os.path.join(ref, "training", "torch_rec_v1", "torchrec_embcache", "src", "torchrec_embcache", "csrc")
+    sources = [os.path.join(src, *p) for p in (
+        ("embedding_cache", "embcache_manager.cpp"), ("embedding_cache", "swap_manager.cpp"),
+        ("feature_filter", "feature_filter.cpp"), ("feature_filter", "evict_feature_record.cpp"),
+        ("utils", "logger.cpp"), ("file_system", "file_system_handler.cpp"),
+        ("file_system", "local_file_system", "local_file_system.cpp"), ("emb_table", "emb_mem_pool.cpp"),
+        ("hash_table", "fast_hashmap.cpp"), ("hash_table", "hash_bucket.cpp"))]
+    sources.append(os.path.join(HERE, "ref_manager_harness.cpp"))
+    out = os.path.join(OUT, "libref_manager.so")
+    if _newer(out, sources):
+        return out
+    import sysconfig
+
+    abi, inc, link = _torch_flags()
+    # the manager's headers pull in torch's Python-facing headers (it is the body of a pybind module)
+    py_inc = sysconfig.get_paths()["include"]
+    _run(["g++", "-O1", "-std=c++17", "-fPIC", "-shared", "-fopenmp", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+          f"-I{src}", f"-I{os.path.join(HERE, 'ref_shims')}", f"-I{py_inc}", *inc, *sources, "-o", out, *link])
+    return out
+
+
 def build_all(verbose: bool = True) -> bool:
     """Build both artefacts if the reference tree is present.  Returns True when
     the reference tree was found (built or already current)."""
@@ -98,6 +128,11 @@ def build_all(verbose: bool = True) -> bool:
     os.makedirs(OUT, exist_ok=True)
     build_hybrid(ref)
     build_embcache(ref)
+    try:
+        build_manager(ref)
+    except subprocess.CalledProcessError:  # optional third artefact: the tests that need it skip without it
+        if verbose:
+            print("[oracle/build_ref] the reference manager did not build; checkpoint cross-checks will skip")
     return True
 
 

@@ -758,6 +758,95 @@ void define_and_implement_kjt(torch::Library& m)
     m.def("dense_to_jagged(Tensor dense, Tensor[] offsets, SymInt? total_L=None) -> (Tensor, Tensor[])", &dense_to_jagged);
 }
 
+// ---------------------------------------------------------------------------- TF-flavour operators
+// The four operators the reference registers with TensorFlow (cust_op/framework/tf_plugin/src/
+// cust_embedding_by_address.cpp:19-52, lazy_adam.cpp:20-35, sgd.cpp:19-28), as torch operators with the same names,
+// input order and attributes.  The TF ops return new tensors that alias their stateful inputs; here the state
+// tensors are updated in place and returned.
+Tensor embedding_lookup_by_address(const Tensor& address, int64_t embedding_dim, int64_t embedding_type)
+{
+    check_i64(address, "address");
+    TORCH_CHECK(address.dim() == 1, "address must be a vector");
+    TORCH_CHECK(embedding_type == 0, "only fp32 (embedding_type 0) is supported");
+    TORCH_CHECK(embedding_dim > 0, "embedding_dim must be positive");
+    Tensor out = at::empty({address.numel(), embedding_dim}, address.options().dtype(at::kFloat));
+    check_rc(recsdk_lookup_by_address(address.data_ptr<int64_t>(), address.numel(), static_cast<int32_t>(embedding_dim),
+                                      out.data_ptr<float>(), cur_stream()),
+             "EmbeddingLookupByAddress");
+    return out;
+}
+
+Tensor embedding_update_by_address(const Tensor& address, const Tensor& embedding, int64_t update_type)
+{
+    check_i64(address, "address");
+    TORCH_CHECK(address.dim() == 1 && embedding.dim() == 2 && embedding.size(0) == address.numel(),
+                "address [n] and embedding [n, dim] expected");
+    TORCH_CHECK(embedding.is_cuda() && embedding.scalar_type() == at::kFloat && embedding.is_contiguous(),
+                "embedding must be a contiguous float32 CUDA tensor");
+    check_rc(recsdk_update_by_address(address.data_ptr<int64_t>(), address.numel(), static_cast<int32_t>(embedding.size(1)),
+                                      embedding.data_ptr<float>(), static_cast<int32_t>(update_type), cur_stream()),
+             "EmbeddingUpdateByAddress");
+    return embedding;
+}
+
+static void check_f32(const Tensor& t, const char* name)
+{
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), name,
+                " must be a contiguous float32 CUDA tensor");
+}
+
+std::tuple<Tensor, Tensor, Tensor> lazy_adam(const Tensor& gradient, const Tensor& indices, Tensor input_m, Tensor input_v,
+                                             Tensor input_var, const Tensor& lr, double beta1, double beta2,
+                                             double epsilon)
+{
+    check_f32(gradient, "gradient");
+    check_f32(input_m, "input_m");
+    check_f32(input_v, "input_v");
+    check_f32(input_var, "input_var");
+    TORCH_CHECK(indices.is_cuda() && indices.scalar_type() == at::kInt && indices.is_contiguous(),
+                "indices must be a contiguous int32 CUDA tensor");
+    TORCH_CHECK(gradient.dim() == 2 && gradient.size(0) == indices.numel(), "gradient [n, dim] and indices [n] expected");
+    TORCH_CHECK(input_m.numel() == input_var.numel() && input_v.numel() == input_var.numel(),
+                "input_m / input_v / input_var must have the same size");
+    const float lr_v = lr.item<float>();  // a scalar tensor in the reference's signature
+    check_rc(recsdk_lazy_adam(gradient.data_ptr<float>(), indices.data_ptr<int32_t>(), indices.numel(),
+                              static_cast<int32_t>(gradient.size(1)), input_m.data_ptr<float>(), input_v.data_ptr<float>(),
+                              input_var.data_ptr<float>(), lr_v, static_cast<float>(beta1), static_cast<float>(beta2),
+                              static_cast<float>(epsilon), cur_stream()),
+             "LazyAdam");
+    return {input_m, input_v, input_var};
+}
+
+Tensor sgd(const Tensor& gradient, const Tensor& indices, Tensor input_var, const Tensor& lr, double weightDecay)
+{
+    check_f32(gradient, "gradient");
+    check_f32(input_var, "input_var");
+    TORCH_CHECK(indices.is_cuda() && indices.is_contiguous() &&
+                    (indices.scalar_type() == at::kInt || indices.scalar_type() == at::kLong),
+                "indices must be a contiguous int32 or int64 CUDA tensor");
+    TORCH_CHECK(gradient.dim() == 2 && gradient.size(0) == indices.numel(), "gradient [n, dim] and indices [n] expected");
+    const Tensor idx64 = indices.scalar_type() == at::kLong ? indices : indices.to(at::kLong);
+    const bool decay = weightDecay != 0.0;
+    Tensor ws = decay ? at::empty({gradient.numel()}, gradient.options()) : Tensor();
+    check_rc(recsdk_sgd(gradient.data_ptr<float>(), idx64.data_ptr<int64_t>(), idx64.numel(),
+                        static_cast<int32_t>(gradient.size(1)), input_var.data_ptr<float>(), lr.item<float>(),
+                        static_cast<float>(weightDecay), decay ? 1 : 0, decay ? ws.data_ptr() : nullptr,
+                        decay ? static_cast<size_t>(ws.numel()) * 4 : 0, cur_stream()),
+             "Sgd");
+    return input_var;
+}
+
+void define_and_implement_tf_flavour(torch::Library& m)
+{
+    m.def("EmbeddingLookupByAddress(Tensor address, int embedding_dim, int embedding_type) -> Tensor",
+          &embedding_lookup_by_address);
+    m.def("EmbeddingUpdateByAddress(Tensor address, Tensor embedding, int update_type) -> Tensor",
+          &embedding_update_by_address);
+    m.def("LazyAdam(Tensor gradient, Tensor indices, Tensor(a!) input_m, Tensor(b!) input_v, Tensor(c!) input_var, Tensor lr, "
+          "float beta1, float beta2, float epsilon) -> (Tensor(a!), Tensor(b!), Tensor(c!))", &lazy_adam);
+    m.def("Sgd(Tensor gradient, Tensor indices, Tensor(a!) input_var, Tensor lr, float weightDecay=0.0) -> Tensor(a!)", &sgd);
+}
+
 }  // namespace recsdk_torch
 
 #ifndef RECSDK_NO_FBGEMM_NS
@@ -786,6 +875,7 @@ TORCH_LIBRARY(recsdk, m)
     m.def("set_plan_ahead(bool on) -> ()", &recsdk_torch::set_plan_ahead);
     m.def("get_plan_ahead() -> bool", &recsdk_torch::get_plan_ahead);
     recsdk_torch::define_and_implement_kjt(m);
+    recsdk_torch::define_and_implement_tf_flavour(m);
 }
 
 // The reference's own registration names (hybrid_torchrec/src/bind_torch_lib.cpp:9-19): callers that say
