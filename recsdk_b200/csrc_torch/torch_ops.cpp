@@ -16,6 +16,9 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include <atomic>
+#include <map>
+#include <memory>
+#include <mutex>
 #include <torch/csrc/autograd/custom_function.h>
 #include <torch/custom_class.h>
 #include <torch/library.h>
@@ -46,6 +49,10 @@ static void check_i64(const Tensor& t, const char* name)
 }
 
 // ---------------------------------------------------------------------------- forward
+// Set by the lookup function around its own forward when it has just enqueued a plan on the side stream: the
+// pooled gather then runs with three resident blocks per SM so that the plan's kernels find SM slots beside it.
+static thread_local bool t_forward_leave_room = false;
+
 Tensor forward_unweighted_cuda(const Tensor& dev_weights, const Tensor& uvm_weights, const Tensor& lxu_cache_weights,
                                const Tensor& weights_placements, const Tensor& weights_offsets, const Tensor& D_offsets,
                                c10::SymInt total_D, c10::SymInt max_D, const Tensor& indices, const Tensor& offsets,
@@ -83,6 +90,7 @@ Tensor forward_unweighted_cuda(const Tensor& dev_weights, const Tensor& uvm_weig
     a.total_D = static_cast<int32_t>(totalD);
     a.max_D = static_cast<int32_t>(maxD);
     a.pooling_mode = static_cast<int32_t>(pooling_mode);
+    a.flags = t_forward_leave_room ? RECSDK_FWD_LEAVE_ROOM : 0;
     check_rc(recsdk_tbe_forward(&a, cur_stream()), "split_embedding_codegen_forward_unweighted_cuda");
     return out;
 }
@@ -93,6 +101,32 @@ struct OptArgs {
     double eps = 0, lr = 0, beta1 = 0.9, beta2 = 0.999;
     int64_t iter = 1;
 };
+
+// Per table set (device, address of dev_weights): the backward's workspace, grown on demand and kept between calls,
+// and -- for plan-ahead -- one high-priority side stream with the two events that order it against the caller's
+// stream.  Allocating the ~100 MB workspace, a stream and two events on every call cost more host time than the
+// launches themselves.  One lookup of a table set is in flight at a time (forward -> backward alternation), which is
+// also what makes a single workspace per table set sufficient.
+struct TableSetCache {
+    Tensor ws;
+    std::optional<c10::cuda::CUDAStream> side;
+    std::unique_ptr<at::cuda::CUDAEvent> ready, done;
+};
+static TableSetCache& table_set_cache(const Tensor& dev_weights)
+{
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, TableSetCache> caches;
+    std::lock_guard<std::mutex> lk(mu);
+    return caches[{static_cast<int>(dev_weights.device().index()), dev_weights.const_data_ptr()}];
+}
+static Tensor cached_workspace(TableSetCache& c, int64_t bytes, const Tensor& like)
+{
+    if (!c.ws.defined() || c.ws.numel() < bytes) {
+        c.ws = at::empty({bytes}, like.options().dtype(at::kByte));
+        if (c.side) c10::cuda::CUDACachingAllocator::recordStream(c.ws.storage().data_ptr(), *c.side);
+    }
+    return c.ws;
+}
 
 // flags / ws / plan_total_D: the split form of the call (RECSDK_BWD_PLAN_ONLY without a gradient, then
 // RECSDK_BWD_APPLY_ONLY with the same workspace); 0 / undefined / 0 = the whole backward with its own workspace.
@@ -151,8 +185,8 @@ static Tensor backward_exact(const Tensor& grad_output_in, const Tensor& dev_wei
     b.beta2 = static_cast<float>(o.beta2);
     b.iter = o.iter;
     if (!ws.defined())
-        ws = at::empty({static_cast<int64_t>(recsdk_tbe_backward_workspace_bytes(b.N, b.max_D))},
-                       dev_weights.options().dtype(at::kByte));
+        ws = cached_workspace(table_set_cache(dev_weights),
+                              static_cast<int64_t>(recsdk_tbe_backward_workspace_bytes(b.N, b.max_D)), dev_weights);
     b.workspace = ws.data_ptr();
     b.workspace_bytes = static_cast<size_t>(ws.numel());
     check_rc(recsdk_tbe_backward(&b, stream ? stream : cur_stream()), "split_embedding_backward_codegen_unweighted_exact_cuda");
@@ -246,26 +280,34 @@ public:
         const Tensor& plan_idx = pick(indices, hash_indices);
         if (g_plan_ahead.load() && dev_weights.is_cuda() && plan_idx.numel() > 0) {
             const c10::cuda::OptionalCUDAGuard guard(device_of(dev_weights));
-            Tensor ws = at::empty({static_cast<int64_t>(recsdk_tbe_backward_workspace_bytes(plan_idx.numel(), static_cast<int32_t>(max_D)))},
-                                  dev_weights.options().dtype(at::kByte));
-            auto side = at::cuda::getStreamFromPool(/*isHighPriority=*/true, dev_weights.device().index());
+            TableSetCache& c = table_set_cache(dev_weights);
+            if (!c.side) {
+                c.side = at::cuda::getStreamFromPool(/*isHighPriority=*/true, dev_weights.device().index());
+                c.ready = std::make_unique<at::cuda::CUDAEvent>();
+                c.done = std::make_unique<at::cuda::CUDAEvent>();
+            }
+            Tensor ws = cached_workspace(
+                c, static_cast<int64_t>(recsdk_tbe_backward_workspace_bytes(plan_idx.numel(), static_cast<int32_t>(max_D))),
+                dev_weights);
             auto cur = at::cuda::getCurrentCUDAStream();
-            at::cuda::CUDAEvent ready;
-            ready.record(cur);
-            ready.block(side);  // the indices are complete before the plan reads them
-            c10::cuda::CUDACachingAllocator::recordStream(ws.storage().data_ptr(), side);
+            c.ready->record(cur);
+            c.ready->block(*c.side);  // the indices are complete (and the previous backward is done with the workspace)
+            for (const Tensor* t : {&plan_idx, &offsets, &unique_ids, &unique_offsets, &unique_inverse})
+                if (t->defined() && t->numel() > 0)
+                    c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), *c.side);  // read on the side stream
             OptArgs o{static_cast<int>(optimizer), eps, lr, beta1, beta2, iter};
             backward_exact(Tensor(), dev_weights, weights_offsets, D_offsets, max_D, hash_size_cumsum, total_hash_size_bits,
                            indices, offsets, pooling_mode, momentum1, momentum2, hash_indices, unique_ids, unique_offsets,
-                           unique_inverse, o, RECSDK_BWD_PLAN_ONLY, ws, total_D, side.stream());
+                           unique_inverse, o, RECSDK_BWD_PLAN_ONLY, ws, total_D, c.side->stream());
+            c.done->record(*c.side);
             ctx->saved_data["planned"] = true;
-            ctx->saved_data["plan_ws"] = ws;
-            ctx->saved_data["plan_stream_id"] = static_cast<int64_t>(side.id());
-            ctx->saved_data["plan_device"] = static_cast<int64_t>(side.device_index());
         }
         const Tensor none;
-        return {forward_unweighted_cuda(dev_weights, none, none, none, weights_offsets, D_offsets, total_D, max_D, indices,
-                                        offsets, pooling_mode, none, none, 0, false, hash_indices, none)};
+        t_forward_leave_room = ctx->saved_data["planned"].toBool();
+        Tensor out = forward_unweighted_cuda(dev_weights, none, none, none, weights_offsets, D_offsets, total_D, max_D,
+                                             indices, offsets, pooling_mode, none, none, 0, false, hash_indices, none);
+        t_forward_leave_room = false;
+        return {out};
     }
 
     static variable_list backward(AutogradContext* ctx, variable_list grad_outputs)
@@ -283,16 +325,12 @@ public:
         int flags = 0;
         Tensor ws;
         if (ctx->saved_data["planned"].toBool()) {
-            // everything enqueued on the side stream so far (the plan) is ordered before the apply phase
+            // the plan (recorded on the side stream by the forward) is ordered before the apply phase
             const c10::cuda::OptionalCUDAGuard guard(device_of(s[0]));
-            const auto side = c10::cuda::CUDAStream(c10::Stream(
-                c10::Stream::UNSAFE, c10::Device(c10::DeviceType::CUDA, static_cast<c10::DeviceIndex>(ctx->saved_data["plan_device"].toInt())),
-                ctx->saved_data["plan_stream_id"].toInt()));
-            at::cuda::CUDAEvent done;
-            done.record(side);
-            done.block(at::cuda::getCurrentCUDAStream());
+            TableSetCache& c = table_set_cache(s[0]);
+            c.done->block(at::cuda::getCurrentCUDAStream());
             flags = RECSDK_BWD_APPLY_ONLY;
-            ws = ctx->saved_data["plan_ws"].toTensor();
+            ws = c.ws;
         }
         backward_exact(g, s[0], s[1], s[2], ctx->saved_data["max_D"].toInt(), s[3], ctx->saved_data["bits"].toInt(), s[4],
                        s[5], ctx->saved_data["pooling_mode"].toInt(), s[6], s[7], s[8], s[9], s[10], s[11], o, flags, ws);

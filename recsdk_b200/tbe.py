@@ -186,10 +186,9 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         from . import torch_ops
 
         if use_torch_ops is None:
-            # with plan_ahead the Python Function is the default route (measured 0.880 vs 0.907 ms per end-to-end step
-            # through the registered operators, which allocate their workspace per call); use_torch_ops=True
-            # selects the registered operators explicitly
-            use_torch_ops = torch_ops.available() and reduce_chunk == 64 and not bounds_check and not plan_ahead
+            # the registered operators (C++ autograd function, workspace / side stream / events kept per table set)
+            # are the default route whenever the library is built; they use reduce_chunk 64 and no bounds checking
+            use_torch_ops = torch_ops.available() and reduce_chunk == 64 and not bounds_check
         if use_torch_ops:
             torch_ops.load()
             if plan_ahead:
@@ -229,6 +228,8 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         self._status = ops.new_status(dev)
         self._ws: Optional[Tensor] = None
         self._ws_counters: Optional[Tensor] = None
+        self._op_kwargs = None
+        self._op = None
 
     # ------------------------------------------------------------------ kernels
     def _forward_impl(self, indices: Tensor, offsets: Tensor, out: Optional[Tensor] = None, out_shards=None):
@@ -255,6 +256,9 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
             self._plan_stream = torch.cuda.Stream(device=self.current_device, priority=-1)
             self._plan_event = torch.cuda.Event()
         self._plan_stream.wait_stream(cur)
+        for t in (indices, offsets, unique_ids, unique_offsets, unique_inverse):
+            if t is not None:
+                t.record_stream(self._plan_stream)  # the plan reads them on the side stream
         with torch.cuda.stream(self._plan_stream):
             self._backward_impl(None, indices, offsets, unique_ids, unique_offsets, unique_inverse, 1,
                                 grad_shards=grad_shards, phase="plan")
@@ -297,6 +301,9 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         self.step += 1
         self.iter[0] += 1  # create_momentum(), batched_embedding_kernel.py:159-176
         iteration = int(self.iter.item())
+        if not torch.is_grad_enabled():
+            # evaluation / no_grad: no backward will follow, so no lookup function and no plan made ahead
+            return self._forward_impl(hash_indices if hash_indices is not None else indices, offsets)
         if self.use_torch_ops:
             return self._invoke_registered_op(indices, offsets, hash_indices, unique_indices, unique_offset,
                                               unique_inverse, iteration)
@@ -308,29 +315,34 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         """The call the reference's invokers make (hybrid_lookup_invoke/hybrid_lookup_{adagrad,adam,sgd}.py):
         torch.ops.fbgemm.split_embedding_codegen_lookup_*_function with the same keyword names."""
         a = self.optimizer_args
-        common = dict(
-            placeholder_autograd_tensor=self.placeholder_autograd_tensor, dev_weights=self.weights_dev.data,
-            uvm_weights=self.weights_uvm, lxu_cache_weights=self.lxu_cache_weights,
-            weights_placements=self.weights_placements, weights_offsets=self.weights_offsets,
-            D_offsets=self.D_offsets, total_D=self.total_D, max_D=self.max_D,
-            hash_size_cumsum=self.hash_size_cumsum, total_hash_size_bits=self.total_hash_size_bits,
-            indices=indices, offsets=offsets, hash_indices=hash_indices, unique_ids=unique_indices,
-            unique_offsets=unique_offset, unique_inverse=unique_inverse, pooling_mode=int(self.pooling_mode),
-            indice_weights=None, feature_requires_grad=None, lxu_cache_locations=self.lxu_cache_locations,
-            gradient_clipping=a.gradient_clipping, max_gradient=a.max_gradient,
-            stochastic_rounding=a.stochastic_rounding, learning_rate=a.learning_rate, iter=iteration,
-            output_dtype=self.output_dtype)
-        m1 = dict(momentum1_dev=self.momentum1_dev, momentum1_uvm=self.momentum1_uvm,
-                  momentum1_offsets=self.momentum1_offsets, momentum1_placements=self.momentum1_placements)
-        m2 = dict(momentum2_dev=self.momentum2_dev, momentum2_uvm=self.momentum2_uvm,
-                  momentum2_offsets=self.momentum2_offsets, momentum2_placements=self.momentum2_placements)
-        ns = torch.ops.fbgemm
-        if self.optimizer == EmbOptimType.EXACT_ADAGRAD:
-            return ns.split_embedding_codegen_lookup_adagrad_function(**common, **m1, eps=a.eps)
-        if self.optimizer == EmbOptimType.ADAM:
-            return ns.split_embedding_codegen_lookup_adam_function(**common, **m1, **m2, eps=a.eps, beta1=a.beta1,
-                                                                   beta2=a.beta2, weight_decay=a.weight_decay)
-        return ns.split_embedding_codegen_lookup_sgd_function(**common)
+        kw = self._op_kwargs
+        if kw is None:
+            # everything that does not change from call to call, built once
+            kw = dict(
+                placeholder_autograd_tensor=self.placeholder_autograd_tensor, dev_weights=self.weights_dev.data,
+                uvm_weights=self.weights_uvm, lxu_cache_weights=self.lxu_cache_weights,
+                weights_placements=self.weights_placements, weights_offsets=self.weights_offsets,
+                D_offsets=self.D_offsets, total_D=self.total_D, max_D=self.max_D,
+                hash_size_cumsum=self.hash_size_cumsum, total_hash_size_bits=self.total_hash_size_bits,
+                pooling_mode=int(self.pooling_mode), indice_weights=None, feature_requires_grad=None,
+                lxu_cache_locations=self.lxu_cache_locations, gradient_clipping=a.gradient_clipping,
+                max_gradient=a.max_gradient, stochastic_rounding=a.stochastic_rounding, output_dtype=self.output_dtype)
+            if self.optimizer != EmbOptimType.EXACT_SGD:
+                kw.update(momentum1_dev=self.momentum1_dev, momentum1_uvm=self.momentum1_uvm,
+                          momentum1_offsets=self.momentum1_offsets, momentum1_placements=self.momentum1_placements,
+                          eps=a.eps)
+            if self.optimizer == EmbOptimType.ADAM:
+                kw.update(momentum2_dev=self.momentum2_dev, momentum2_uvm=self.momentum2_uvm,
+                          momentum2_offsets=self.momentum2_offsets, momentum2_placements=self.momentum2_placements,
+                          beta1=a.beta1, beta2=a.beta2, weight_decay=a.weight_decay)
+            ns = torch.ops.fbgemm
+            self._op = {EmbOptimType.EXACT_ADAGRAD: ns.split_embedding_codegen_lookup_adagrad_function,
+                        EmbOptimType.ADAM: ns.split_embedding_codegen_lookup_adam_function,
+                        EmbOptimType.EXACT_SGD: ns.split_embedding_codegen_lookup_sgd_function}[self.optimizer]
+            self._op_kwargs = kw
+        return self._op(indices=indices, offsets=offsets, hash_indices=hash_indices, unique_ids=unique_indices,
+                        unique_offsets=unique_offset, unique_inverse=unique_inverse, learning_rate=a.learning_rate,
+                        iter=iteration, **kw)
 
     # swap helpers (batched_embedding_kernel.py:297-345); rows move by bulk copies
     def _check_same_dim(self):

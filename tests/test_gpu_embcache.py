@@ -75,7 +75,8 @@ def test_manager_argument_errors_and_host_tier():
 
     with pytest.raises(RuntimeError, match="Size of embConfigs must > 0"):
         EmbcacheManager([], device=DEV)
-    mgr = EmbcacheManager([EmbConfig("a", cache_size=64), EmbConfig("b", cache_size=64)], device=DEV)
+    mgr = EmbcacheManager([EmbConfig("a", cache_size=64, emb_dim=4, optim_num=1, weight_init_max=1.0),
+                           EmbConfig("b", cache_size=64, emb_dim=4, optim_num=1, weight_init_max=1.0)], device=DEV)
     keys = torch.arange(10, dtype=torch.int64, device=DEV)
     with pytest.raises(RuntimeError, match="tableIndices size\\+1 must be equal to offsetPerKey size"):
         mgr.compute_swap_info_async(keys, [0, 10])
@@ -85,5 +86,12 @@ def test_manager_argument_errors_and_host_tier():
         mgr.compute_swap_info_async(keys.int(), [0, 5, 10])
     info = mgr.compute_swap_info(keys, [0, 10], table_indices=[1])  # only table 1
     assert info.swapin_keys[0].numel() == 10 and info.batch_offs.numel() == 10
-    with pytest.raises(NotImplementedError):
-        mgr.embedding_lookup_async(info)
+    # host tier: the swap-in keys of table 1 get LINEAR rows and zero optimizer state, in pinned host tensors
+    st = mgr.embedding_lookup_async(info, table_indices=[1]).get()
+    assert st.swapin_embs.is_pinned() and st.jagged_offs.tolist() == [0, 40]
+    np.testing.assert_array_equal(st.swapin_embs.view(10, 4).numpy(),
+                                  np.tile(np.array([0, 1 / 3, 2 / 3, 1], np.float64).astype(np.float32), (10, 1)))
+    assert len(st.swapin_optims) == 1 and torch.count_nonzero(st.swapin_optims[0]) == 0
+    assert mgr.host_tables[1].size() == 10 and mgr.host_tables[0].size() == 0
+    with pytest.raises(RuntimeError, match="tableIndices size must be equal"):
+        mgr.embedding_lookup_async(info).get()  # one key list, two tables

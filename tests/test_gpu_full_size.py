@@ -141,3 +141,36 @@ def test_one_hot_config_full_size_adam_properties():
         off += n
     U = m.last_num_unique()
     assert U == int(sum(torch.unique(idx[t * B:(t + 1) * B]).numel() for t in range(T)))
+
+
+@pytest.mark.parametrize("eps", [1e-8, 0.0])
+def test_config1_exact_size_bit_exact(eps):
+    """The single-table config at its exact size -- 1,000,000 rows x 16, batch 4096 one-hot ids ~ Zipf(1.05) through a
+    seeded permutation, N(0,1) upstream gradient, sparse Adagrad lr 0.01 with the accumulator starting at 0.1 -- in the
+    torch flavour (eps 1e-8) and the TF flavour (eps 0: acc += g^2; w -= lr * g / sqrt(acc)), two steps, every bit of
+    output, table and accumulator against the CPU oracle."""
+    from oracle import port
+    from recsdk_b200.tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
+    from tests.golden.driver import zipf_ids
+
+    rows, D, B = 1_000_000, 16, 4096
+    rng = np.random.default_rng(1234)
+    w = rng.uniform(-0.05, 0.05, rows * D).astype(np.float32)
+    perm = rng.permutation(rows)
+    m = HybridSplitTableBatchedEmbeddingBagsCodegen([(rows, D)], optimizer=EmbOptimType.EXACT_ADAGRAD,
+                                                    pooling_mode=PoolingMode.SUM, device="cuda", learning_rate=0.01,
+                                                    eps=eps, initial_accumulator_value=0.1)
+    m.weights_dev.data.copy_(torch.from_numpy(w))
+    acc = np.full_like(w, 0.1)
+    wo, do, hs = np.zeros(1, np.int64), np.array([0, D], np.int32), np.array([0, rows], np.int64)
+    offs = np.arange(B + 1, dtype=np.int64)
+    for it in (1, 2):
+        ids = perm[zipf_ids(rng, B, rows, 1.05)].astype(np.int64)
+        grad = rng.standard_normal((B, D)).astype(np.float32)
+        exp = port.tbe_forward(w, wo, do, ids, offs, 1, B, D, D, 0)
+        out = m(torch.from_numpy(ids).cuda(), torch.from_numpy(offs).cuda())
+        np.testing.assert_array_equal(out.detach().cpu().numpy(), exp)
+        out.backward(torch.from_numpy(grad).cuda())
+        port.tbe_backward(grad, w, acc, None, wo, do, hs, ids, offs, 1, B, D, D, 0, 1, 0.01, eps, reduce_chunk=64)
+    np.testing.assert_array_equal(m.weights_dev.data.cpu().numpy(), w)
+    np.testing.assert_array_equal(m.momentum1_dev.cpu().numpy(), acc)

@@ -237,3 +237,51 @@ def test_registered_ops_plan_ahead_same_bits():
         torch.ops.recsdk.set_plan_ahead(False)
     for a, b in zip(*results):
         assert torch.equal(a, b)
+
+
+def test_tf_flavour_torch_operators_match_oracle():
+    """torch.ops.recsdk.{EmbeddingLookupByAddress, EmbeddingUpdateByAddress, LazyAdam, Sgd}: the reference's TF operator
+    signatures (cust_op/framework/tf_plugin/src/*.cpp) as torch operators, bit for bit against the oracle."""
+    from oracle import port
+    from recsdk_b200 import torch_ops
+
+    if not torch_ops.available():
+        pytest.skip("torch op library not built")
+    torch_ops.load()
+    rng = np.random.default_rng(21)
+    rows, dim, n = 5000, 16, 700
+    table_np = rng.standard_normal((rows, dim)).astype(np.float32)
+    table = torch.from_numpy(table_np).cuda()
+    slots = rng.permutation(rows)[:n]
+    addr = table.data_ptr() + slots.astype(np.int64) * dim * 4
+    addr[::50] = 0
+    out = torch.ops.recsdk.EmbeddingLookupByAddress(torch.from_numpy(addr).cuda(), dim, 0)
+    exp = table_np[slots].copy()
+    exp[::50] = 0
+    np.testing.assert_array_equal(out.cpu().numpy(), exp)
+    upd = rng.standard_normal((n, dim)).astype(np.float32)
+    torch.ops.recsdk.EmbeddingUpdateByAddress(torch.from_numpy(addr).cuda(), torch.from_numpy(upd).cuda(), 1)
+    e2 = table_np.copy()
+    live = addr != 0
+    e2[slots[live]] = upd[live]
+    np.testing.assert_array_equal(table.cpu().numpy(), e2)
+
+    m, v, var = (rng.uniform(1, 2, (rows, dim)).astype(np.float32) for _ in range(3))
+    g = rng.uniform(1, 2, (n, dim)).astype(np.float32)
+    idx = slots.astype(np.int32)
+    idx[3] = -1
+    dm, dv, dvar = (torch.from_numpy(a.copy()).cuda() for a in (m, v, var))
+    om, ov, ovar = torch.ops.recsdk.LazyAdam(torch.from_numpy(g).cuda(), torch.from_numpy(idx).cuda(), dm, dv, dvar,
+                                             torch.tensor(1e-3), 0.9, 0.999, 1e-7)
+    port.lazy_adam(g, idx, m, v, var, 1e-3, 0.9, 0.999, 1e-7)
+    assert om.data_ptr() == dm.data_ptr() and ovar.data_ptr() == dvar.data_ptr()  # state updated in place
+    for a, b in ((dm, m), (dv, v), (dvar, var)):
+        np.testing.assert_array_equal(a.cpu().numpy(), b)
+
+    var2 = rng.standard_normal((rows, dim)).astype(np.float32)
+    dvar2 = torch.from_numpy(var2.copy()).cuda()
+    idx64 = slots.astype(np.int64)
+    torch.ops.recsdk.Sgd(torch.from_numpy(g).cuda(), torch.from_numpy(idx64.astype(np.int32)).cuda(), dvar2,
+                         torch.tensor(0.1), 0.01)
+    port.sgd(g, idx64, var2, 0.1, 0.01)
+    np.testing.assert_array_equal(dvar2.cpu().numpy(), var2)

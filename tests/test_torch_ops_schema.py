@@ -61,3 +61,22 @@ def test_kjt_utilities_are_registered():
                        "float padding_value) -> Tensor",
                        f"{ns}::jagged_to_padded_dense.v2(Tensor values, Tensor[] offsets, int[] max_lengths, "
                        "float padding_value) -> Tensor"]
+
+
+def test_tf_flavour_operators_are_registered():
+    """cust_op/framework/tf_plugin/src/{cust_embedding_by_address,lazy_adam,sgd}.cpp: same operator names, input order
+    and attribute names as the REGISTER_OP blocks."""
+    from recsdk_b200 import torch_ops
+
+    if not torch_ops.available():
+        pytest.skip("torch op library not built")
+    torch_ops.load()
+    want = {
+        "EmbeddingLookupByAddress": ["address", "embedding_dim", "embedding_type"],
+        "EmbeddingUpdateByAddress": ["address", "embedding", "update_type"],
+        "LazyAdam": ["gradient", "indices", "input_m", "input_v", "input_var", "lr", "beta1", "beta2", "epsilon"],
+        "Sgd": ["gradient", "indices", "input_var", "lr", "weightDecay"],
+    }
+    for name, args in want.items():
+        schema = getattr(torch.ops.recsdk, name).default._schema
+        assert [a.name for a in schema.arguments] == args
