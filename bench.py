@@ -731,6 +731,394 @@ def run_dedup_multi(args):
     dist.destroy_process_group()
 
 
+
+# ============================================================================ the other configs (--config c1|c3|c4|c5)
+def _time_loop(torch, fn, steps, warmup):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        fn(warmup + i)
+    issue_ms = (time.perf_counter() - t0) * 1e3 / steps
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps, issue_ms
+
+
+def run_tbe_config(args, name):
+    """configs[0] (c1: one table 1e6 x 16, batch 4096 one-hot Zipf(1.05), Adagrad acc 0.1) and configs[2] (c3: 26 tables
+    of 1e6..1e7 rows x 64, batch 16384, bag length U[1,100], Zipf(1.2), SUM, Adagrad) on one GPU: forward + fused
+    backward through the module's stepping calls, end to end with host index buffers, the row-update kernel against
+    the measured copy peak, and the CPU restatement beside it."""
+    import numpy as np
+    import torch
+
+    from recsdk_b200.synthetic import multi_hot_batch, one_hot_batch
+    from recsdk_b200.tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if name == "c1":
+        rows, D, B, alpha, max_len, seed, init = [1_000_000], 16, 4096, 1.05, 1, 1234, 0.05
+        label = "configs[0]: one table 1e6 x 16 fp32, batch 4096 one-hot Zipf(1.05), sparse Adagrad lr 0.01 acc 0.1"
+    else:
+        rng = np.random.default_rng(7)
+        rows = [int(r) for r in np.round(10 ** rng.uniform(6, 7, 26)).astype(np.int64)]
+        D, B, alpha, max_len, seed, init = 64, 16384, 1.2, 100, 7, 0.05
+        label = ("configs[2]: 26 tables of 1e6..1e7 rows (log-uniform, seed 7) x 64 fp32, batch 16384, bag length "
+                 "U[1,100], ids Zipf(1.2), SUM pooling, sparse Adagrad lr 0.01 acc 0.1")
+    T = len(rows)
+    module = HybridSplitTableBatchedEmbeddingBagsCodegen(
+        [(r, D) for r in rows], optimizer=EmbOptimType.EXACT_ADAGRAD, pooling_mode=PoolingMode.SUM, device=dev,
+        learning_rate=0.01, eps=1e-8, initial_accumulator_value=0.1, weights_init=(-init, init), seed=seed,
+        plan_ahead=not args.no_plan_ahead)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    n_batches = 4
+    batches = [one_hot_batch(gen, rows, B, alpha, dev) if max_len == 1 else multi_hot_batch(gen, rows, B, max_len, alpha, dev)
+               for _ in range(n_batches)]
+    grad = torch.randn((B, T * D), generator=gen, device=dev)
+    out = torch.empty((B, T * D), device=dev)
+    ev_pairs = []
+
+    def step(i, timed=False):
+        idx, offs = batches[i % n_batches]
+        evs = None
+        if timed:
+            evs = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            for e in evs:
+                e.record()
+            ev_pairs.append(evs)
+        module.forward_into(idx, offs, out)
+        module.backward_from(grad, idx, offs, update_events=evs)
+
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms_step, _ = _time_loop(torch, lambda i: step(i, timed=True), args.steps, args.warmup)
+    upd_ms = sum(a.elapsed_time(b) for a, b in ev_pairs[-args.steps:]) / args.steps
+    U, n_chunks, n_long = module.last_plan_counters()
+    N = int(np.mean([b[0].numel() for b in batches]))
+
+    # end to end through module(indices, offsets) + backward with pinned host index buffers (int32 on the wire)
+    host = [(i.to(torch.int32).cpu().pin_memory(), o.to(torch.int32).cpu().pin_memory()) for i, o in batches]
+    result_host = torch.empty(min(4096, B * T * D), dtype=torch.float32).pin_memory()
+
+    def step_e2e(i):
+        hi, ho = host[i % n_batches]
+        o = module(hi.to(dev, non_blocking=True), ho.to(dev, non_blocking=True))
+        o.backward(grad)
+        result_host.copy_(o.detach().reshape(-1)[:result_host.numel()], non_blocking=True)
+
+    e2e_ms, issue_ms = _time_loop(torch, step_e2e, args.steps, max(args.warmup, 3))
+    clocks = sampler.stop()
+    peak, peak_kind = measured_peak_gbs()
+    S = 1
+    upd_bytes = U * (4 * D * 2 * (1 + S) + 32) + (N - n_long) * (4 * D + 4) + n_chunks * 4 * D
+    bags = T * B
+    step_bytes = (16 * N + 8 * U) + (N * (8 + 4 * D) + 8 * (bags + 1) + 4 * D * bags) + \
+                 (4 * D * bags + 8 * N + 8 * U + U * 4 * D * 2 * (1 + S))
+    line = {
+        "metric": "embedding ids/sec (fwd+bwd+sparse Adagrad)", "value": N / (ms_step * 1e-3), "unit": "ids/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "us_per_step": ms_step * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": label, "ids_per_step": N, "bags_per_step": bags, "unique_rows_per_step": U,
+                   "table_state_gb": round(sum(rows) * D * 4 * 2 / 1e9, 2),
+                   "l2": (f"{n_batches} distinct batches rotate; " +
+                          ("the step moves ~0.6 MB: launch / latency bound, the roofline fraction is informational"
+                           if name == "c1" else "output + gradient + touched rows per step exceed L2"))},
+        "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+        "step_hbm_frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+        "roofline": {"kernel": "update_kernel<Adagrad>", "bound": "hbm", "achieved": upd_bytes / (upd_ms * 1e-3) / 1e9,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": upd_bytes / (upd_ms * 1e-3) / 1e9 / peak,
+                     "bytes_per_launch": upd_bytes, "ms_per_launch": upd_ms, "traffic": None},
+        "e2e": {"value": N / (e2e_ms * 1e-3), "unit": "ids/s", "ms_per_step": e2e_ms, "host_enqueue_ms_per_step": issue_ms,
+                "h2d_bytes_per_step": int(host[0][0].numel() * 4 + host[0][1].numel() * 4),
+                "d2h_bytes_per_step": int(result_host.numel() * 4)},
+        "gpu_launches": (1 + 1 + 2 * 3 + 3 + 1 + 1 + 1) * args.steps,
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = _cpu_tbe_config(name, rows, D, B, alpha, max_len, args.cpu_budget)
+    emit(line)
+
+
+def _cpu_tbe_config(name, rows, D, B, alpha, max_len, budget_s):
+    """The CPU restatement on the same shapes; c3's tables are capped at 262144 rows and the batch at 2048 samples so
+    that the sample stays within the time budget (c1 runs at full size)."""
+    import numpy as np
+
+    from oracle import port
+
+    cores = os.cpu_count() or 1
+    port.set_num_threads(cores)
+    rng = np.random.default_rng(3)
+    if name != "c1":
+        rows, B = [min(r, 262_144) for r in rows], 2048
+    T = len(rows)
+    wo = np.concatenate([[0], np.cumsum([r * D for r in rows])]).astype(np.int64)
+    do = (np.arange(T + 1) * D).astype(np.int32)
+    hs = np.concatenate([[0], np.cumsum(rows)]).astype(np.int64)
+    w = rng.uniform(-0.05, 0.05, int(wo[-1])).astype(np.float32)
+    acc = np.full_like(w, 0.1)
+    lens = np.ones(T * B, np.int64) if max_len == 1 else rng.integers(1, max_len + 1, T * B)
+    idx = []
+    for t, r in enumerate(rows):
+        n = int(lens[t * B:(t + 1) * B].sum())
+        p = np.arange(1, r + 1, dtype=np.float64) ** (-alpha)
+        cdf = np.cumsum(p)
+        idx.append(np.minimum(np.searchsorted(cdf, rng.random(n) * cdf[-1]), r - 1))
+    idx = np.concatenate(idx).astype(np.int64)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    grad = rng.standard_normal((B, T * D)).astype(np.float32)
+
+    def one():
+        port.tbe_forward(w, wo[:-1].copy(), do, idx, offs, T, B, T * D, D, 0)
+        port.tbe_backward(grad, w, acc, None, wo[:-1].copy(), do, hs, idx, offs, T, B, T * D, D, 0, 1, 0.01, 1e-8,
+                          reduce_chunk=64)
+
+    one()
+    t0, n = time.perf_counter(), 0
+    while time.perf_counter() - t0 < budget_s and n < 200:
+        one()
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": idx.size * n / dt, "unit": "ids/s", "cores": cores, "kind": "port",
+            "sample": f"{n} steps of {T} table(s) with rows capped at {max(rows)} x {B} samples ({idx.size} ids per step), "
+                      "oracle C restatement with OpenMP"}
+
+
+def run_c4(args):
+    """configs[3]: dynamic hash-keyed table, 64 Mi slots x 32 fp32, 131072 keys per step with 30 % new keys, admission
+    at count >= 2, eviction of keys idle for more than 50 steps every 10 steps, gather + sparse Adam on the cache rows.
+    One step = timestamps -> counts -> first-occurrence unique -> admission filter -> slot policy (-> evict) -> pooled
+    gather over the slots -> fused backward.  Before timing, the slots of the first steps are compared with the CPU
+    restatement of SwapManager + FeatureFilter (or the reference's compiled classes when oracle/_ref holds them)."""
+    import numpy as np
+    import torch
+
+    from recsdk_b200 import ops
+    from recsdk_b200.embcache import AdmitAndEvictConfig, EmbcacheManager, EmbConfig
+    from recsdk_b200.tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    cache, D, n_keys, interval, thr = 64 << 20, 32, 131072, 10, 50
+    total_steps = args.warmup + args.steps + 8
+    rng = np.random.default_rng(99)
+    issued = rng.integers(0, 2**63 - 1, size=n_keys, dtype=np.int64)
+    stream = []
+    for _ in range(total_steps):
+        fresh = rng.integers(0, 2**63 - 1, size=int(n_keys * 0.3), dtype=np.int64)
+        keys = np.concatenate([fresh, issued[rng.integers(0, issued.size, size=n_keys - fresh.size)]])
+        rng.shuffle(keys)
+        issued = np.concatenate([issued, fresh])
+        stream.append(keys)
+    cfg = EmbConfig("dyn", emb_dim=D, optim_num=2, cache_size=cache, weight_init_max=1.0,
+                    admit_and_evict_config=AdmitAndEvictConfig(2, 0.0, thr, interval), filter_capacity=1 << 26)
+    mgr = EmbcacheManager([cfg], device=dev)
+    module = HybridSplitTableBatchedEmbeddingBagsCodegen([(cache, D)], optimizer=EmbOptimType.ADAM,
+                                                        pooling_mode=PoolingMode.SUM, device=dev, learning_rate=LR, eps=EPS,
+                                                        beta1=BETA1, beta2=BETA2, weights_init=(-0.01, 0.01), seed=99)
+    d_stream = [torch.from_numpy(k).to(dev) for k in stream]
+    offsets = torch.arange(n_keys + 1, dtype=torch.int64, device=dev)
+    grad = torch.randn((n_keys, D), device=dev)
+    out = torch.empty((n_keys, D), device=dev)
+
+    def step(i):
+        k = d_stream[i]
+        ts = torch.full_like(k, i)
+        offs2 = [0, n_keys]
+        mgr.record_timestamp(k, offs2, ts)
+        if i > 0 and (i + 1) % interval == 0:
+            mgr.evict_features()
+            mgr.remove_embedding_table_info()
+        mgr.feature_filters[0].StatisticsKeyCount(k)
+        uq, inv, cnt = ops.unique_sorted(k)  # the CPU side of the slot check dedups in the same (ascending) order
+        n_u = int(cnt.item())
+        info = mgr.compute_swap_info(uq[:n_u].contiguous(), [0, n_u])
+        slots = info.batch_offs[inv]
+        module.forward_into(slots, offsets, out)
+        module.backward_from(grad, slots, offsets)
+        return uq, info
+
+    # ---- slot parity on the first steps against the CPU classes
+    from oracle import port, ref
+
+    try:
+        have_ref = ref.available() and ref.embcache() is not None
+    except OSError:
+        have_ref = False
+    cs, cf = (ref.SwapManager(cache, 1), ref.FeatureFilter(2, thr, interval)) if have_ref else \
+             (port.SwapManager(cache, 1), port.FeatureFilter(2, thr, interval))
+    parity = "bit-exact"
+    for i in range(min(8, total_steps)):
+        uq, info = step(i)
+        k = stream[i]
+        cf.record_timestamp(k, np.full(k.size, i, np.int64))
+        cf.statistics_key_count(k)
+        res = cs.compute_swap_info(cf.count_filter(np.unique(k)))
+        exp_offs = np.asarray(res[4] if isinstance(res, (tuple, list)) else res["batch_offs"])
+        if not np.array_equal(info.batch_offs.cpu().numpy(), exp_offs):
+            parity = f"MISMATCH of slots at step {i}"
+            break
+    it = [8]
+
+    def timed(_):
+        step(it[0])
+        it[0] += 1
+
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms_step, issue_ms = _time_loop(torch, timed, args.steps, args.warmup)
+    clocks = sampler.stop()
+    peak, peak_kind = measured_peak_gbs()
+    U = int(ops.unique_sorted(d_stream[it[0] - 1])[2].item())
+    S = 2
+    step_bytes = (16 * n_keys + 8 * U) + 16 * n_keys + (n_keys * (8 + 4 * D) + 8 * (n_keys + 1) + 4 * D * n_keys) + \
+                 (4 * D * n_keys + 8 * n_keys + 8 * U + U * 4 * D * 2 * (1 + S))
+    line = {
+        "metric": "embedding ids/sec (key->slot + fwd+bwd+sparse Adam)", "value": n_keys / (ms_step * 1e-3), "unit": "ids/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int64 keys / f32 rows", "data": "synthetic",
+        "config": {"workload": "configs[3]: dynamic hash-keyed table, 64 Mi slots x 32 fp32, 131072 keys per step, 30 % "
+                               "new keys, admit at count >= 2, evict idle > 50 steps every 10 steps, gather + sparse Adam",
+                   "ids_per_step": n_keys, "unique_keys_last_step": U,
+                   "host_reads_per_step": "two (unique count, swap counts): the reference's interface returns host lists"},
+        "parity_check": parity + (" (slots of the first 8 steps vs the reference's compiled SwapManager + FeatureFilter)"
+                                  if have_ref else " (slots of the first 8 steps vs the CPU restatement)"),
+        "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+        "roofline": {"kernel": "whole step (policy phases are latency bound)", "bound": "hbm",
+                     "achieved": step_bytes / (ms_step * 1e-3) / 1e9, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak, "traffic": None},
+        "e2e": {"value": n_keys / (ms_step * 1e-3), "unit": "ids/s", "ms_per_step": ms_step,
+                "host_enqueue_ms_per_step": issue_ms, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 32,
+                "note": "keys resident; the step itself reads two counts back per step"},
+        "clocks": clocks,
+    }
+    emit(line)
+
+
+def run_c5(args):
+    """configs[4]: one row-wise sharded table, 1e9 rows x 64 fp32 with Adam state at 8 GPUs (1.25e8 rows per GPU at any
+    N: 5e8 at 4, 2.5e8 at 2, 1.25e8 at 1), batch 262144 one-hot ids ~ Zipf(1.05) per GPU, through the device-driven
+    dedup exchange with rows placed by id % W."""
+    import torch
+    import torch.distributed as dist
+
+    from recsdk_b200.rowwise import RowWiseShardedEmbeddingBag
+    from recsdk_b200.tbe import EmbOptimType
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rows, D, B, alpha = 125_000_000 * world, 64, 262144, 1.05
+    bag = RowWiseShardedEmbeddingBag([rows], D, world, rank, batch_size=B, optimizer=EmbOptimType.ADAM, device=dev,
+                                     learning_rate=LR, eps=EPS, beta1=BETA1, beta2=BETA2, weights_init=(-0.01, 0.01),
+                                     seed=5 + rank, one_hot=True)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5 + 17 * rank)
+
+    def zipf_large(n):
+        # inverse of the continuous Zipf CDF (a 1e9-entry table of exact probabilities would not fit beside the
+        # rows): rank = (1 + u (V^(1-a) - 1))^(1/(1-a)); ranks spread over the ids by a multiplicative hash
+        u = torch.rand(n, generator=gen, dtype=torch.float64, device=dev)
+        r = (1.0 + u * (float(rows) ** (1.0 - alpha) - 1.0)).pow(1.0 / (1.0 - alpha)).to(torch.int64).clamp_(1, rows) - 1
+        return (r * 2654435761 + 12345) % rows
+
+    batches = [zipf_large(B) for _ in range(4)]
+    offsets = torch.arange(B + 1, dtype=torch.int64, device=dev)
+    grad = torch.randn((B, D), generator=gen, device=dev)
+    out = torch.empty((B, D), device=dev)
+
+    def step(i):
+        bag.forward(batches[i % 4], offsets, out=out)
+        bag.backward(grad)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    t1.record()
+    barrier()
+    ms = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev, dtype=torch.float64)
+    host = [b.cpu().pin_memory() for b in batches]
+    result_host = torch.empty(4096, dtype=torch.float32).pin_memory()
+
+    def step_e2e(i):
+        bag.forward(host[i % 4].to(dev, non_blocking=True), offsets, out=out)
+        bag.backward(grad)
+        result_host.copy_(out.reshape(-1)[:4096], non_blocking=True)
+
+    for i in range(3):
+        step_e2e(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step_e2e(i)
+    e1.record()
+    barrier()
+    e2e = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+    counters = bag.counters()
+    bag.raise_if_error()
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        ms_step, e2e_ms = ms.item(), e2e.item()
+        U_req, n_recv, U_own, _, U_self, _ = counters
+        S = 2
+        step_bytes = (16 * B + 8 * U_req) + (U_req * 4 * D + 8 * (B + 1) + 4 * D * B) + (4 * D * B + 8 * B + U_req * 4 * D) + \
+                     (n_recv * (8 + 4 * D) + U_own * 4 * D * 2 * (1 + S))
+        remote = U_req - U_self
+        emit({
+            "metric": "embedding ids/sec (fwd+bwd+sparse Adam)", "value": B * world / (ms_step * 1e-3), "unit": "ids/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"configs[4]: row-wise sharded table, {rows} rows x 64 fp32 + Adam state over {world} GPU(s) "
+                                   "(1.25e8 rows = 96 GB per GPU), batch 262144 one-hot ids ~ Zipf(1.05) per GPU, rows "
+                                   "placed by id % W, device-driven dedup exchange",
+                       "ids_per_step": B * world, "distinct_rows_requested_rank0": U_req,
+                       "distinct_rows_updated_rank0": U_own,
+                       "ids": "continuous inverse-CDF Zipf sampler (an exact 1e9-entry CDF does not fit beside the rows)"},
+            "step_hbm_gbs_rank0": step_bytes / (ms_step * 1e-3) / 1e9,
+            "roofline": {"kernel": "whole step of rank 0 (sort / scan phases are latency bound at this batch size)",
+                         "bound": "hbm", "achieved": step_bytes / (ms_step * 1e-3) / 1e9, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+                         "traffic": None},
+            "nvlink": {"bytes_per_step_per_gpu": {"in": remote * D * 4, "out": remote * (D * 4 + 8)}},
+            "e2e": {"value": B * world / (e2e_ms * 1e-3), "unit": "ids/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": 4096 * 4},
+            "clocks": clocks,
+        })
+    if world > 1:
+        dist.barrier()
+        bag.close()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # ============================================================================ per-operator measurements
 def run_ops(args):
     """`--workload ops`: every other entry point of the path (dedup, key tables, cache policy, bucketize, row
@@ -1057,6 +1445,9 @@ def main():
                          "gradients through NCCL all-to-alls (nccl, the reference's scheme) or stored / loaded inside "
                          "the owners' kernels over peer mappings (fused)")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
+                    help="which BASELINE config: c2 (default, the headline: 26-table DLRM step), c1 (one small table, "
+                         "Adagrad), c3 (multi-hot, Adagrad), c4 (dynamic hash-keyed table), c5 (row-wise sharded large table)")
     args = ap.parse_args()
     if args.exchange == "auto":
         args.exchange = "dedup"
@@ -1067,7 +1458,13 @@ def main():
     else:
         if args.warmup < 3:
             args.warmup = 3
-        if int(os.environ.get("WORLD_SIZE", "1")) > 1 and args.exchange == "dedup":
+        if args.config in ("c1", "c3"):
+            run_tbe_config(args, args.config)
+        elif args.config == "c4":
+            run_c4(args)
+        elif args.config == "c5":
+            run_c5(args)
+        elif int(os.environ.get("WORLD_SIZE", "1")) > 1 and args.exchange == "dedup":
             run_dedup_multi(args)
         else:
             run_ours(args)

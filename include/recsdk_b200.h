@@ -233,6 +233,12 @@ RECSDK_API int recsdk_gather_rows(const float* table, const int64_t* slots, int6
                                   int64_t table_rows, int64_t* dev_status, void* stream);
 RECSDK_API int recsdk_scatter_rows(float* table, const int64_t* slots, int64_t k, int32_t D, const float* rows,
                                    int64_t table_rows, int64_t* dev_status, void* stream);
+/* recsdk_gather_rows with the poll limit of its mbarrier waits as an argument (the default is 2^22 polls).  For
+ * failure-handling tests: with wait_limit 0 the first wait runs out at once, the kernel records RECSDK_ERR_CUDA in the
+ * status block, lets the copies it already issued land (bounded) and returns; `out` is then incomplete.  The context
+ * stays usable. */
+RECSDK_API int recsdk_gather_rows_wait_limit(const float* table, const int64_t* slots, int64_t k, int32_t D, float* out,
+                                             int64_t table_rows, int64_t* dev_status, int32_t wait_limit, void* stream);
 
 /* =========================================================================
  * A9  TF-flavour operators (signatures of cust_op/framework/tf_plugin/src/
@@ -370,6 +376,23 @@ RECSDK_API int recsdk_filter_clear_evict(const recsdk_filter_t* f, void* stream)
 /* count of one key -> *count_out (device), -1 if absent from the count map */
 RECSDK_API int recsdk_filter_count_of(const recsdk_filter_t* f, const int64_t* keys, int64_t n, int64_t* count_out,
                                       void* stream);
+
+/* =========================================================================
+ * Load statistics and tombstone compaction of the open-addressing key tables above (mapper, swap manager: 2 words per
+ * entry; feature filter: 4).  Erases leave TOMBSTONE entries that lookups walk past and that only a rebuild turns back
+ * into EMPTY; the reference's std::unordered_map / flat_hash_map (ids_mapper.h:30-102, swap_manager.h:41-54,
+ * feature_filter.h:26-60) has no such decay, so a long run rebuilds a table when live + tombstones passes ~3/4 of
+ * the capacity.
+ * stats_out (device, 4 words): {live entries, tombstones, longest displacement of a live entry from its home, 0}.
+ * rebuild: collect the live entries into the workspace, clear, insert again (same key -> payload mapping, no
+ * tombstones).  max_live bounds the scratch; when more entries are live nothing is changed and RECSDK_ERR_WORKSPACE is
+ * put into the status block.  Must be ordered against every other call on the same table.
+ * ========================================================================= */
+RECSDK_API int recsdk_key_table_stats(const int64_t* table, int64_t hash_capacity, int32_t entry_words, int64_t* stats_out,
+                                      void* stream);
+RECSDK_API size_t recsdk_key_table_rebuild_workspace_bytes(int64_t max_live, int32_t entry_words);
+RECSDK_API int recsdk_key_table_rebuild(int64_t* table, int64_t hash_capacity, int32_t entry_words, int64_t max_live,
+                                        int64_t* dev_status, void* workspace, size_t workspace_bytes, void* stream);
 
 /* =========================================================================
  * A3  row-hash bucketize for row-wise sharding

@@ -107,6 +107,7 @@ SIGNATURES = {
     "recsdk_tbe_backward": (C.c_int, [C.POINTER(TbeBackwardArgs), vp]),
     "recsdk_adam_beta2sqrt": (C.c_float, [C.c_float, C.c_float, C.c_int64]),
     "recsdk_gather_rows": (C.c_int, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int64, vp, vp]),
+    "recsdk_gather_rows_wait_limit": (C.c_int, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int64, vp, C.c_int32, vp]),
     "recsdk_scatter_rows": (C.c_int, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int64, vp, vp]),
     "recsdk_lookup_by_address": (C.c_int, [vp, C.c_int64, C.c_int32, vp, vp]),
     "recsdk_update_by_address": (C.c_int, [vp, C.c_int64, C.c_int32, vp, C.c_int32, vp]),
@@ -160,6 +161,9 @@ SIGNATURES = {
                                                  C.c_size_t, vp]),
     "recsdk_filter_clear_evict": (C.c_int, [C.POINTER(FilterT), vp]),
     "recsdk_filter_count_of": (C.c_int, [C.POINTER(FilterT), vp, C.c_int64, vp, vp]),
+    "recsdk_key_table_stats": (C.c_int, [vp, C.c_int64, C.c_int32, vp, vp]),
+    "recsdk_key_table_rebuild_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
+    "recsdk_key_table_rebuild": (C.c_int, [vp, C.c_int64, C.c_int32, C.c_int64, vp, vp, C.c_size_t, vp]),
     "recsdk_bucketize_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "recsdk_bucketize": (C.c_int, [vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, vp,
                                    vp, vp, vp, vp, vp, C.c_size_t, vp]),

@@ -699,6 +699,143 @@ static __global__ void __launch_bounds__(256) filter_evict_kernel(recsdk_filter_
 }
 static __global__ void filter_clear_evict_kernel(recsdk_filter_t f) { f.counters[2] = 0; }
 
+
+// ============================================================================ load statistics and tombstone compaction
+// Erased keys leave TOMBSTONE entries behind (a lookup must walk past them), and nothing in the batch phases turns
+// one back into EMPTY: under steady churn -- evictions, cache replacement -- the EMPTY entries only become fewer,
+// and a lookup of an absent key stops only at an EMPTY entry.  So the tables are rebuilt now and then: the live
+// entries are collected into scratch, the table is cleared, the entries are inserted again.  The collect phase
+// counts; when the live entries do not fit the scratch the clear and re-insert phases do nothing (they read the
+// count on the device) and the status block says so.  Must not run concurrently with other work on the table.
+template <int STRIDE>
+static __global__ void __launch_bounds__(256) kt_stats_kernel(const int64_t* __restrict__ table, int64_t cap,
+                                                              int64_t* __restrict__ stats)
+{
+    int64_t live = 0, tomb = 0, maxd = 0;
+    const uint64_t mask = static_cast<uint64_t>(cap) - 1;
+    RECSDK_GRID_STRIDE(e, cap)
+    {
+        const int64_t k = table[e * STRIDE];
+        if (k == kTomb) ++tomb;
+        if (k >= 0) {
+            ++live;
+            const int64_t d = static_cast<int64_t>((static_cast<uint64_t>(e) - (mix64(static_cast<uint64_t>(k)) & mask)) & mask);
+            maxd = d > maxd ? d : maxd;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        live += __shfl_down_sync(kFullMask, live, o);
+        tomb += __shfl_down_sync(kFullMask, tomb, o);
+        const int64_t other = __shfl_down_sync(kFullMask, maxd, o);
+        maxd = other > maxd ? other : maxd;
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(reinterpret_cast<unsigned long long*>(stats), static_cast<unsigned long long>(live));
+        atomicAdd(reinterpret_cast<unsigned long long*>(stats + 1), static_cast<unsigned long long>(tomb));
+        atomic_max_i64(stats + 2, maxd);
+    }
+}
+
+template <int STRIDE>
+static __global__ void __launch_bounds__(256) kt_collect_kernel(const int64_t* __restrict__ table, int64_t cap,
+                                                                int64_t* __restrict__ list, int64_t max_live,
+                                                                int64_t* __restrict__ counter)
+{
+    RECSDK_GRID_STRIDE(e, cap)
+    {
+        if (table[e * STRIDE] < 0) continue;
+        const int64_t i = static_cast<int64_t>(atomicAdd(reinterpret_cast<unsigned long long*>(counter), 1ull));
+        if (i >= max_live) continue;
+#pragma unroll
+        for (int w = 0; w < STRIDE; ++w) list[i * STRIDE + w] = table[e * STRIDE + w];
+    }
+}
+
+template <int STRIDE>
+static __global__ void __launch_bounds__(256) kt_clear_kernel(int64_t* __restrict__ table, int64_t cap, int64_t max_live,
+                                                              const int64_t* __restrict__ counter, int64_t* status)
+{
+    if (*counter > max_live) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) set_status(status, RECSDK_ERR_WORKSPACE, *counter, max_live);
+        return;
+    }
+    RECSDK_GRID_STRIDE(e, cap)
+    {
+        table[e * STRIDE] = kEmpty;
+        if (STRIDE == 2) table[e * STRIDE + 1] = kValFree;
+        if (STRIDE == 4) {
+            table[e * STRIDE + 1] = 0;
+            table[e * STRIDE + 2] = kTsNone;
+            table[e * STRIDE + 3] = 0;
+        }
+    }
+}
+
+template <int STRIDE>
+static __global__ void __launch_bounds__(256) kt_reinsert_kernel(int64_t* __restrict__ table, int64_t cap,
+                                                                 const int64_t* __restrict__ list, int64_t max_live,
+                                                                 const int64_t* __restrict__ counter, int64_t* status)
+{
+    const int64_t n = *counter;
+    if (n > max_live) return;
+    RECSDK_GRID_STRIDE(i, n)
+    {
+        const int64_t e = ht_insert<STRIDE>(table, cap, list[i * STRIDE]);
+        if (e < 0) {
+            set_status(status, RECSDK_ERR_HASH_FULL, list[i * STRIDE], i);
+            continue;
+        }
+#pragma unroll
+        for (int w = 1; w < STRIDE; ++w) table[e * STRIDE + w] = list[i * STRIDE + w];
+    }
+}
+
+}  // namespace recsdk
+using namespace recsdk;
+
+extern "C" int recsdk_key_table_stats(const int64_t* table, int64_t hash_capacity, int32_t entry_words, int64_t* stats_out,
+                                      void* stream)
+{
+    if (!table || !stats_out || !is_pow2(hash_capacity) || (entry_words != 2 && entry_words != 4)) return RECSDK_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaMemsetAsync(stats_out, 0, 4 * sizeof(int64_t), st);
+    const int grid = grid_for(hash_capacity, 256, 8);
+    if (entry_words == 2) kt_stats_kernel<2><<<grid, 256, 0, st>>>(table, hash_capacity, stats_out);
+    else kt_stats_kernel<4><<<grid, 256, 0, st>>>(table, hash_capacity, stats_out);
+    RECSDK_CUDA_CHECK_LAUNCH();
+    return RECSDK_OK;
+}
+
+extern "C" size_t recsdk_key_table_rebuild_workspace_bytes(int64_t max_live, int32_t entry_words)
+{
+    return align_up(8 * sizeof(int64_t)) + align_up(static_cast<size_t>(max_live > 0 ? max_live : 1) * entry_words * sizeof(int64_t));
+}
+
+extern "C" int recsdk_key_table_rebuild(int64_t* table, int64_t hash_capacity, int32_t entry_words, int64_t max_live,
+                                        int64_t* dev_status, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (!table || !is_pow2(hash_capacity) || (entry_words != 2 && entry_words != 4) || max_live <= 0) return RECSDK_ERR_INVALID_ARG;
+    if (!workspace || workspace_bytes < recsdk_key_table_rebuild_workspace_bytes(max_live, entry_words)) return RECSDK_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int64_t* counter = static_cast<int64_t*>(workspace);
+    int64_t* list = reinterpret_cast<int64_t*>(static_cast<char*>(workspace) + align_up(8 * sizeof(int64_t)));
+    cudaMemsetAsync(counter, 0, 8 * sizeof(int64_t), st);
+    const int grid = grid_for(hash_capacity, 256, 8), grid2 = grid_for(max_live, 256, 8);
+    if (entry_words == 2) {
+        kt_collect_kernel<2><<<grid, 256, 0, st>>>(table, hash_capacity, list, max_live, counter);
+        kt_clear_kernel<2><<<grid, 256, 0, st>>>(table, hash_capacity, max_live, counter, dev_status);
+        kt_reinsert_kernel<2><<<grid2, 256, 0, st>>>(table, hash_capacity, list, max_live, counter, dev_status);
+    } else {
+        kt_collect_kernel<4><<<grid, 256, 0, st>>>(table, hash_capacity, list, max_live, counter);
+        kt_clear_kernel<4><<<grid, 256, 0, st>>>(table, hash_capacity, max_live, counter, dev_status);
+        kt_reinsert_kernel<4><<<grid2, 256, 0, st>>>(table, hash_capacity, list, max_live, counter, dev_status);
+    }
+    RECSDK_CUDA_CHECK_LAUNCH();
+    return RECSDK_OK;
+}
+
+namespace recsdk {
 }  // namespace recsdk
 
 using namespace recsdk;

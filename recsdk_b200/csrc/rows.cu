@@ -25,7 +25,8 @@ template <bool GATHER>
 __global__ void __launch_bounds__(kTmaWarps * 32) rows_tma_kernel(float* __restrict__ table,
                                                                   const int64_t* __restrict__ slots, int64_t k,
                                                                   int32_t D, float* __restrict__ dense,
-                                                                  int64_t table_rows, int64_t* __restrict__ status)
+                                                                  int64_t table_rows, int64_t* __restrict__ status,
+                                                                  int wait_limit)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bars[kTmaWarps][kStages];
@@ -93,9 +94,13 @@ __global__ void __launch_bounds__(kTmaWarps * 32) rows_tma_kernel(float* __restr
             __syncwarp();
             issue_load(next, nstage);
         }
-        if (!mbar_wait_bounded(&bars[warp][stage], phase[stage])) {
+        if (!mbar_wait_bounded(&bars[warp][stage], phase[stage], wait_limit)) {
+            // the wait ran out: report, stop taking work, and give the loads already issued (this stage, and the next
+            // one when it was armed) a bounded time to land before the block's shared memory is released
             set_status(status, RECSDK_ERR_CUDA, -1, batch);
             failed = true;
+            (void)mbar_wait_bounded(&bars[warp][stage], phase[stage]);
+            if (next < nbatch) (void)mbar_wait_bounded(&bars[warp][nstage], phase[nstage]);
             break;
         }
         phase[stage] ^= 1;
@@ -131,7 +136,7 @@ __global__ void __launch_bounds__(256) rows_plain_kernel(float* __restrict__ tab
 
 template <bool GATHER>
 static int launch_rows(float* table, const int64_t* slots, int64_t k, int32_t D, float* dense, int64_t table_rows,
-                       int64_t* status, cudaStream_t st)
+                       int64_t* status, cudaStream_t st, int wait_limit = 1 << 22)
 {
     if (k == 0) return RECSDK_OK;
     const size_t row_bytes = static_cast<size_t>(D) * 4;
@@ -145,7 +150,7 @@ static int launch_rows(float* table, const int64_t* slots, int64_t k, int32_t D,
         }
         const int64_t nbatch = ceil_div(k, kRowsPerStage);
         int grid = grid_for(nbatch, kTmaWarps, 8);
-        kern<<<grid, kTmaWarps * 32, smem, st>>>(table, slots, k, D, dense, table_rows, status);
+        kern<<<grid, kTmaWarps * 32, smem, st>>>(table, slots, k, D, dense, table_rows, status, wait_limit);
     } else {
         rows_plain_kernel<GATHER><<<grid_for(k, 8), 256, 0, st>>>(table, slots, k, D, dense, table_rows, status);
     }
@@ -289,6 +294,15 @@ extern "C" int recsdk_gather_rows(const float* table, const int64_t* slots, int6
     if (k > 0 && (!table || !slots || !out)) return RECSDK_ERR_INVALID_ARG;
     return launch_rows<true>(const_cast<float*>(table), slots, k, D, out, table_rows, dev_status,
                              static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int recsdk_gather_rows_wait_limit(const float* table, const int64_t* slots, int64_t k, int32_t D, float* out,
+                                             int64_t table_rows, int64_t* dev_status, int32_t wait_limit, void* stream)
+{
+    if (k < 0 || D <= 0 || wait_limit < 0) return RECSDK_ERR_INVALID_ARG;
+    if (k > 0 && (!table || !slots || !out)) return RECSDK_ERR_INVALID_ARG;
+    return launch_rows<true>(const_cast<float*>(table), slots, k, D, out, table_rows, dev_status,
+                             static_cast<cudaStream_t>(stream), wait_limit);
 }
 
 extern "C" int recsdk_scatter_rows(float* table, const int64_t* slots, int64_t k, int32_t D, const float* rows,

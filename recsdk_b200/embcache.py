@@ -321,6 +321,9 @@ class EmbcacheManager:
             self.swap_managers[i].RemoveKeys(keys, count)  # the count stays on the device: no synchronisation
             self._evict_swap_count[i] = self.swap_count  # evictFeatureRecord_.SetSwapCount (embcache_manager.cpp:710)
             total += int(count.item())
+            # an eviction round turns entries of both tables into tombstones: rebuild them when they pile up
+            f.compact_if_needed()
+            self.swap_managers[i].compact_if_needed()
         return total
 
     def evicted_keys(self, table_index: int) -> torch.Tensor:

@@ -128,7 +128,37 @@ class IdsMapper:
                 m.raise_if_error("parallel_ids2indices_unique_out")
 
 
-class SwapManager:
+class _KeyTableCare:
+    """Load statistics and tombstone compaction shared by the three key tables (`self._table`, `self._cap`,
+    `self._entry_words`, `self._max_live`, `self._status`, `self._lib`, `self.device`)."""
+
+    def table_stats(self):
+        """(live entries, tombstones, longest displacement, capacity) of the key table; synchronises."""
+        st = torch.zeros(4, dtype=torch.int64, device=self.device)
+        _lib.check(self._lib.recsdk_key_table_stats(_ptr(self._table), self._cap, self._entry_words, _ptr(st), _stream()),
+                   "recsdk_key_table_stats")
+        live, tomb, disp, _ = st.tolist()
+        return live, tomb, disp, self._cap
+
+    def compact(self) -> None:
+        """Rebuild the key table without tombstones (stream-ordered; nothing else may run on the table meanwhile)."""
+        need = self._lib.recsdk_key_table_rebuild_workspace_bytes(self._max_live, self._entry_words)
+        ws = _workspace(need, self.device)
+        _lib.check(self._lib.recsdk_key_table_rebuild(_ptr(self._table), self._cap, self._entry_words, self._max_live,
+                                                      _ptr(self._status), _ptr(ws), ws.numel(), _stream()),
+                   "recsdk_key_table_rebuild")
+
+    def compact_if_needed(self, threshold: float = 0.75) -> bool:
+        """Compacts when live + tombstones exceed `threshold` of the capacity (one host read).  The callers that own
+        a natural point for it (after an eviction round, every so many slot-policy steps) call this themselves."""
+        live, tomb, _, cap = self.table_stats()
+        if tomb > 0 and live + tomb > threshold * cap:
+            self.compact()
+            return True
+        return False
+
+
+class SwapManager(_KeyTableCare):
     """Slot policy of the HBM cache (hit / append / clock-sweep replacement)."""
 
     def __init__(self, cacheSize: int, memStartOffset: int = 0, device="cuda", load_factor: float = 0.5):
@@ -145,6 +175,8 @@ class SwapManager:
         self._c = _lib.SwapT(_ptr(self._table), cap, _ptr(self._slot_key), _ptr(self._slot_version),
                              _ptr(self._counters), self.cacheSize, self.memStartOffset)
         self._ws: Optional[torch.Tensor] = None
+        self._cap, self._entry_words, self._max_live = cap, 2, self.cacheSize
+        self._calls_since_check = 0
         with torch.cuda.device(self.device):
             _lib.check(self._lib.recsdk_swap_init(C.byref(self._c), _stream()), "recsdk_swap_init")
 
@@ -174,6 +206,10 @@ class SwapManager:
         sok, soo, sik, sio, bo, counts = self.ComputeSwapInfoDevice(keys)
         self.raise_if_error("ComputeSwapInfo")
         nin, nout = counts.tolist()
+        self._calls_since_check += 1
+        if self._calls_since_check >= 256:  # replacement and RemoveKeys leave tombstones: look now and then
+            self._calls_since_check = 0
+            self.compact_if_needed()
         return sok[:nout], soo[:nout], sik[:nin], sio[:nin], bo
 
     def RemoveKeys(self, keys: torch.Tensor, n_keys_dev: Optional[torch.Tensor] = None) -> None:
@@ -199,7 +235,7 @@ class SwapManager:
         return int(self._slot_key[off].item())
 
 
-class FeatureFilter:
+class FeatureFilter(_KeyTableCare):
     """Count-based admission and timestamp eviction, per-key state in HBM.
 
     ``capacity`` bounds the number of distinct keys tracked at once (admitted or not)."""
@@ -213,6 +249,7 @@ class FeatureFilter:
         self._table = torch.empty(cap * 4, dtype=torch.int64, device=self.device)
         self._counters = torch.zeros(4, dtype=torch.int64, device=self.device)
         self._status = new_status(self.device)
+        self._cap, self._entry_words, self._max_live = cap, 4, int(capacity)
         self._evict_cap = int(evict_list_capacity or capacity)
         self._evict_keys = torch.empty(self._evict_cap, dtype=torch.int64, device=self.device)
         self._c = _lib.FilterT(_ptr(self._table), cap, _ptr(self._counters), int(admitThreshold), int(evictThreshold),

@@ -370,3 +370,78 @@ def test_restore():
     exp = port.restore(uq, inv, uoff, tab_off)
     got = ops.restore(_t(uq), _t(inv), _t(uoff), tab_off.tolist())
     np.testing.assert_array_equal(_np(got), exp)
+
+
+def test_long_churn_keeps_probe_chains_bounded():
+    """Small tables under thousands of steps of churn (new keys every step, eviction every 4 steps, cache
+    replacement): without compaction the EMPTY entries of the open-addressing tables run out; with it the results
+    still match the CPU classes step by step and the longest displacement stays small."""
+    from recsdk_b200.embcache import AdmitAndEvictConfig, EmbcacheManager, EmbConfig
+
+    steps, n, interval, cache = 3000, 96, 4, 1024
+    cfg = EmbConfig("t", emb_dim=4, optim_num=0, cache_size=cache, weight_init_max=1.0,
+                    admit_and_evict_config=AdmitAndEvictConfig(-1, 0.0, 3, interval), filter_capacity=1024)
+    mgr = EmbcacheManager([cfg], device=DEV)
+    sw, fl = port.SwapManager(cache, 0), port.FeatureFilter(-1, 3, interval)
+    rng = np.random.default_rng(77)
+    recent = rng.integers(0, 2**62, size=n, dtype=np.int64)
+    compactions = 0
+    worst = 0
+    for s in range(steps):
+        fresh = rng.integers(0, 2**62, size=n // 2, dtype=np.int64)
+        keys = np.concatenate([fresh, recent[rng.integers(0, recent.size, size=n - fresh.size)]])
+        recent = np.concatenate([recent[-2 * n:], fresh])
+        uq = first_occurrence_unique(keys)
+        d_keys = torch.from_numpy(keys).to(DEV)
+        mgr.record_timestamp(d_keys, [0, keys.size], torch.full((keys.size,), s, dtype=torch.int64, device=DEV))
+        fl.record_timestamp(keys, np.full(keys.size, s, np.int64))
+        if s > 0 and (s + 1) % interval == 0:
+            before = mgr.feature_filters[0].table_stats()[1] + mgr.swap_managers[0].table_stats()[1]
+            mgr.evict_features()
+            after = mgr.feature_filters[0].table_stats()[1] + mgr.swap_managers[0].table_stats()[1]
+            compactions += int(after < before)
+            ev = fl.evict_keys()
+            np.testing.assert_array_equal(np.sort(mgr.evicted_keys(0).cpu().numpy()), np.sort(ev))
+            mgr.remove_embedding_table_info()
+            sw.remove_keys(ev)
+            fl.clear_evict()
+        info = mgr.compute_swap_info(torch.from_numpy(uq).to(DEV), [0, uq.size])
+        exp = sw.compute_swap_info(uq)
+        np.testing.assert_array_equal(info.batch_offs.cpu().numpy(), exp[4])
+        np.testing.assert_array_equal(info.swapout_keys[0].cpu().numpy(), exp[0])
+        if s % 250 == 249:
+            worst = max(worst, mgr.feature_filters[0].table_stats()[2], mgr.swap_managers[0].table_stats()[2])
+    assert compactions > 0  # the tables were rebuilt along the way
+    assert worst < 256  # displacement from the home entry stays far below the capacity (2048 / 4096 entries)
+
+
+def test_bounded_wait_runs_out_cleanly():
+    """The row mover's mbarrier waits are bounded.  With a poll limit of 0 the first wait gives up at once: the
+    kernel must record RECSDK_ERR_CUDA in the status block and return (after letting its own copies land), and the
+    context must stay usable -- the same call with the normal limit then moves the rows."""
+    import ctypes as C
+
+    from recsdk_b200 import _lib, ops
+
+    lib = _lib.load()
+    rng = np.random.default_rng(4)
+    rows, dim, k = 4096, 64, 512
+    table = _t(rng.standard_normal((rows, dim)).astype(np.float32))
+    slots = _t(rng.permutation(rows)[:k].astype(np.int64))
+    out = torch.zeros((k, dim), dtype=torch.float32, device=DEV)
+    st = ops.new_status(DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = lib.recsdk_gather_rows_wait_limit(table.data_ptr(), slots.data_ptr(), k, dim, out.data_ptr(), rows, st.data_ptr(), 0,
+                                           stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    code = st.tolist()[0]
+    assert code == _lib.ERR_CUDA
+    with pytest.raises(RuntimeError):
+        ops.raise_on_status(st)
+    rc = lib.recsdk_gather_rows_wait_limit(table.data_ptr(), slots.data_ptr(), k, dim, out.data_ptr(), rows, st.data_ptr(),
+                                           1 << 22, stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 0
+    np.testing.assert_array_equal(_np(out), _np(table)[_np(slots)])
