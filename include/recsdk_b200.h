@@ -41,7 +41,8 @@ enum {
     RECSDK_ERR_CACHE_TOO_SMALL = 6, /* torchrec_embcache/csrc/embedding_cache/swap_manager.cpp:114-116      */
     RECSDK_ERR_INDEX_RANGE = 7,     /* a row index / slot / offset outside its table                        */
     RECSDK_ERR_HASH_FULL = 8,       /* open-addressing key table has no free entry left                     */
-    RECSDK_ERR_TOO_LARGE = 9        /* size beyond a stated maximum                                         */
+    RECSDK_ERR_TOO_LARGE = 9,       /* size beyond a stated maximum                                         */
+    RECSDK_ERR_STATIC_SCRATCH = 10  /* the library's built-in scratch array could not be located on this device     */
 };
 
 /* Device status block: 4 x int64 {code, detail0, detail1, reserved}.  The first
@@ -134,7 +135,11 @@ RECSDK_API int recsdk_unique_sorted(const int64_t* ids, int64_t n, int key_bits,
  *   - every GPU that loads the library holds the scratch (8 MiB) until the process exits;
  *   - the first call on a device resolves the array's device address
  *     (cudaGetSymbolAddress, once per device, with that device current): make that first
- *     call before starting any stream capture;
+ *     call before starting any stream capture.  It is also a warm-up: CUDA loads a library's
+ *     device image lazily, so the first use of this file's code on a device is when the
+ *     driver places the image -- the 8 MiB array included -- in device memory.  Make that
+ *     first call (n = 0 is enough) during start-up, where allocating is still allowed; a
+ *     failure to locate the array is reported as RECSDK_ERR_STATIC_SCRATCH;
  *   - all calls on a device share the scratch and it keeps the previous call's contents
  *     (nothing needs to start at zero: every word is written before it is read); calls whose
  *     kernels overlap on the GPU race on it, so serialise them (one stream, or events).

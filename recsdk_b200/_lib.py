@@ -20,7 +20,7 @@ STATUS_WORDS = 4
 
 OK = 0
 ERR_INVALID_ARG, ERR_WORKSPACE, ERR_CUDA, ERR_NEGATIVE_KEY, ERR_TABLE_FULL = 1, 2, 3, 4, 5
-ERR_CACHE_TOO_SMALL, ERR_INDEX_RANGE, ERR_HASH_FULL, ERR_TOO_LARGE = 6, 7, 8, 9
+ERR_CACHE_TOO_SMALL, ERR_INDEX_RANGE, ERR_HASH_FULL, ERR_TOO_LARGE, ERR_STATIC_SCRATCH = 6, 7, 8, 9, 10
 
 POOL_SUM, POOL_MEAN, POOL_NONE = 0, 1, 2
 OPT_ADAGRAD, OPT_ADAM, OPT_SGD = 1, 2, 3

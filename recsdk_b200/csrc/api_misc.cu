@@ -21,6 +21,7 @@ extern "C" const char* recsdk_error_string(int code)
         case RECSDK_ERR_INDEX_RANGE: return "row index out of range";
         case RECSDK_ERR_HASH_FULL: return "key table has no free entry";
         case RECSDK_ERR_TOO_LARGE: return "size beyond the supported maximum";
+        case RECSDK_ERR_STATIC_SCRATCH: return "the built-in scratch array could not be located on this device";
         default: return "unknown error";
     }
 }

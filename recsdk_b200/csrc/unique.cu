@@ -121,7 +121,9 @@ extern "C" int recsdk_unique_sorted(const int64_t* ids, int64_t n, int key_bits,
 // The array's name is only a host-side stand-in for the symbol: its device address
 // is resolved with cudaGetSymbolAddress, once per device, on the first call made with
 // that device current.  That first call should therefore happen before any stream
-// capture is started.  All calls on one device share the same scratch, which keeps the
+// capture is started -- and during start-up: with lazy module loading the driver places
+// this file's device image (the array included) in device memory at its first use, so
+// the first call is the one call of this entry point that can make the driver allocate.  All calls on one device share the same scratch, which keeps the
 // contents of the previous call: nothing in this pipeline needs it zeroed (every
 // scratch word is written before it is read), but two calls whose kernels overlap on
 // the GPU (different streams) race on it -- serialise them.
@@ -147,7 +149,10 @@ static int unique_static_scratch(void** out)
     if (g_unique_static_ptr[dev] == nullptr) {
         if (carve_unique(nullptr, kUniqueStaticMaxN).bytes > kUniqueStaticBytes) return RECSDK_ERR_WORKSPACE;
         void* ptr = nullptr;
-        if (cudaGetSymbolAddress(&ptr, g_unique_static_scratch) != cudaSuccess || ptr == nullptr) return RECSDK_ERR_CUDA;
+        if (cudaGetSymbolAddress(&ptr, g_unique_static_scratch) != cudaSuccess || ptr == nullptr) {
+            (void)cudaGetLastError();
+            return RECSDK_ERR_STATIC_SCRATCH;
+        }
         g_unique_static_ptr[dev] = ptr;
     }
     *out = g_unique_static_ptr[dev];

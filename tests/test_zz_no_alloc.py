@@ -25,9 +25,17 @@ def _call_static(lib, ids, bits):
     inv = torch.full((max(n, 1),), -1, dtype=torch.int64, device=DEV)
     cnt = torch.full((1,), -1, dtype=torch.int64, device=DEV)
     st = torch.cuda.current_stream().cuda_stream
+    # warm-up: the first call on a device locates the array (and is when the driver loads this code's device image);
+    # the check below is about the calls after it
+    warm = torch.empty(0, dtype=torch.int64, device=DEV)
+    assert lib.recsdk_unique_sorted_static(warm.data_ptr(), 0, 64, uq.data_ptr(), inv.data_ptr(), cnt.data_ptr(), st) == 0
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = lib.recsdk_unique_sorted_static(ids.data_ptr(), n, bits, uq.data_ptr(), inv.data_ptr(), cnt.data_ptr(), st)
-    assert torch.cuda.memory_allocated() == before  # nothing was allocated through torch either
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before  # nothing was allocated through torch
+    assert torch.cuda.mem_get_info()[0] >= free_before  # nor by the driver: the device's free memory did not shrink
     return rc, uq, inv, cnt
 
 
