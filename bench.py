@@ -577,6 +577,9 @@ def run_dedup_multi(args):
             mark()
             bag.forward(batches[i % n_batches] if ids is None else ids, offsets, out=out)
             mark()
+            if args.owner_plan == "ahead":
+                bag.fence()  # the ids of every rank are in the owners' inboxes
+                bag.plan_owner_ahead()  # the owner phase's index work runs beside the local phase, on a side stream
             bag.backward_local(grad)
             mark()
             bag.fence()
@@ -702,7 +705,8 @@ def run_dedup_multi(args):
                 "exchange": "device-driven dedup exchange over peer mappings: distinct ids and counts stored into the "
                             "owners' inboxes, distinct rows loaded from the owners' tables, per-row gradient sums stored "
                             "into the owners' inboxes, counts read on the device; two one-element NCCL all-reduces per "
-                            "step as fences",
+                            "step as fences" + (", a third one after the forward so that the owner phase's index work runs "
+                                                "beside the local backward phase" if args.owner_plan == "ahead" else ""),
             },
             "parity_check": parity,
             "step_hbm_gbs_rank0": step_bytes / (weak["ms_step"] * 1e-3) / 1e9,
@@ -1444,6 +1448,10 @@ def main():
                          "rows they need from the table owners and pool locally.  Kept as baselines: pooled rows / "
                          "gradients through NCCL all-to-alls (nccl, the reference's scheme) or stored / loaded inside "
                          "the owners' kernels over peer mappings (fused)")
+    ap.add_argument("--owner-plan", default="ahead", choices=["ahead", "inline"],
+                    help="N>1: where the owner phase of the exchange makes its plan (sort of the received ids, runs, "
+                         "records): ahead = on a side stream beside the local backward phase, after one more fence; "
+                         "inline = inside the owner phase")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
                     help="which BASELINE config: c2 (default, the headline: 26-table DLRM step), c1 (one small table, "

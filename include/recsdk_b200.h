@@ -538,10 +538,16 @@ RECSDK_API int recsdk_xchg_backward_local(const recsdk_xchg_t* x, const float* g
                                           int64_t N, int32_t pooling_mode, int32_t gradient_clipping,
                                           float max_gradient, void* stream);
 /* Updates this rank's table in place from its inbox.  ev_update_*: optional cudaEvent_t recorded around the row-update
- * kernel. */
+ * kernel.  flags 0: the whole phase.  PLAN_ONLY / APPLY_ONLY split it: the plan (compaction of the id lists, sort, runs,
+ * per-row records) reads only the ids and counts, which are complete once every rank's forward has run, so a caller
+ * that fences after the forward can run it on a second stream beside recsdk_xchg_backward_local; the apply call (row
+ * update) then follows the gradient fence and an event wait on the plan. */
+#define RECSDK_XCHG_OWNER_PLAN_ONLY 1
+#define RECSDK_XCHG_OWNER_APPLY_ONLY 2
 RECSDK_API int recsdk_xchg_backward_owner(const recsdk_xchg_t* x, float* weights, float* momentum1, float* momentum2,
                                           int32_t optimizer, float learning_rate, float eps, float beta1, float beta2,
-                                          int64_t iter, void* ev_update_start, void* ev_update_stop, void* stream);
+                                          int64_t iter, void* ev_update_start, void* ev_update_stop, int32_t flags,
+                                          void* stream);
 /* Plan counters of the most recent step, copied to host memory (6 words): [0] distinct rows this rank asked for,
  * [1] ids this rank received as an owner, [2] distinct rows it updated, [3] ids in chunked local runs, [4] how many
  * of [0] this rank owns itself (the others crossed the links), [5] chunk sums of the local phase.  Synchronises the

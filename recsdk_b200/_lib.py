@@ -131,7 +131,7 @@ SIGNATURES = {
     "recsdk_xchg_forward": (C.c_int, [C.POINTER(XchgT), vp, vp, C.c_int64, C.c_int32, vp, vp]),
     "recsdk_xchg_backward_local": (C.c_int, [C.POINTER(XchgT), vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_float, vp]),
     "recsdk_xchg_backward_owner": (C.c_int, [C.POINTER(XchgT), vp, vp, vp, C.c_int32, C.c_float, C.c_float, C.c_float,
-                                             C.c_float, C.c_int64, vp, vp, vp]),
+                                             C.c_float, C.c_int64, vp, vp, C.c_int32, vp]),
     "recsdk_xchg_counters": (C.c_int, [C.POINTER(XchgT), C.POINTER(C.c_int64), vp]),
     "recsdk_host_table_create": (vp, [C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float, C.c_float, C.c_float,
                                       C.c_int64, C.c_int64]),

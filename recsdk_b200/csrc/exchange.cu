@@ -709,8 +709,10 @@ static void xchg_launch_update(const BwdParams& p, const RunMeta* meta, int64_t 
 
 template <typename KeyT>
 static int xchg_owner_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, BwdParams p, void* ev0, void* ev1,
-                           cudaStream_t st)
+                           int32_t flags, cudaStream_t st)
 {
+    const bool do_plan = (flags & RECSDK_XCHG_OWNER_APPLY_ONLY) == 0;
+    const bool do_apply = (flags & RECSDK_XCHG_OWNER_PLAN_ONLY) == 0;
     const XchgParams q = xchg_params(x, 0, RECSDK_POOL_NONE);
     const int64_t n_cap = static_cast<int64_t>(x->world) * x->inbox_cap;
     const int key_bits = xchg_bits_for(x->local_rows);
@@ -721,17 +723,26 @@ static int xchg_owner_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, BwdP
     const int which = passes & 1;
     const KeyT* keys = which ? kb : ka;
     p.vals = which ? ws.ovals_b : ws.ovals_a;
-    cudaMemsetAsync(ws.oc, 0, 8 * sizeof(int64_t), st);
-    const RadixFusedPlan plan = radix_fused_begin(n_cap, key_bits, ws.osort_scratch, st);
-    xchg_owner_expand_kernel<KeyT><<<grid_for(n_cap, 256), 256, 0, st>>>(q, x->inbox_ids[x->rank], x->inbox_counts[x->rank],
-                                                                         ka, ws.ovals_a, plan.first, ws.oc, ws.lay_i64,
-                                                                         ws.lay_i32, x->local_rows);
-    const int64_t* n_dev = ws.oc + 4;
-    const int got = radix_sort_pairs_fused<KeyT>(plan, ka, ws.ovals_a, kb, ws.ovals_b, n_cap, ws.osort_scratch, st, n_dev);
-    if (got != which) return RECSDK_ERR_CUDA;
-    device_scan_fn<true>(HeadFlagIn<KeyT>{keys}, RunStartOut{ws.orun_start, ws.oc}, n_cap, ws.oscan_scratch, nullptr, st,
-                         n_dev);
-    run_meta_kernel<KeyT><<<grid_for(n_cap, 256), 256, 0, st>>>(p, keys, ws.oc, ws.ometa, ws.odesc);
+    if (do_plan) {
+        // needs the ids and counts in the inbox only (they arrive with the forwards of all ranks), not the gradient
+        // sums: it can run beside this rank's local backward phase, on another stream, after a fence of its own
+        cudaMemsetAsync(ws.oc, 0, 8 * sizeof(int64_t), st);
+        const RadixFusedPlan plan = radix_fused_begin(n_cap, key_bits, ws.osort_scratch, st);
+        xchg_owner_expand_kernel<KeyT><<<grid_for(n_cap, 256), 256, 0, st>>>(q, x->inbox_ids[x->rank],
+                                                                             x->inbox_counts[x->rank], ka, ws.ovals_a,
+                                                                             plan.first, ws.oc, ws.lay_i64, ws.lay_i32,
+                                                                             x->local_rows);
+        const int64_t* n_dev = ws.oc + 4;
+        const int got = radix_sort_pairs_fused<KeyT>(plan, ka, ws.ovals_a, kb, ws.ovals_b, n_cap, ws.osort_scratch, st, n_dev);
+        if (got != which) return RECSDK_ERR_CUDA;
+        device_scan_fn<true>(HeadFlagIn<KeyT>{keys}, RunStartOut{ws.orun_start, ws.oc}, n_cap, ws.oscan_scratch, nullptr, st,
+                             n_dev);
+        run_meta_kernel<KeyT><<<grid_for(n_cap, 256), 256, 0, st>>>(p, keys, ws.oc, ws.ometa, ws.odesc);
+    }
+    if (!do_apply) {
+        RECSDK_CUDA_CHECK_LAUNCH();
+        return RECSDK_OK;
+    }
     const int vec_per_row = x->D >> 2;
     if (x->world > p.direct_max) {  // a row has at most one contribution per source rank: no run is longer than `world`
 #define CALL_PARTIAL(G, K) xchg_launch_partial<G, K>(p, n_cap, st)
@@ -799,9 +810,11 @@ extern "C" int recsdk_xchg_backward_local(const recsdk_xchg_t* x, const float* g
 
 extern "C" int recsdk_xchg_backward_owner(const recsdk_xchg_t* x, float* weights, float* momentum1, float* momentum2,
                                           int32_t optimizer, float learning_rate, float eps, float beta1, float beta2,
-                                          int64_t iter, void* ev_update_start, void* ev_update_stop, void* stream)
+                                          int64_t iter, void* ev_update_start, void* ev_update_stop, int32_t flags,
+                                          void* stream)
 {
     const int rc = xchg_validate(x, 0);
+    if ((flags & RECSDK_XCHG_OWNER_PLAN_ONLY) && (flags & RECSDK_XCHG_OWNER_APPLY_ONLY)) return RECSDK_ERR_INVALID_ARG;
     if (rc != RECSDK_OK) return rc;
     if (optimizer < RECSDK_OPT_ADAGRAD || optimizer > RECSDK_OPT_SGD || !weights) return RECSDK_ERR_INVALID_ARG;
     if (optimizer != RECSDK_OPT_SGD && !momentum1) return RECSDK_ERR_INVALID_ARG;
@@ -841,8 +854,8 @@ extern "C" int recsdk_xchg_backward_owner(const recsdk_xchg_t* x, float* weights
     p.chunk_desc = ws.odesc;
     p.partial = ws.opartial;
     p.counters = ws.oc;
-    if (xchg_bits_for(x->local_rows) <= 32) return xchg_owner_impl<uint32_t>(x, ws, p, ev_update_start, ev_update_stop, st);
-    return xchg_owner_impl<uint64_t>(x, ws, p, ev_update_start, ev_update_stop, st);
+    if (xchg_bits_for(x->local_rows) <= 32) return xchg_owner_impl<uint32_t>(x, ws, p, ev_update_start, ev_update_stop, flags, st);
+    return xchg_owner_impl<uint64_t>(x, ws, p, ev_update_start, ev_update_stop, flags, st);
 }
 
 extern "C" int recsdk_xchg_counters(const recsdk_xchg_t* x, int64_t* out6, void* stream)

@@ -158,6 +158,9 @@ class DedupExchange:
         self._token = None
         self._offsets = None
         self._N = 0
+        self._plan_stream = None
+        self._plan_event = None
+        self._owner_planned = False
         if world == 1:
             connect_local([self])
 
@@ -246,8 +249,7 @@ class DedupExchange:
                                                      self._N, int(self.pooling_mode), int(self.gradient_clipping),
                                                      self.max_gradient, _stream()), "recsdk_xchg_backward_local")
 
-    def backward_owner(self, update_events=None) -> None:
-        self.iter += 1
+    def _owner_call(self, flags: int, update_events=None, stream=None) -> None:
         ev0 = update_events[0].cuda_event if update_events else None
         ev1 = update_events[1].cuda_event if update_events else None
         h = self.hp
@@ -255,10 +257,39 @@ class DedupExchange:
             C.byref(self._x), self.weights_dev.data_ptr(),
             self.momentum1_dev.data_ptr() if self.momentum1_dev is not None else None,
             self.momentum2_dev.data_ptr() if self.momentum2_dev is not None else None, _OPT_CODE[self.optimizer],
-            h["lr"], h["eps"], h["beta1"], h["beta2"], self.iter, ev0, ev1, _stream()), "recsdk_xchg_backward_owner")
+            h["lr"], h["eps"], h["beta1"], h["beta2"], self.iter, ev0, ev1, flags,
+            _stream() if stream is None else stream.cuda_stream), "recsdk_xchg_backward_owner")
 
-    def backward(self, grad_output: torch.Tensor, update_events=None) -> None:
-        """All three backward steps of this rank with the fences between them (every rank calls it)."""
+    def backward_owner(self, update_events=None) -> None:
+        """The whole owner phase on the current stream (after the fence that follows backward_local)."""
+        self.iter += 1
+        if self._owner_planned:
+            torch.cuda.current_stream(self.device).wait_event(self._plan_event)
+            self._owner_planned = False
+            self._owner_call(2, update_events)  # RECSDK_XCHG_OWNER_APPLY_ONLY
+        else:
+            self._owner_call(0, update_events)
+
+    def plan_owner_ahead(self) -> None:
+        """Call after a fence that follows every rank's forward: the owner phase's index work (compaction of the id
+        lists, sort, runs, records) is enqueued on a high-priority side stream, where it runs beside
+        backward_local; backward_owner then only waits for it and updates the rows."""
+        cur = torch.cuda.current_stream(self.device)
+        if self._plan_stream is None:
+            self._plan_stream = torch.cuda.Stream(device=self.device, priority=-1)
+            self._plan_event = torch.cuda.Event()
+        self._plan_stream.wait_stream(cur)
+        self._owner_call(1, stream=self._plan_stream)  # RECSDK_XCHG_OWNER_PLAN_ONLY
+        self._plan_event.record(self._plan_stream)
+        self._owner_planned = True
+
+    def backward(self, grad_output: torch.Tensor, update_events=None, plan_ahead: bool = False) -> None:
+        """All backward steps of this rank with the fences between them (every rank calls it).  ``plan_ahead``: one
+        more fence right away (the ids of all ranks are in the inboxes) and the owner phase's index work overlaps the
+        local phase."""
+        if plan_ahead:
+            self.fence()
+            self.plan_owner_ahead()
         self.backward_local(grad_output)
         self.fence()
         self.backward_owner(update_events)

@@ -49,13 +49,16 @@ def _batches(rng, rows, world, B, max_len, hot=7, one_hot=False):
     return out
 
 
-def _run_and_compare(ranks, orc, batches, grads, B, mode, steps=2):
+def _run_and_compare(ranks, orc, batches, grads, B, mode, steps=2, plan_ahead=False):
     world = len(ranks)
     dev_b = [(torch.from_numpy(i).to(DEV), torch.from_numpy(o).to(DEV)) for i, o in batches]
     dev_g = [torch.from_numpy(g).to(DEV) for g in grads]
     for _ in range(steps):
         exp_out = orc.step(batches, grads, B, mode)
         outs = [ranks[q].forward(*dev_b[q]) for q in range(world)]  # phase by phase, all ranks: the stream orders them
+        if plan_ahead:  # every rank's ids are in the inboxes: the owners' index work goes to their side streams
+            for q in range(world):
+                ranks[q].plan_owner_ahead()
         for q in range(world):
             ranks[q].backward_local(dev_g[q])
         for q in range(world):
@@ -130,6 +133,21 @@ def test_exchange_one_id_per_bag_promise_is_checked():
     offs = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)).to(DEV)
     with pytest.raises(RuntimeError):
         ranks[0].forward(idx, offs)
+
+
+@pytest.mark.parametrize("partition", ["row", "table"])
+def test_exchange_owner_plan_on_side_stream_bit_exact(partition):
+    """The owner phase split in two: its index work on a side stream while the local phase runs, the row update after
+    the gradient sums have arrived.  Same bits."""
+    rng = np.random.default_rng(31)
+    F, D, B, world = len(ROWS), 32, 40, 4
+    owner = [f % world for f in range(F)] if partition == "table" else None
+    ranks = _make_ranks(ROWS, D, world, partition, owner, B, F * B * 3, 2, 0, inbox_cap=F * B * 3)
+    orc = port.ShardedDedupOracle(ROWS, D, world, partition, owner, optimizer=2, lr=0.05)
+    _load(ranks, orc, [rng.uniform(-0.1, 0.1, (r, D)).astype(np.float32) for r in ROWS])
+    batches = _batches(rng, ROWS, world, B, 3)
+    grads = [rng.standard_normal((B, F * D)).astype(np.float32) for _ in batches]
+    _run_and_compare(ranks, orc, batches, grads, B, 0, steps=3, plan_ahead=True)
 
 
 def test_exchange_hot_rows_long_runs_and_wide_rows():

@@ -68,7 +68,7 @@ def _worker(rank, world, port, errors, scheme):
         for _ in range(2):
             exp = orc.step(batches, grads, B_LOCAL, 0)
             out = bag.forward(idx_t, offs_t)
-            bag.backward(g_t)  # local sums -> fence -> owner update -> fence
+            bag.backward(g_t, plan_ahead=(scheme == "row"))  # [fence, owner plan ahead ->] local sums -> fence -> owner update -> fence
             np.testing.assert_array_equal(out.cpu().numpy(), exp[rank])
         bag.raise_if_error()
         n = bag.weights_dev.numel()
