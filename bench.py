@@ -430,9 +430,12 @@ def run_ours(args):
             "roofline": {"kernel": "update_kernel<Adam>", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                          "bytes_per_launch": upd_bytes, "ms_per_launch": upd_ms_avg,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one update_kernel launch of THIS workload
-                         # (full size, 1 GPU), from the ncu capture summarised in profiles/dram_traffic_configs1_1gpu.md
-                         "traffic": UPDATE_KERNEL_DRAM_BYTES if (world == 1 and args.profile_tables == 0) else None},
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one update_kernel launch of this workload
+                         # (full size, 1 GPU) from a recorded ncu capture; traffic_source says where it comes from
+                         "traffic": UPDATE_KERNEL_DRAM_BYTES if (world == 1 and args.profile_tables == 0) else None,
+                         "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, captured on an "
+                                            "earlier build of this kernel at the same workload; not re-measured by this run")
+                         if (world == 1 and args.profile_tables == 0) else None},
             "e2e": None if args.profile_tables > 0 else
                    {"value": ids_per_step / (e2e_ms_step * 1e-3), "unit": "ids/s", "ms_per_step": e2e_ms_step,
                     "host_enqueue_ms_per_step": e2e_issue_ms, "h2d_bytes_per_step": int(h2d_bytes),
