@@ -492,7 +492,8 @@ def exchange_parity_check(world, rank, dev):
     idx, offs = (torch.from_numpy(a).to(dev) for a in batches[rank])
     g = torch.from_numpy(grads[rank]).to(dev)
     torch.cuda.synchronize()
-    dist.barrier()
+    if world > 1:
+        dist.barrier()
     ok = True
     for _ in range(2):
         exp = orc.step(batches, grads, B, 0)
@@ -508,10 +509,11 @@ def exchange_parity_check(world, rank, dev):
     except RuntimeError:
         ok = False
     flag = torch.tensor([1.0 if ok else 0.0], device=dev)
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    dist.barrier()
-    bag.close()
-    dist.barrier()
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        dist.barrier()
+        bag.close()
+        dist.barrier()
     return "bit-exact" if flag.item() == 1.0 else "MISMATCH against the oracle of the sharded lookup"
 
 
@@ -526,15 +528,21 @@ def run_dedup_multi(args):
     from recsdk_b200.synthetic import zipf_ids
     from recsdk_b200.tbe import EmbOptimType
 
-    world = int(os.environ["WORLD_SIZE"])
-    rank = int(os.environ["RANK"])
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", device_id=dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     parity = exchange_parity_check(world, rank, dev)
 
     rows_all = seeded_rows()
+    if world == 1:
+        # one rank (asked for with --exchange dedup): the exchange kernels with local buffers as "peers"; rows capped
+        # as in the default single-GPU run, or to the reduced case for profiler captures
+        cap = args.profile_row_cap if args.profile_tables > 0 else ROW_CAP_1GPU
+        rows_all = [min(r, cap) for r in rows_all]
     F = len(rows_all)
     owner = greedy_table_placement(rows_all, [DIM] * F, world)
     bag = TableWiseDedupEmbeddingBag(rows_all, DIM, owner, world, rank, batch_size=BATCH, optimizer=EmbOptimType.ADAM,
@@ -548,8 +556,14 @@ def run_dedup_multi(args):
 
     def barrier():
         torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def allreduce_max(t):
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t
 
     def measure(B):
         """One scaling mode: B samples per rank.  Returns a dict of timings."""
@@ -644,10 +658,8 @@ def run_dedup_multi(args):
         issue_ms = (time.perf_counter() - t_issue) * 1e3 / args.steps
         e1.record()
         barrier()
-        tt = torch.tensor([ms_total, e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        cc = torch.tensor([counters[0] - counters[4]], device=dev, dtype=torch.float64)  # distinct rows that crossed
-        dist.all_reduce(cc, op=dist.ReduceOp.MAX)
+        tt = allreduce_max(torch.tensor([ms_total, e0.elapsed_time(e1)], device=dev, dtype=torch.float64))
+        cc = allreduce_max(torch.tensor([counters[0] - counters[4]], device=dev, dtype=torch.float64))  # rows that crossed
         return dict(ms_step=tt[0].item() / args.steps, e2e_ms_step=tt[1].item() / args.steps, phases=phases,
                     upd_ms=upd_ms, counters=counters, issue_ms=issue_ms, h2d=int(host[0].numel() * 4),
                     remote_rows_max=int(cc.item()), B=B)
@@ -655,9 +667,11 @@ def run_dedup_multi(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    torch.cuda.cudart().cudaProfilerStart()
     weak = measure(BATCH)
+    torch.cuda.cudart().cudaProfilerStop()
     clocks = sampler.stop() if rank == 0 else None
-    strong = measure(BATCH // world)  # the config as written: a global batch of 65536 split over the ranks
+    strong = measure(BATCH // world) if world > 1 else weak  # the config as written: a global batch of 65536 split over the ranks
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
@@ -698,7 +712,8 @@ def run_dedup_multi(args):
             "config": {
                 "workload": "configs[1]: 26 tables dim 128 fp32, batch 65536 per GPU one-hot Zipf(1.1), sparse Adam, "
                             "table-wise sharding",
-                "tables_this_rank": owner.count(rank), "rows_this_rank": bag.local_rows, "row_cap": None,
+                "tables_this_rank": owner.count(rank), "rows_this_rank": bag.local_rows,
+                "row_cap": None if world > 1 else max(rows_all),
                 "table_state_gb_this_rank": round(state_bytes / 1e9, 1), "ids_per_step": ids_per_step,
                 "distinct_rows_requested_rank0": U_req, "ids_received_as_owner_rank0": n_recv,
                 "distinct_rows_updated_rank0": U_own,
@@ -732,10 +747,11 @@ def run_dedup_multi(args):
             "clocks": clocks,
         }
         emit(line)
-    dist.barrier()
-    bag.close()
-    dist.barrier()
-    dist.destroy_process_group()
+    if world > 1:
+        dist.barrier()
+        bag.close()
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 
@@ -1460,6 +1476,7 @@ def main():
                     help="which BASELINE config: c2 (default, the headline: 26-table DLRM step), c1 (one small table, "
                          "Adagrad), c3 (multi-hot, Adagrad), c4 (dynamic hash-keyed table), c5 (row-wise sharded large table)")
     args = ap.parse_args()
+    explicit_dedup = args.exchange == "dedup"  # at N = 1: run the exchange kernels on one rank instead of the fused path
     if args.exchange == "auto":
         args.exchange = "dedup"
     if args.workload == "ops":
@@ -1475,7 +1492,7 @@ def main():
             run_c4(args)
         elif args.config == "c5":
             run_c5(args)
-        elif int(os.environ.get("WORLD_SIZE", "1")) > 1 and args.exchange == "dedup":
+        elif args.exchange == "dedup" and (int(os.environ.get("WORLD_SIZE", "1")) > 1 or explicit_dedup):
             run_dedup_multi(args)
         else:
             run_ours(args)

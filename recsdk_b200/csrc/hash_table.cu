@@ -48,6 +48,31 @@ __device__ __forceinline__ int64_t ht_lookup(const int64_t* __restrict__ table, 
     return -1;
 }
 
+// Warp-cooperative lookup: kProbeLanes consecutive lanes probe ONE key.  Per round they read kProbeLanes consecutive
+// entries of the chain (for 16-byte entries: one 128-byte line when the chain starts on a line boundary, two
+// otherwise) and vote: the first lane whose entry holds the key wins unless an EMPTY entry comes before it in probe
+// order (then the key is absent).  All lanes of the group must call with the same key; every lane gets the result.
+// `gmask` is the ballot mask of the group, `gl` the lane's number inside it.
+constexpr int kProbeLanes = 8;
+template <int STRIDE>
+__device__ __forceinline__ int64_t ht_lookup_coop(const int64_t* __restrict__ table, int64_t cap, int64_t key, int gl,
+                                                  unsigned gmask, int gshift)
+{
+    const uint64_t mask = static_cast<uint64_t>(cap) - 1;
+    const uint64_t e0 = mix64(static_cast<uint64_t>(key)) & mask;
+    for (int64_t probes = 0; probes < cap; probes += kProbeLanes) {
+        const uint64_t e = (e0 + static_cast<uint64_t>(probes) + static_cast<uint64_t>(gl)) & mask;
+        const int64_t k = table[e * STRIDE];
+        const unsigned hit = (__ballot_sync(gmask, k == key) & gmask) >> gshift;
+        const unsigned emp = (__ballot_sync(gmask, k == kEmpty) & gmask) >> gshift;
+        const int first_hit = hit ? __ffs(hit) - 1 : kProbeLanes;
+        const int first_emp = emp ? __ffs(emp) - 1 : kProbeLanes;
+        if (first_hit < first_emp) return static_cast<int64_t>((e0 + static_cast<uint64_t>(probes) + first_hit) & mask);
+        if (emp) return -1;
+    }
+    return -1;
+}
+
 // Returns the entry that holds `key` after the call (inserting it into the
 // first free entry of its probe chain when absent), or -1 when no entry is free.
 // Must not run concurrently with erases.
@@ -129,27 +154,38 @@ static __global__ void __launch_bounds__(256) phase_lookup_kernel(const int64_t*
                                                                   const int64_t* __restrict__ counters,
                                                                   int64_t* __restrict__ status)
 {
+    // kProbeLanes lanes per key: the group probes its key together (ballots), lane 0 of the group writes the results
     const int64_t now = MODE == 1 ? counters[1] : 0;
-    RECSDK_GRID_STRIDE(i, n)
-    {
+    const int gl = threadIdx.x & (kProbeLanes - 1);
+    const int gshift = (threadIdx.x & 31) & ~(kProbeLanes - 1);
+    const unsigned gmask = ((1u << kProbeLanes) - 1u) << gshift;
+    const int64_t groups_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) / kProbeLanes;
+    // group-uniform trip count: the ballots inside need every lane of the group
+    for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / kProbeLanes; i < n; i += groups_total) {
         const int64_t key = keys[i];
         int m = 0;
         int64_t e = -1;
         if (key < 0) {
-            out_slots[i] = 0;
-            if (MODE == 0 || key != -1) set_status(status, RECSDK_ERR_NEGATIVE_KEY, key, i);
+            if (gl == 0) {
+                out_slots[i] = 0;
+                if (MODE == 0 || key != -1) set_status(status, RECSDK_ERR_NEGATIVE_KEY, key, i);
+            }
         } else {
-            e = ht_lookup<2>(table, cap, key);
+            e = ht_lookup_coop<2>(table, cap, key, gl, gmask, gshift);
             if (e >= 0) {
-                const int64_t slot = table[e * 2 + 1];
-                out_slots[i] = slot;
-                if (MODE == 1) slot_version[slot] = now;
+                if (gl == 0) {
+                    const int64_t slot = table[e * 2 + 1];
+                    out_slots[i] = slot;
+                    if (MODE == 1) slot_version[slot] = now;
+                }
             } else {
                 m = 1;
             }
         }
-        ent[i] = e;
-        miss[i] = m;
+        if (gl == 0) {
+            ent[i] = e;
+            miss[i] = m;
+        }
     }
 }
 
@@ -321,8 +357,8 @@ static int mapper_map(const recsdk_mapper_t* m, const int64_t* ids, int64_t n, i
                       int64_t* status, const MapperWs& ws, cudaStream_t st)
 {
     const int grid = grid_for(n, 256);
-    phase_lookup_kernel<0><<<grid, 256, 0, st>>>(m->table, m->hash_capacity, ids, n, hash_indices, ws.ent, ws.miss,
-                                                 nullptr, m->counters, status);
+    phase_lookup_kernel<0><<<grid_for(n, 256 / kProbeLanes), 256, 0, st>>>(m->table, m->hash_capacity, ids, n, hash_indices,
+                                                                           ws.ent, ws.miss, nullptr, m->counters, status);
     phase_claim_kernel<<<grid, 256, 0, st>>>(m->table, m->hash_capacity, ids, n, ws.ent, ws.miss, status);
     phase_first_kernel<<<grid, 256, 0, st>>>(m->table, n, ws.ent, ws.miss, ws.first);
     device_scan<false>(ws.first, ws.rank, n, ws.scan_scratch, ws.tmp, st);
@@ -954,8 +990,9 @@ extern "C" int recsdk_swap_compute(const recsdk_swap_t* s, const int64_t* keys, 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = grid_for(n > 0 ? n : 1, 256);
     if (n > 0) {
-        phase_lookup_kernel<1><<<grid, 256, 0, st>>>(s->table, s->hash_capacity, keys, n, batch_offs, ws.ent, ws.miss,
-                                                     s->slot_version, s->counters, dev_status);
+        phase_lookup_kernel<1><<<grid_for(n, 256 / kProbeLanes), 256, 0, st>>>(s->table, s->hash_capacity, keys, n, batch_offs,
+                                                                               ws.ent, ws.miss, s->slot_version, s->counters,
+                                                                               dev_status);
         phase_claim_kernel<<<grid, 256, 0, st>>>(s->table, s->hash_capacity, keys, n, ws.ent, ws.miss, dev_status);
         phase_first_kernel<<<grid, 256, 0, st>>>(s->table, n, ws.ent, ws.miss, ws.first);
     }
