@@ -575,7 +575,10 @@ def run_dedup_multi(args):
         out = torch.empty((B, F * DIM), device=dev, dtype=torch.float32)
         ev_pairs, marks_all = [], []
 
-        def step(i, timed=False, ids=None):
+        def step(i, timed=False, ids=None, next_ids=None):
+            """One step on `ids` (default: the resident batch i).  `next_ids`: a callable that returns the ids tensor
+            of the following step, or None; with --fwd-plan ahead its sort-dedup is enqueued on the side stream as
+            soon as this step's local backward phase no longer needs the scratch."""
             marks = []
 
             def mark():
@@ -598,6 +601,8 @@ def run_dedup_multi(args):
                 bag.fence()  # the ids of every rank are in the owners' inboxes
                 bag.plan_owner_ahead()  # the owner phase's index work runs beside the local phase, on a side stream
             bag.backward_local(grad)
+            if args.fwd_plan == "ahead" and next_ids is not None:
+                bag.plan_forward_ahead(next_ids(), offsets)  # beside the fences and the owner phase
             mark()
             bag.fence()
             mark()
@@ -606,13 +611,18 @@ def run_dedup_multi(args):
             bag.fence()
             mark()
 
+        total = args.warmup + args.steps
+
+        def resident_next(i):
+            return (lambda: batches[(i + 1) % n_batches]) if i + 1 < total else None
+
         for i in range(args.warmup):
-            step(i)
+            step(i, next_ids=resident_next(i))
         barrier()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         for i in range(args.steps):
-            step(args.warmup + i, timed=True)
+            step(args.warmup + i, timed=True, next_ids=resident_next(args.warmup + i))
         t1.record()
         barrier()
         ms_total = t0.elapsed_time(t1)
@@ -641,12 +651,25 @@ def run_dedup_multi(args):
             for e in consumed:
                 e.record(main_stream)
             prefetch(0)
+            main_stream.wait_event(copied[0])
+            cur_ids = d_bufs[0].long()
+            consumed[0].record(main_stream)
             for i in range(n):
                 if i + 1 < n:
                     prefetch(i + 1)
-                main_stream.wait_event(copied[i % 2])
-                step(i, ids=d_bufs[i % 2].long())
-                consumed[i % 2].record(main_stream)
+                nxt = [None]
+
+                def widen_next(j=i + 1):
+                    # the next batch's ids are on the device (double-buffered copy): widen them now so that their
+                    # sort-dedup can be planned beside this step's owner phase
+                    main_stream.wait_event(copied[j % 2])
+                    nxt[0] = d_bufs[j % 2].long()
+                    consumed[j % 2].record(main_stream)
+                    return nxt[0]
+
+                step(i, ids=cur_ids, next_ids=widen_next if i + 1 < n else None)
+                if i + 1 < n:
+                    cur_ids = nxt[0] if nxt[0] is not None else widen_next()
                 result_host.copy_(out.reshape(-1)[:4096], non_blocking=True)
 
         run_e2e(max(args.warmup, 3))
@@ -1467,6 +1490,9 @@ def main():
                          "rows they need from the table owners and pool locally.  Kept as baselines: pooled rows / "
                          "gradients through NCCL all-to-alls (nccl, the reference's scheme) or stored / loaded inside "
                          "the owners' kernels over peer mappings (fused)")
+    ap.add_argument("--fwd-plan", default="ahead", choices=["ahead", "inline"],
+                    help="N>1: ahead = the sort-dedup of the next batch's ids runs on a side stream beside the owner phase "
+                         "and the fences of the current step (it touches no table); inline = inside the forward")
     ap.add_argument("--owner-plan", default="ahead", choices=["ahead", "inline"],
                     help="N>1: where the owner phase of the exchange makes its plan (sort of the received ids, runs, "
                          "records): ahead = on a side stream beside the local backward phase, after one more fence; "

@@ -530,9 +530,16 @@ typedef struct {
     int64_t* dev_status; /* optional */
 } recsdk_xchg_t;
 RECSDK_API size_t recsdk_xchg_workspace_bytes(int64_t max_ids, int64_t inbox_cap, int32_t world, int32_t D, int64_t F);
-/* indices [N], offsets [F*B+1] feature-major, out [B, F*D] (NONE: [N, D]).  pooling_mode RECSDK_POOL_*. */
+/* indices [N], offsets [F*B+1] feature-major, out [B, F*D] (NONE: [N, D]).  pooling_mode RECSDK_POOL_*.
+ * flags 0: the whole forward.  PLAN_ONLY / FETCH_ONLY split it: the plan (sort-dedup of this rank's ids) touches only
+ * the ids and this rank's scratch, so the plan of step k+1 can run on a second stream beside the owner phase of step k
+ * and BEFORE the fence that makes the tables final, once this rank's recsdk_xchg_backward_local of step k is done with
+ * the scratch; the fetch call (same arguments; counts and ids to the owners' inboxes, rows from the owners' tables,
+ * output) follows that fence and an event wait on the plan.  `out` may be NULL in the plan call. */
+#define RECSDK_XCHG_FWD_PLAN_ONLY 1
+#define RECSDK_XCHG_FWD_FETCH_ONLY 2
 RECSDK_API int recsdk_xchg_forward(const recsdk_xchg_t* x, const int64_t* indices, const int64_t* offsets, int64_t N,
-                                   int32_t pooling_mode, float* out, void* stream);
+                                   int32_t pooling_mode, float* out, int32_t flags, void* stream);
 /* grad_output [B, F*D] (NONE: [N, D]) of the batch of the preceding recsdk_xchg_forward (same offsets). */
 RECSDK_API int recsdk_xchg_backward_local(const recsdk_xchg_t* x, const float* grad_output, const int64_t* offsets,
                                           int64_t N, int32_t pooling_mode, int32_t gradient_clipping,

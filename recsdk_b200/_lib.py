@@ -128,7 +128,7 @@ SIGNATURES = {
     "recsdk_peer_release": (C.c_int, [vp, C.c_int64]),
     "recsdk_peer_copy": (C.c_int, [vp, vp, C.c_size_t, vp]),
     "recsdk_xchg_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int64]),
-    "recsdk_xchg_forward": (C.c_int, [C.POINTER(XchgT), vp, vp, C.c_int64, C.c_int32, vp, vp]),
+    "recsdk_xchg_forward": (C.c_int, [C.POINTER(XchgT), vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp]),
     "recsdk_xchg_backward_local": (C.c_int, [C.POINTER(XchgT), vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_float, vp]),
     "recsdk_xchg_backward_owner": (C.c_int, [C.POINTER(XchgT), vp, vp, vp, C.c_int32, C.c_float, C.c_float, C.c_float,
                                              C.c_float, C.c_int64, vp, vp, C.c_int32, vp]),

@@ -585,27 +585,35 @@ static BwdParams xchg_local_params(const recsdk_xchg_t* x, const XchgWorkspace& 
 
 template <typename KeyT>
 static int xchg_forward_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, const int64_t* indices,
-                             const int64_t* offsets, int64_t N, int32_t mode, float* out, cudaStream_t st)
+                             const int64_t* offsets, int64_t N, int32_t mode, float* out, int32_t flags, cudaStream_t st)
 {
     const XchgParams q = xchg_params(x, N, mode);
-    KeyT* ka = static_cast<KeyT*>(ws.keys_a);
-    KeyT* kb = static_cast<KeyT*>(ws.keys_b);
-    cudaMemsetAsync(ws.lc, 0, 8 * sizeof(int64_t), st);
-    const RadixFusedPlan plan = radix_fused_begin(N, x->key_bits, ws.sort_scratch, st);
-    if (mode == RECSDK_POOL_NONE)
-        xchg_expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(q, indices, offsets, ka, ws.vals_a, plan.first,
-                                                                         ws.zeros_F, ws.dofs);
-    else
-        xchg_expand_pooled_kernel<KeyT><<<grid_for(x->F * x->B, 8 * 32), 256, 0, st>>>(
-            q, indices, offsets, ka, ws.vals_a, ws.tag_of_pos, plan.first, ws.zeros_F, ws.dofs);
-    const int which = radix_sort_pairs_fused<KeyT>(plan, ka, ws.vals_a, kb, ws.vals_b, N, ws.sort_scratch, st);
-    const KeyT* keys = which ? kb : ka;
-    const uint32_t* pos_sorted = which ? ws.vals_b : ws.vals_a;
-    device_scan_fn<true>(HeadFlagIn<KeyT>{keys},
-                         XchgRunOut<KeyT>{keys, pos_sorted, mode == RECSDK_POOL_NONE ? nullptr : ws.tag_of_pos,
-                                          ws.run_start, ws.uniq, ws.inverse, ws.tags_sorted, ws.lc,
-                                          (q.one_hot && mode != RECSDK_POOL_NONE) ? x->B : 0, q.bshift},
-                         N, ws.scan_scratch, nullptr, st);
+    if ((flags & RECSDK_XCHG_FWD_FETCH_ONLY) == 0) {
+        // the plan: touches this rank's ids and scratch only -- no table, no inbox -- so it may run before the fence
+        // that makes the tables final, beside the owner phase of the previous step
+        KeyT* ka = static_cast<KeyT*>(ws.keys_a);
+        KeyT* kb = static_cast<KeyT*>(ws.keys_b);
+        cudaMemsetAsync(ws.lc, 0, 8 * sizeof(int64_t), st);
+        const RadixFusedPlan plan = radix_fused_begin(N, x->key_bits, ws.sort_scratch, st);
+        if (mode == RECSDK_POOL_NONE)
+            xchg_expand_nobag_kernel<KeyT><<<grid_for(N, 256), 256, 0, st>>>(q, indices, offsets, ka, ws.vals_a, plan.first,
+                                                                             ws.zeros_F, ws.dofs);
+        else
+            xchg_expand_pooled_kernel<KeyT><<<grid_for(x->F * x->B, 8 * 32), 256, 0, st>>>(
+                q, indices, offsets, ka, ws.vals_a, ws.tag_of_pos, plan.first, ws.zeros_F, ws.dofs);
+        const int which = radix_sort_pairs_fused<KeyT>(plan, ka, ws.vals_a, kb, ws.vals_b, N, ws.sort_scratch, st);
+        const KeyT* keys = which ? kb : ka;
+        const uint32_t* pos_sorted = which ? ws.vals_b : ws.vals_a;
+        device_scan_fn<true>(HeadFlagIn<KeyT>{keys},
+                             XchgRunOut<KeyT>{keys, pos_sorted, mode == RECSDK_POOL_NONE ? nullptr : ws.tag_of_pos,
+                                              ws.run_start, ws.uniq, ws.inverse, ws.tags_sorted, ws.lc,
+                                              (q.one_hot && mode != RECSDK_POOL_NONE) ? x->B : 0, q.bshift},
+                             N, ws.scan_scratch, nullptr, st);
+    }
+    if (flags & RECSDK_XCHG_FWD_PLAN_ONLY) {
+        RECSDK_CUDA_CHECK_LAUNCH();
+        return RECSDK_OK;
+    }
     PeerTable<const float*> tables;
     PeerTable<int64_t*> in_ids, in_counts;
     for (int r = 0; r < RECSDK_MAX_SHARDS; ++r) {
@@ -768,20 +776,22 @@ extern "C" size_t recsdk_xchg_workspace_bytes(int64_t max_ids, int64_t inbox_cap
 }
 
 extern "C" int recsdk_xchg_forward(const recsdk_xchg_t* x, const int64_t* indices, const int64_t* offsets, int64_t N,
-                                   int32_t pooling_mode, float* out, void* stream)
+                                   int32_t pooling_mode, float* out, int32_t flags, void* stream)
 {
     const int rc = xchg_validate(x, N);
     if (rc != RECSDK_OK) return rc;
     if (pooling_mode < RECSDK_POOL_SUM || pooling_mode > RECSDK_POOL_NONE) return RECSDK_ERR_INVALID_ARG;
-    if (!offsets || !out || (N > 0 && !indices)) return RECSDK_ERR_INVALID_ARG;
+    const bool plan_only = (flags & RECSDK_XCHG_FWD_PLAN_ONLY) != 0;
+    if (plan_only && (flags & RECSDK_XCHG_FWD_FETCH_ONLY)) return RECSDK_ERR_INVALID_ARG;
+    if (!offsets || (!out && !plan_only) || (N > 0 && !indices)) return RECSDK_ERR_INVALID_ARG;
     if (pooling_mode != RECSDK_POOL_NONE && xchg_bits_for(x->B - 1 > 0 ? x->B - 1 : 1) + xchg_bits_for(x->F) > 32)
         return RECSDK_ERR_TOO_LARGE;
     if ((x->flags & RECSDK_XCHG_ONE_HOT) && pooling_mode != RECSDK_POOL_NONE && N != x->F * x->B)
         return RECSDK_ERR_INVALID_ARG;  // one id per bag was promised
     const XchgWorkspace ws = carve_xchg(x->workspace, x->max_ids, x->inbox_cap, x->world, x->D, x->F);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (x->key_bits <= 32) return xchg_forward_impl<uint32_t>(x, ws, indices, offsets, N, pooling_mode, out, st);
-    return xchg_forward_impl<uint64_t>(x, ws, indices, offsets, N, pooling_mode, out, st);
+    if (x->key_bits <= 32) return xchg_forward_impl<uint32_t>(x, ws, indices, offsets, N, pooling_mode, out, flags, st);
+    return xchg_forward_impl<uint64_t>(x, ws, indices, offsets, N, pooling_mode, out, flags, st);
 }
 
 extern "C" int recsdk_xchg_backward_local(const recsdk_xchg_t* x, const float* grad_output, const int64_t* offsets,

@@ -161,6 +161,8 @@ class DedupExchange:
         self._plan_stream = None
         self._plan_event = None
         self._owner_planned = False
+        self._fwd_planned = None
+        self._fwd_plan_event = None
         if world == 1:
             connect_local([self])
 
@@ -239,10 +241,39 @@ class DedupExchange:
         shape = (N, self.dim) if mode == _lib.POOL_NONE else (self.B, self.F * self.dim)
         if out is None:
             out = torch.empty(shape, dtype=torch.float32, device=self.device)
+        flags = 0
+        if self._fwd_planned is not None:
+            if self._fwd_planned != (indices.data_ptr(), N, offsets.data_ptr()):
+                raise RuntimeError("the forward plan made ahead belongs to other indices / offsets")
+            torch.cuda.current_stream(self.device).wait_event(self._fwd_plan_event)
+            self._fwd_planned = None
+            flags = 2  # RECSDK_XCHG_FWD_FETCH_ONLY
         check(_lib.load().recsdk_xchg_forward(C.byref(self._x), indices.data_ptr(), offsets.data_ptr(), N, mode,
-                                              out.data_ptr(), _stream()), "recsdk_xchg_forward")
+                                              out.data_ptr(), flags, _stream()), "recsdk_xchg_forward")
         self._offsets, self._N = offsets, N
         return out
+
+    def plan_forward_ahead(self, indices: torch.Tensor, offsets: torch.Tensor) -> None:
+        """The sort-dedup of the NEXT batch's ids on the side stream, ordered after what is enqueued on the current
+        stream so far (call it after backward_local of the current batch: the plan reuses that scratch).  It touches
+        no table and no inbox, so it runs beside the owner phase and the fences; the next forward(indices, offsets)
+        -- exactly these tensors -- then only waits for it and fetches."""
+        if not self._connected:
+            raise RuntimeError("connect_processes / connect_local first")
+        cur = torch.cuda.current_stream(self.device)
+        if self._plan_stream is None:
+            self._plan_stream = torch.cuda.Stream(device=self.device, priority=-1)
+            self._plan_event = torch.cuda.Event()
+        if self._fwd_plan_event is None:
+            self._fwd_plan_event = torch.cuda.Event()
+        self._plan_stream.wait_stream(cur)
+        indices.record_stream(self._plan_stream)
+        offsets.record_stream(self._plan_stream)
+        check(_lib.load().recsdk_xchg_forward(C.byref(self._x), indices.data_ptr(), offsets.data_ptr(), indices.numel(),
+                                              int(self.pooling_mode), None, 1, self._plan_stream.cuda_stream),
+              "recsdk_xchg_forward")  # RECSDK_XCHG_FWD_PLAN_ONLY
+        self._fwd_plan_event.record(self._plan_stream)
+        self._fwd_planned = (indices.data_ptr(), indices.numel(), offsets.data_ptr())
 
     def backward_local(self, grad_output: torch.Tensor) -> None:
         check(_lib.load().recsdk_xchg_backward_local(C.byref(self._x), grad_output.data_ptr(), self._offsets.data_ptr(),

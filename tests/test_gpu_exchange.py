@@ -49,11 +49,11 @@ def _batches(rng, rows, world, B, max_len, hot=7, one_hot=False):
     return out
 
 
-def _run_and_compare(ranks, orc, batches, grads, B, mode, steps=2, plan_ahead=False):
+def _run_and_compare(ranks, orc, batches, grads, B, mode, steps=2, plan_ahead=False, fwd_plan_ahead=False):
     world = len(ranks)
     dev_b = [(torch.from_numpy(i).to(DEV), torch.from_numpy(o).to(DEV)) for i, o in batches]
     dev_g = [torch.from_numpy(g).to(DEV) for g in grads]
-    for _ in range(steps):
+    for step_no in range(steps):
         exp_out = orc.step(batches, grads, B, mode)
         outs = [ranks[q].forward(*dev_b[q]) for q in range(world)]  # phase by phase, all ranks: the stream orders them
         if plan_ahead:  # every rank's ids are in the inboxes: the owners' index work goes to their side streams
@@ -61,6 +61,9 @@ def _run_and_compare(ranks, orc, batches, grads, B, mode, steps=2, plan_ahead=Fa
                 ranks[q].plan_owner_ahead()
         for q in range(world):
             ranks[q].backward_local(dev_g[q])
+        if fwd_plan_ahead and step_no + 1 < steps:  # the next step's sort-dedup, beside this step's owner phase
+            for q in range(world):
+                ranks[q].plan_forward_ahead(*dev_b[q])
         for q in range(world):
             ranks[q].backward_owner()
         for q in range(world):
@@ -148,6 +151,24 @@ def test_exchange_owner_plan_on_side_stream_bit_exact(partition):
     batches = _batches(rng, ROWS, world, B, 3)
     grads = [rng.standard_normal((B, F * D)).astype(np.float32) for _ in batches]
     _run_and_compare(ranks, orc, batches, grads, B, 0, steps=3, plan_ahead=True)
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_exchange_forward_plan_ahead_bit_exact(mode):
+    """The forward split in two: the sort-dedup of the next step's ids on a side stream while the owner phase of the
+    current step runs (it touches no table), the fetch after it.  Same bits; a plan made for other tensors is refused."""
+    rng = np.random.default_rng(33)
+    F, D, B, world = len(ROWS), 32, 40, 4
+    ranks = _make_ranks(ROWS, D, world, "row", None, B, F * B * 3, 2, mode, inbox_cap=F * B * 3)
+    orc = port.ShardedDedupOracle(ROWS, D, world, "row", optimizer=2, lr=0.05)
+    _load(ranks, orc, [rng.uniform(-0.1, 0.1, (r, D)).astype(np.float32) for r in ROWS])
+    batches = _batches(rng, ROWS, world, B, 3)
+    grads = [rng.standard_normal((b[0].size, D) if mode == 2 else (B, F * D)).astype(np.float32) for b in batches]
+    _run_and_compare(ranks, orc, batches, grads, B, mode, steps=3, plan_ahead=True, fwd_plan_ahead=True)
+    idx, offs = (torch.from_numpy(a).to(DEV) for a in batches[0])
+    ranks[0].plan_forward_ahead(idx, offs)
+    with pytest.raises(RuntimeError, match="other indices"):
+        ranks[0].forward(idx.clone(), offs)
 
 
 def test_exchange_hot_rows_long_runs_and_wide_rows():
