@@ -136,7 +136,14 @@ __global__ void __launch_bounds__(256) expand_pooled_kernel(BwdParams p, KeyT* _
         const int64_t bag = bag0 + lane;
         const int64_t start = bag < num_bags ? p.offs[bag] : INT64_MAX;  // lane l: first position of bag0+l
         const int64_t last_bag = (bag0 + 32 < num_bags) ? bag0 + 32 : num_bags;
-        const int64_t p0 = p.offs[bag0], p1 = p.offs[last_bag];
+        int64_t p0 = p.offs[bag0], p1 = p.offs[last_bag];
+        if (p0 < 0 || p1 > p.N || p0 > p1) {
+            // offsets that do not describe N positions (e.g. a buffer rewritten under a plan made ahead): never write
+            // past the workspace
+            set_status(p.status, RECSDK_ERR_INDEX_RANGE, p1, p.N);
+            p0 = p0 < 0 ? 0 : (p0 > p.N ? p.N : p0);
+            p1 = p1 > p.N ? p.N : (p1 < p0 ? p0 : p1);
+        }
         const uint32_t f_l = bag < num_bags ? static_cast<uint32_t>(bag / p.B) : 0u;
         const uint32_t b_l = bag < num_bags ? static_cast<uint32_t>(bag - static_cast<int64_t>(f_l) * p.B) : 0u;
         for (int64_t base = p0; base < p1; base += 32) {

@@ -64,3 +64,33 @@ def test_oracle_placement_round_trip():
             orc.load_table(f, w)
         for f, w in enumerate(ws):
             np.testing.assert_array_equal(orc.table(f), w)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_exchange_layouts_agree_with_the_oracle_placement(world):
+    """Host-side layout of the exchange (linear row numbering, per-rank bases) against the oracle's own placement:
+    row `idx` of table f must land on the same rank at the same local row in both."""
+    from recsdk_b200.exchange import row_wise_layout, table_wise_layout
+
+    rng = np.random.default_rng(world)
+    rows = [int(r) for r in rng.integers(1, 2000, size=7)]
+    owner = [int(o) for o in rng.integers(0, world, size=7)]
+    orc_t = port.ShardedDedupOracle(rows, 4, world, "table", owner=owner)
+    part_base, rank_base = table_wise_layout(rows, owner, world)
+    assert rank_base[0] == 0 and rank_base[world] == sum(rows)
+    for f, r in enumerate(rows):
+        idx = rng.integers(0, r, size=20)
+        own, lrow = orc_t.place(f, idx)
+        lin = part_base[f] + idx
+        np.testing.assert_array_equal(np.searchsorted(np.array(rank_base[1:]), lin, side="right"), own)
+        np.testing.assert_array_equal(lin - np.array(rank_base)[own], lrow)
+    orc_r = port.ShardedDedupOracle(rows, 4, world, "row")
+    part_base, rank_base, local = row_wise_layout(rows, world)
+    assert rank_base[world] == sum(sum(x) for x in local)
+    for f, r in enumerate(rows):
+        idx = rng.integers(0, r, size=20)
+        own, lrow = orc_r.place(f, idx)
+        np.testing.assert_array_equal(idx % world, own)
+        lin = np.array([part_base[int(o) * len(rows) + f] for o in own]) + idx // world
+        np.testing.assert_array_equal(lin - np.array(rank_base)[own], lrow)
+        assert (lin < np.array(rank_base)[own + 1]).all()
