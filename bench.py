@@ -565,8 +565,9 @@ def run_dedup_multi(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t
 
-    def measure(B):
-        """One scaling mode: B samples per rank.  Returns a dict of timings."""
+    def measure(B, profile=False):
+        """One scaling mode: B samples per rank.  Returns a dict of timings.  `profile`: a profiler started with
+        --profile-from-start off sees the resident loop only (not the generation of the batches)."""
         bag.set_batch_size(B)
         batches = [torch.stack([zipf_ids(gen, B, rows_all[t], ALPHA, dev) for t in range(F)]).view(-1)
                    for _ in range(n_batches)]
@@ -616,6 +617,9 @@ def run_dedup_multi(args):
         def resident_next(i):
             return (lambda: batches[(i + 1) % n_batches]) if i + 1 < total else None
 
+        if profile:
+            barrier()
+            torch.cuda.cudart().cudaProfilerStart()
         for i in range(args.warmup):
             step(i, next_ids=resident_next(i))
         barrier()
@@ -625,6 +629,8 @@ def run_dedup_multi(args):
             step(args.warmup + i, timed=True, next_ids=resident_next(args.warmup + i))
         t1.record()
         barrier()
+        if profile:
+            torch.cuda.cudart().cudaProfilerStop()
         ms_total = t0.elapsed_time(t1)
         names = ("forward", "backward_local", "fence", "backward_owner", "fence2")
         phases = {n: sum(m[k].elapsed_time(m[k + 1]) for m in marks_all) / len(marks_all) for k, n in enumerate(names)}
@@ -690,9 +696,7 @@ def run_dedup_multi(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    torch.cuda.cudart().cudaProfilerStart()
-    weak = measure(BATCH)
-    torch.cuda.cudart().cudaProfilerStop()
+    weak = measure(BATCH, profile=True)
     clocks = sampler.stop() if rank == 0 else None
     strong = measure(BATCH // world) if world > 1 else weak  # the config as written: a global batch of 65536 split over the ranks
 

@@ -811,8 +811,18 @@ extern "C" int recsdk_xchg_backward_local(const recsdk_xchg_t* x, const float* g
 #define CALL_PARTIAL(G, K) xchg_launch_partial<G, K>(p, N, st)
     RECSDK_XCHG_DISPATCH_GK(vec_per_row, CALL_PARTIAL);
 #undef CALL_PARTIAL
+    // The store variant is bound by the bytes a warp keeps in flight (most runs hold one position: record -> one
+    // gradient row -> one store), and it is light on registers: for rows of 64 and 128 floats half as many lanes per
+    // row with two vectors each put twice as many rows in flight per warp (local phase of the benchmark step 0.35 ->
+    // 0.30 ms).  The optimizer variants hold w / m / v as well and lose more occupancy than they gain.
 #define CALL_UPDATE(G, K) xchg_launch_update<G, K>(p, ws.meta, N, kOptStore, st)
-    RECSDK_XCHG_DISPATCH_GK(vec_per_row, CALL_UPDATE);
+    if (vec_per_row == 32) {
+        CALL_UPDATE(16, 2);
+    } else if (vec_per_row == 16) {
+        CALL_UPDATE(8, 2);
+    } else {
+        RECSDK_XCHG_DISPATCH_GK(vec_per_row, CALL_UPDATE);
+    }
 #undef CALL_UPDATE
     RECSDK_CUDA_CHECK_LAUNCH();
     return RECSDK_OK;
