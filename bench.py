@@ -544,7 +544,15 @@ def run_dedup_multi(args):
         cap = args.profile_row_cap if args.profile_tables > 0 else ROW_CAP_1GPU
         rows_all = [min(r, cap) for r in rows_all]
     F = len(rows_all)
-    owner = greedy_table_placement(rows_all, [DIM] * F, world)
+    if args.placement == "load" and world > 1:
+        # what a table costs its owner per step is the distinct rows the ranks ask for, not its share of the ids:
+        # count them on one profile batch (same seed on every rank, not one of the timed batches) and balance those
+        pg = torch.Generator(device=dev)
+        pg.manual_seed(SEED + 4242)
+        loads = [int(torch.unique(zipf_ids(pg, BATCH, rows_all[t], ALPHA, dev)).numel()) for t in range(F)]
+        owner = greedy_table_placement(rows_all, [DIM] * F, world, loads=loads, bytes_cap=150 * 10**9)
+    else:
+        owner = greedy_table_placement(rows_all, [DIM] * F, world)
     bag = TableWiseDedupEmbeddingBag(rows_all, DIM, owner, world, rank, batch_size=BATCH, optimizer=EmbOptimType.ADAM,
                                      device=dev, learning_rate=LR, eps=EPS, beta1=BETA1, beta2=BETA2,
                                      weights_init=(-0.01, 0.01), seed=SEED + rank, one_hot=True)
@@ -637,6 +645,19 @@ def run_dedup_multi(args):
         upd_ms = sum(a.elapsed_time(b) for a, b in ev_pairs) / len(ev_pairs)
         counters = bag.counters()
         bag.raise_if_error()
+        # what one fence costs when nobody is late: 20 back to back on an idle stream
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(20):
+            bag.fence()
+        f1.record()
+        barrier()
+        fence_idle_ms = f0.elapsed_time(f1) / 20
+        phases_all = [phases]
+        if world > 1:
+            phases_all = [None] * world
+            dist.all_gather_object(phases_all, phases)
 
         # end to end: ids of every step cross PCIe from pinned host memory (int32, widened on the device) on a copy
         # stream, double-buffered; 16 KB of the result are read back
@@ -690,6 +711,7 @@ def run_dedup_multi(args):
         tt = allreduce_max(torch.tensor([ms_total, e0.elapsed_time(e1)], device=dev, dtype=torch.float64))
         cc = allreduce_max(torch.tensor([counters[0] - counters[4]], device=dev, dtype=torch.float64))  # rows that crossed
         return dict(ms_step=tt[0].item() / args.steps, e2e_ms_step=tt[1].item() / args.steps, phases=phases,
+                    phases_all=phases_all, fence_idle_ms=fence_idle_ms,
                     upd_ms=upd_ms, counters=counters, issue_ms=issue_ms, h2d=int(host[0].numel() * 4),
                     remote_rows_max=int(cc.item()), B=B)
 
@@ -739,6 +761,7 @@ def run_dedup_multi(args):
             "config": {
                 "workload": "configs[1]: 26 tables dim 128 fp32, batch 65536 per GPU one-hot Zipf(1.1), sparse Adam, "
                             "table-wise sharding",
+                "placement": (args.placement if world > 1 else None), "tables_per_rank": [owner.count(r) for r in range(world)],
                 "tables_this_rank": owner.count(rank), "rows_this_rank": bag.local_rows,
                 "row_cap": None if world > 1 else max(rows_all),
                 "table_state_gb_this_rank": round(state_bytes / 1e9, 1), "ids_per_step": ids_per_step,
@@ -769,6 +792,9 @@ def run_dedup_multi(args):
                     "ms_per_step": weak["e2e_ms_step"], "host_enqueue_ms_per_step": weak["issue_ms"],
                     "h2d_bytes_per_step": weak["h2d"], "d2h_bytes_per_step": 4096 * 4},
             "phases_ms_rank0": weak["phases"],
+            "phases_ms_min_max_over_ranks": {k: [min(p[k] for p in weak["phases_all"]), max(p[k] for p in weak["phases_all"])]
+                                             for k in weak["phases"]},
+            "fence_ms_when_idle": weak["fence_idle_ms"],
             "strong_scaling": scal(strong, "strong: global batch 65536 split over the ranks"),
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
@@ -1497,6 +1523,9 @@ def main():
     ap.add_argument("--fwd-plan", default="ahead", choices=["ahead", "inline"],
                     help="N>1: ahead = the sort-dedup of the next batch's ids runs on a side stream beside the owner phase "
                          "and the fences of the current step (it touches no table); inline = inside the forward")
+    ap.add_argument("--placement", default="load", choices=["load", "count"],
+                    help="N>1: which rank owns which table.  load = balance the distinct rows per table of one profile "
+                         "batch (what an owner serves and updates per step); count = equal table counts, big tables apart")
     ap.add_argument("--owner-plan", default="ahead", choices=["ahead", "inline"],
                     help="N>1: where the owner phase of the exchange makes its plan (sort of the received ids, runs, "
                          "records): ahead = on a side stream beside the local backward phase, after one more fence; "

@@ -626,6 +626,9 @@ static int xchg_forward_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, co
     // the records of the local backward phase depend on the batch and on the LAYOUT of the gradient only: made here,
     // they also tell the one-id-per-bag forward which runs are chunked
     const BwdParams lp = xchg_local_params(x, ws, q, nullptr, offsets, N, mode, 0, 0.f);
+    // the records reserve chunk slots by counting up from zero: reset here, not only in the plan, so that a fetch
+    // repeated on the same plan stays inside the slot arrays
+    cudaMemsetAsync(ws.lc + 1, 0, 2 * sizeof(int64_t), st);
     xchg_local_meta_kernel<<<grid_for(N, 256), 256, 0, st>>>(lp, q, ws.seg, ws.lc, ws.meta, ws.desc, ws.chunk_row);
     const int G = group_lanes_for(x->D >> 2);
     // kRows rows per group and pass; several resident blocks per SM keep many peer loads in flight

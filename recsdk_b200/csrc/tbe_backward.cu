@@ -101,13 +101,17 @@ template <int G, int K>
 static void launch_update(const BwdParams& p, const RunMeta* meta, int64_t N, cudaStream_t st)
 {
     if (G == 32 && launch_update_staged(p, meta, st)) return;
-    const int groups_per_block = 256 / G;
-    // as many blocks as are resident at once (64 registers: 4 per SM), each striding over the rows: no second wave
-    const int grid = grid_for(N, groups_per_block, 4);
+    // blocks of 64 threads, up to 128 per SM queued (16 resident at 64 registers): small blocks retire and are replaced
+    // one by one, which measured a few percent faster on the benchmark step than one resident wave of 256-thread
+    // blocks striding over the rows (0.299 vs 0.315 ms); each group still walks several rows, so the record of its
+    // next row is fetched ahead
+    constexpr int kBlock = 64;
+    const int groups_per_block = kBlock / G;
+    const int grid = grid_for(N, groups_per_block, 128);
     switch (p.opt) {
-        case RECSDK_OPT_ADAGRAD: update_kernel<G, K, RECSDK_OPT_ADAGRAD><<<grid, 256, 0, st>>>(p, meta); break;
-        case RECSDK_OPT_ADAM: update_kernel<G, K, RECSDK_OPT_ADAM><<<grid, 256, 0, st>>>(p, meta); break;
-        default: update_kernel<G, K, RECSDK_OPT_SGD><<<grid, 256, 0, st>>>(p, meta); break;
+        case RECSDK_OPT_ADAGRAD: update_kernel<G, K, RECSDK_OPT_ADAGRAD><<<grid, kBlock, 0, st>>>(p, meta); break;
+        case RECSDK_OPT_ADAM: update_kernel<G, K, RECSDK_OPT_ADAM><<<grid, kBlock, 0, st>>>(p, meta); break;
+        default: update_kernel<G, K, RECSDK_OPT_SGD><<<grid, kBlock, 0, st>>>(p, meta); break;
     }
 }
 

@@ -22,19 +22,40 @@ import torch
 import torch.distributed as dist
 
 
-def greedy_table_placement(rows: Sequence[int], dims: Sequence[int], world: int) -> List[int]:
-    """Whole tables onto ranks.  Every table receives the same number of ids per step, so the lookup / update
-    work of a rank is proportional to its table COUNT while its memory is proportional to its table BYTES:
-    biggest table first onto the rank with the fewest tables so far, ties to the rank with the fewest bytes.
-    Counts differ by at most one and the big tables are spread out.  Deterministic on every rank."""
+def greedy_table_placement(rows: Sequence[int], dims: Sequence[int], world: int,
+                           loads: Optional[Sequence[float]] = None, bytes_cap: Optional[int] = None,
+                           bytes_per_element: int = 12) -> List[int]:
+    """Whole tables onto ranks.  Deterministic on every rank.
+
+    Without `loads`: every table receives the same number of ids per step, so the lookup / update work of a rank is
+    taken as proportional to its table COUNT while its memory is proportional to its table BYTES: biggest table
+    first onto the rank with the fewest tables so far, ties to the rank with the fewest bytes.  Counts differ by at
+    most one and the big tables are spread out.
+
+    With `loads` (one number per table, e.g. the distinct rows a profile batch touches -- what the owner of a table
+    serves to the other ranks and updates once per step): heaviest table first onto the rank with the least load so
+    far among those where the table still fits under `bytes_cap` (weights + optimizer state, `bytes_per_element`
+    bytes per element; no cap when None); a table that fits nowhere goes to the rank with the fewest bytes."""
     count = [0] * world
     load = [0] * world
     owner = [0] * len(rows)
-    for t in sorted(range(len(rows)), key=lambda i: (-rows[i] * dims[i], i)):
-        r = min(range(world), key=lambda k: (count[k], load[k], k))
+    if loads is None:
+        for t in sorted(range(len(rows)), key=lambda i: (-rows[i] * dims[i], i)):
+            r = min(range(world), key=lambda k: (count[k], load[k], k))
+            owner[t] = r
+            count[r] += 1
+            load[r] += rows[t] * dims[t]
+        return owner
+    if len(loads) != len(rows):
+        raise ValueError("loads must have one entry per table")
+    work = [0.0] * world
+    for t in sorted(range(len(rows)), key=lambda i: (-float(loads[i]), -rows[i] * dims[i], i)):
+        size = rows[t] * dims[t] * bytes_per_element
+        fits = [k for k in range(world) if bytes_cap is None or load[k] + size <= bytes_cap]
+        r = min(fits, key=lambda k: (work[k], load[k], k)) if fits else min(range(world), key=lambda k: (load[k], k))
         owner[t] = r
-        count[r] += 1
-        load[r] += rows[t] * dims[t]
+        work[r] += float(loads[t])
+        load[r] += size
     return owner
 
 

@@ -185,6 +185,44 @@ def test_exchange_hot_rows_long_runs_and_wide_rows():
     assert ranks[0].counters()[3] > 0  # some ids lived in chunked runs
 
 
+def test_exchange_fetch_repeated_on_one_plan():
+    """A fetch may be repeated on the plan it belongs to: the records of the local backward phase, which the fetch
+    writes, reserve their chunk slots from zero every time.  One id per bag, hot rows (chunked runs)."""
+    import ctypes as C
+
+    from recsdk_b200 import _lib
+    from recsdk_b200.ops import _stream, check
+
+    rng = np.random.default_rng(8)
+    rows, D, B, world = [40, 3000], 128, 1200, 2
+    ranks = _make_ranks(rows, D, world, "table", [0, 1], B, 2 * B, 2, 0, inbox_cap=2 * B, one_hot=True)
+    orc = port.ShardedDedupOracle(rows, D, world, "table", [0, 1], optimizer=2, lr=0.05)
+    _load(ranks, orc, [rng.uniform(-0.1, 0.1, (r, D)).astype(np.float32) for r in rows])
+    batches = _batches(rng, rows, world, B, 1, hot=3, one_hot=True)
+    grads = [rng.standard_normal((B, 2 * D)).astype(np.float32) for _ in batches]
+    exp_out = orc.step(batches, grads, B, 0)
+    dev_b = [(torch.from_numpy(i).to(DEV), torch.from_numpy(o).to(DEV)) for i, o in batches]
+    outs = [ranks[q].forward(*dev_b[q]) for q in range(world)]
+    for q in range(world):
+        x, (idx, offs) = ranks[q], dev_b[q]
+        again = torch.empty_like(outs[q])
+        for _ in range(4):
+            check(_lib.load().recsdk_xchg_forward(C.byref(x._x), idx.data_ptr(), offs.data_ptr(), idx.numel(), 0,
+                                                  again.data_ptr(), 2, _stream()), "recsdk_xchg_forward")
+        np.testing.assert_array_equal(again.cpu().numpy(), exp_out[q])
+        np.testing.assert_array_equal(outs[q].cpu().numpy(), exp_out[q])
+    for q in range(world):
+        ranks[q].backward_local(torch.from_numpy(grads[q]).to(DEV))
+    for q in range(world):
+        ranks[q].backward_owner()
+    for r, x in enumerate(ranks):
+        x.raise_if_error()
+        assert x.counters()[3] > 0  # chunked runs were there
+        n = x.weights_dev.numel()
+        np.testing.assert_array_equal(x.weights_dev.cpu().numpy(), orc.w[r][:n])
+        np.testing.assert_array_equal(x.momentum2_dev.cpu().numpy(), orc.m2[r][:n])
+
+
 def test_exchange_large_rowwise_twin():
     """Down-scaled twin of the large row-wise config: one table of 1e6 rows x 64, W = 8, rows placed by id % W,
     one-hot Zipf(1.05) ids, Adam; 4096 ids per rank."""

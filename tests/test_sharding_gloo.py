@@ -93,3 +93,23 @@ def test_single_rank_is_identity():
     x = torch.randn(B, sum(DIMS))
     assert torch.equal(sh.exchange_outputs(x, B), x)
     assert torch.equal(sh.exchange_gradients(x), x)
+
+
+def test_placement_by_load_balances_load_under_a_byte_cap():
+    from recsdk_b200.sharding import greedy_table_placement
+
+    rows = [4000, 10, 3000, 20, 2000, 30, 1000, 40]
+    dims = [8] * 8
+    loads = [5, 100, 5, 90, 5, 80, 5, 70]  # the small tables are the busy ones
+    by_count = greedy_table_placement(rows, dims, 2)
+    assert sorted(by_count.count(r) for r in range(2)) == [4, 4]
+    by_load = greedy_table_placement(rows, dims, 2, loads=loads)
+    work = [sum(loads[t] for t in range(8) if by_load[t] == r) for r in range(2)]
+    assert abs(work[0] - work[1]) <= 10 and by_load == greedy_table_placement(rows, dims, 2, loads=loads)
+    # a cap that only lets one of the big tables on a rank
+    cap = (4000 + 1000 + 100) * 8 * 12
+    capped = greedy_table_placement(rows, dims, 2, loads=[1] * 8, bytes_cap=cap)
+    size = [sum(rows[t] * 8 * 12 for t in range(8) if capped[t] == r) for r in range(2)]
+    assert capped[0] != capped[2] and max(size) <= (4000 + 2000 + 100) * 8 * 12
+    with pytest.raises(ValueError):
+        greedy_table_placement(rows, dims, 2, loads=[1, 2])
