@@ -1523,7 +1523,7 @@ def main():
     ap.add_argument("--fwd-plan", default="ahead", choices=["ahead", "inline"],
                     help="N>1: ahead = the sort-dedup of the next batch's ids runs on a side stream beside the owner phase "
                          "and the fences of the current step (it touches no table); inline = inside the forward")
-    ap.add_argument("--placement", default="load", choices=["load", "count"],
+    ap.add_argument("--placement", default="count", choices=["count", "load"],
                     help="N>1: which rank owns which table.  load = balance the distinct rows per table of one profile "
                          "batch (what an owner serves and updates per step); count = equal table counts, big tables apart")
     ap.add_argument("--owner-plan", default="ahead", choices=["ahead", "inline"],

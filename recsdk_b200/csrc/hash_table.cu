@@ -143,18 +143,20 @@ static __global__ void set4_kernel(int64_t* p, int64_t a, int64_t b, int64_t c, 
 static bool is_pow2(int64_t x) { return x > 0 && (x & (x - 1)) == 0; }
 
 // ============================================================================ shared phases
-// phase 1: lookup.  ent[i] = entry (hit) or -1; miss[i] = 1 for keys to insert.
+// phase 1: find or claim.  kProbeLanes lanes probe one key together (ballots).  A key that the table held before
+// this batch is a hit: out_slots[i] = its slot, miss[i] = 0.  Any other key is a miss: lane 0 of the group inserts
+// it (or finds the entry another position of this batch has just inserted -- its value is still a bid, >= kPending)
+// and bids for it with its position; ent[i] = the entry, or -1 when the table is full.
 // MODE 0: mapper (negative key is an error), MODE 1: swap (-1 = not admitted -> slot 0).
 template <int MODE>
-static __global__ void __launch_bounds__(256) phase_lookup_kernel(const int64_t* __restrict__ table, int64_t cap,
-                                                                  const int64_t* __restrict__ keys, int64_t n,
-                                                                  int64_t* __restrict__ out_slots,
-                                                                  int64_t* __restrict__ ent, int* __restrict__ miss,
-                                                                  int64_t* __restrict__ slot_version,
-                                                                  const int64_t* __restrict__ counters,
-                                                                  int64_t* __restrict__ status)
+static __global__ void __launch_bounds__(256) phase_find_or_claim_kernel(int64_t* __restrict__ table, int64_t cap,
+                                                                         const int64_t* __restrict__ keys, int64_t n,
+                                                                         int64_t* __restrict__ out_slots,
+                                                                         int64_t* __restrict__ ent, int* __restrict__ miss,
+                                                                         int64_t* __restrict__ slot_version,
+                                                                         const int64_t* __restrict__ counters,
+                                                                         int64_t* __restrict__ status)
 {
-    // kProbeLanes lanes per key: the group probes its key together (ballots), lane 0 of the group writes the results
     const int64_t now = MODE == 1 ? counters[1] : 0;
     const int gl = threadIdx.x & (kProbeLanes - 1);
     const int gshift = (threadIdx.x & 31) & ~(kProbeLanes - 1);
@@ -163,63 +165,59 @@ static __global__ void __launch_bounds__(256) phase_lookup_kernel(const int64_t*
     // group-uniform trip count: the ballots inside need every lane of the group
     for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / kProbeLanes; i < n; i += groups_total) {
         const int64_t key = keys[i];
-        int m = 0;
-        int64_t e = -1;
         if (key < 0) {
             if (gl == 0) {
                 out_slots[i] = 0;
                 if (MODE == 0 || key != -1) set_status(status, RECSDK_ERR_NEGATIVE_KEY, key, i);
+                ent[i] = -1;
+                miss[i] = 0;
             }
-        } else {
-            e = ht_lookup_coop<2>(table, cap, key, gl, gmask, gshift);
-            if (e >= 0) {
-                if (gl == 0) {
-                    const int64_t slot = table[e * 2 + 1];
-                    out_slots[i] = slot;
-                    if (MODE == 1) slot_version[slot] = now;
-                }
-            } else {
-                m = 1;
-            }
-        }
-        if (gl == 0) {
-            ent[i] = e;
-            miss[i] = m;
-        }
-    }
-}
-
-// phase 2: misses insert their key and bid with their position
-static __global__ void __launch_bounds__(256) phase_claim_kernel(int64_t* __restrict__ table, int64_t cap,
-                                                                 const int64_t* __restrict__ keys, int64_t n,
-                                                                 int64_t* __restrict__ ent, const int* __restrict__ miss,
-                                                                 int64_t* __restrict__ status)
-{
-    RECSDK_GRID_STRIDE(i, n)
-    {
-        if (!miss[i]) continue;
-        const int64_t e = ht_insert<2>(table, cap, keys[i]);
-        ent[i] = e;
-        if (e < 0) {
-            set_status(status, RECSDK_ERR_HASH_FULL, keys[i], i);
             continue;
         }
-        atomic_min_i64(table + e * 2 + 1, kPending + i);
+        int64_t e = ht_lookup_coop<2>(table, cap, key, gl, gmask, gshift);
+        if (gl != 0) continue;
+        const int64_t held = e >= 0 ? *reinterpret_cast<const volatile int64_t*>(table + e * 2 + 1) : kValFree;
+        if (held < kPending) {  // the key was there before this batch
+            out_slots[i] = held;
+            if (MODE == 1) slot_version[held] = now;
+            ent[i] = e;
+            miss[i] = 0;
+            continue;
+        }
+        if (e < 0) e = ht_insert<2>(table, cap, key);
+        if (e < 0) {
+            set_status(status, RECSDK_ERR_HASH_FULL, key, i);
+            out_slots[i] = 0;
+        } else {
+            atomic_min_i64(table + e * 2 + 1, kPending + i);
+        }
+        ent[i] = e;
+        miss[i] = 1;
     }
 }
 
-// phase 3: first[i] = 1 where position i won the bid for its key
-static __global__ void __launch_bounds__(256) phase_first_kernel(const int64_t* __restrict__ table, int64_t n,
-                                                                 const int64_t* __restrict__ ent,
-                                                                 const int* __restrict__ miss, int* __restrict__ first)
-{
-    RECSDK_GRID_STRIDE(i, n)
+// phase 2, as the input of a scan: 1 where position i won the bid for its key.  The scan's consumer may overwrite
+// the bid of a winner with its slot while other positions are still being evaluated: a loser's comparison fails
+// against the slot as it failed against the winner's bid.
+struct WonBidIn {
+    const int64_t* table;
+    const int64_t* ent;
+    const int* miss;
+    __device__ __forceinline__ int operator()(int64_t i) const
     {
-        int f = 0;
-        if (miss[i] && ent[i] >= 0) f = table[ent[i] * 2 + 1] == kPending + i ? 1 : 0;
-        first[i] = f;
+        return (miss[i] && ent[i] >= 0 && table[ent[i] * 2 + 1] == kPending + i) ? 1 : 0;
     }
-}
+};
+// flag and exclusive rank of every position, for the kernels that need both later
+struct FlagRankOut {
+    int* first;
+    int* rank;
+    __device__ __forceinline__ void operator()(int64_t i, int item, int prefix, int64_t) const
+    {
+        first[i] = item;
+        rank[i] = prefix;
+    }
+};
 
 // last phase: every miss reads the slot its key finally got
 static __global__ void __launch_bounds__(256) phase_readback_kernel(const int64_t* __restrict__ table, int64_t n,
@@ -258,58 +256,72 @@ static MapperWs carve_mapper(void* base, int64_t N)
     return w;
 }
 
-// slot = max_index + rank for first occurrences (ids_mapper.cpp:84-98)
-static __global__ void __launch_bounds__(256) mapper_assign_kernel(recsdk_mapper_t m, const int64_t* __restrict__ keys,
-                                                                   int64_t n, const int64_t* __restrict__ ent,
-                                                                   const int* __restrict__ first,
-                                                                   const int* __restrict__ rank,
-                                                                   int64_t* __restrict__ status)
-{
-    const int64_t base = m.counters[0];
-    RECSDK_GRID_STRIDE(i, n)
+// slot = max_index + rank for first occurrences (ids_mapper.cpp:84-98), as the consumer of the scan over WonBidIn
+struct MapperAssignOut {
+    recsdk_mapper_t m;
+    const int64_t* keys;
+    const int64_t* ent;
+    int64_t* status;
+    __device__ __forceinline__ void operator()(int64_t i, int item, int prefix, int64_t) const
     {
-        if (!first[i]) continue;
-        const int64_t slot = base + rank[i];
+        if (!item) return;
+        const int64_t slot = m.counters[0] + prefix;
         if (slot >= m.init_max_index) {
             // the reference raises only with onlyDeviceMem; the HBM arrays of this
             // mapper hold init_max_index slots, so running past them is an error either way
             set_status(status, RECSDK_ERR_TABLE_FULL, m.init_max_index, keys[i]);
-            continue;
+            return;
         }
         m.table[ent[i] * 2 + 1] = slot;
         m.slot_key[slot] = keys[i];
     }
-}
+};
 
-static __global__ void mapper_bump_kernel(recsdk_mapper_t m, const int64_t* __restrict__ tmp)
-{
-    int64_t v = m.counters[0] + tmp[0];
-    m.counters[0] = v < m.init_max_index ? v : m.init_max_index;
-}
-
-// first-occurrence unique of the slots of one segment (ids_mapper.cpp:115-174)
-static __global__ void __launch_bounds__(256) uniq_bid_kernel(const int64_t* __restrict__ slots, int64_t n,
-                                                              int32_t* __restrict__ mark, int64_t max_index)
+// Last phase of the mapper: every miss reads the slot its key finally got; one thread moves max_index on by the
+// number of new keys (tmp[0], the scan's total); BID: every position also bids for its slot with its position
+// (first phase of the first-occurrence unique below).
+template <bool BID>
+static __global__ void __launch_bounds__(256) mapper_readback_kernel(recsdk_mapper_t m, int64_t n,
+                                                                     const int64_t* __restrict__ ent,
+                                                                     const int* __restrict__ miss,
+                                                                     int64_t* __restrict__ out_slots,
+                                                                     const int64_t* __restrict__ tmp)
 {
     RECSDK_GRID_STRIDE(i, n)
     {
-        const int64_t s = slots[i];
-        if (s >= 0 && s < max_index) atomicMin(mark + s, static_cast<int>(i));
+        int64_t s = 0;
+        if (miss[i]) {
+            if (ent[i] >= 0) {
+                const int64_t v = m.table[ent[i] * 2 + 1];
+                s = v < kPending ? v : 0;
+            }
+            out_slots[i] = s;
+        } else if (BID) {
+            s = out_slots[i];
+        }
+        if (BID && s >= 0 && s < m.init_max_index) atomicMin(m.mark + s, static_cast<int>(i));
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        // no position reads max_index in this kernel
+        const int64_t v = m.counters[0] + tmp[0];
+        m.counters[0] = v < m.init_max_index ? v : m.init_max_index;
     }
 }
-static __global__ void __launch_bounds__(256) uniq_first_kernel(const int64_t* __restrict__ slots, int64_t n,
-                                                                const int32_t* __restrict__ mark, int64_t max_index,
-                                                                int* __restrict__ first)
-{
-    RECSDK_GRID_STRIDE(i, n)
+
+// first-occurrence unique of the slots of one segment (ids_mapper.cpp:115-174): the positions bid for their slot in
+// mapper_readback_kernel<true>; position i is a first occurrence when it holds the mark of its slot
+struct HoldsMarkIn {
+    const int64_t* slots;
+    const int32_t* mark;
+    int64_t max_index;
+    __device__ __forceinline__ int operator()(int64_t i) const
     {
         const int64_t s = slots[i];
-        first[i] = (s >= 0 && s < max_index && mark[s] == static_cast<int>(i)) ? 1 : 0;
+        return (s >= 0 && s < max_index && mark[s] == static_cast<int>(i)) ? 1 : 0;
     }
-}
+};
 static __global__ void __launch_bounds__(256) uniq_write_kernel(const int64_t* __restrict__ slots, int64_t n,
                                                                 const int32_t* __restrict__ mark, int64_t max_index,
-                                                                const int* __restrict__ first,
                                                                 const int* __restrict__ rank,
                                                                 const int64_t* __restrict__ slot_key,
                                                                 int64_t* __restrict__ unique,
@@ -326,11 +338,12 @@ static __global__ void __launch_bounds__(256) uniq_write_kernel(const int64_t* _
             inverse[i] = 0;
             continue;
         }
-        if (first[i]) {
+        const int holder = mark[s];
+        if (holder == static_cast<int>(i)) {
             unique[base + rank[i]] = s;
             unique_ids[base + rank[i]] = slot_key[s];
         }
-        inverse[i] = rank[mark[s]];
+        inverse[i] = rank[holder];
     }
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         if (table_id == 0) unique_offset[0] = 0;
@@ -352,19 +365,20 @@ static __global__ void empty_segment_kernel(int64_t* unique_offset, int64_t tabl
     unique_offset[table_id + 1] = unique_offset[table_id];
 }
 
-// key -> slot for ids[0..n) (find or insert, first-come numbering)
+// key -> slot for ids[0..n) (find or insert, first-come numbering): find-or-claim, a scan over "won the bid" whose
+// consumer numbers the new keys, read back.  `bid_marks`: the read-back also opens the first-occurrence unique.
 static int mapper_map(const recsdk_mapper_t* m, const int64_t* ids, int64_t n, int64_t* hash_indices,
-                      int64_t* status, const MapperWs& ws, cudaStream_t st)
+                      int64_t* status, const MapperWs& ws, cudaStream_t st, bool bid_marks = false)
 {
     const int grid = grid_for(n, 256);
-    phase_lookup_kernel<0><<<grid_for(n, 256 / kProbeLanes), 256, 0, st>>>(m->table, m->hash_capacity, ids, n, hash_indices,
-                                                                           ws.ent, ws.miss, nullptr, m->counters, status);
-    phase_claim_kernel<<<grid, 256, 0, st>>>(m->table, m->hash_capacity, ids, n, ws.ent, ws.miss, status);
-    phase_first_kernel<<<grid, 256, 0, st>>>(m->table, n, ws.ent, ws.miss, ws.first);
-    device_scan<false>(ws.first, ws.rank, n, ws.scan_scratch, ws.tmp, st);
-    mapper_assign_kernel<<<grid, 256, 0, st>>>(*m, ids, n, ws.ent, ws.first, ws.rank, status);
-    mapper_bump_kernel<<<1, 1, 0, st>>>(*m, ws.tmp);
-    phase_readback_kernel<<<grid, 256, 0, st>>>(m->table, n, ws.ent, ws.miss, hash_indices);
+    phase_find_or_claim_kernel<0><<<grid_for(n, 256 / kProbeLanes), 256, 0, st>>>(
+        m->table, m->hash_capacity, ids, n, hash_indices, ws.ent, ws.miss, nullptr, m->counters, status);
+    device_scan_fn<false>(WonBidIn{m->table, ws.ent, ws.miss}, MapperAssignOut{*m, ids, ws.ent, status}, n,
+                          ws.scan_scratch, ws.tmp, st);
+    if (bid_marks)
+        mapper_readback_kernel<true><<<grid, 256, 0, st>>>(*m, n, ws.ent, ws.miss, hash_indices, ws.tmp);
+    else
+        mapper_readback_kernel<false><<<grid, 256, 0, st>>>(*m, n, ws.ent, ws.miss, hash_indices, ws.tmp);
     RECSDK_CUDA_CHECK_LAUNCH();
     return RECSDK_OK;
 }
@@ -919,15 +933,13 @@ extern "C" int recsdk_mapper_unique_out(const recsdk_mapper_t* m, const int64_t*
     if (ws.bytes > workspace_bytes) return RECSDK_ERR_WORKSPACE;
     const int64_t* seg_ids = ids + seg_start;
     int64_t* seg_hi = hash_indices + seg_start;
-    int rc = mapper_map(m, seg_ids, seg_len, seg_hi, dev_status, ws, st);
+    int rc = mapper_map(m, seg_ids, seg_len, seg_hi, dev_status, ws, st, true);
     if (rc != RECSDK_OK) return rc;
     const int grid = grid_for(seg_len, 256);
-    uniq_bid_kernel<<<grid, 256, 0, st>>>(seg_hi, seg_len, m->mark, m->init_max_index);
-    uniq_first_kernel<<<grid, 256, 0, st>>>(seg_hi, seg_len, m->mark, m->init_max_index, ws.first);
-    device_scan<false>(ws.first, ws.rank, seg_len, ws.scan_scratch, ws.tmp + 1, st);
-    uniq_write_kernel<<<grid, 256, 0, st>>>(seg_hi, seg_len, m->mark, m->init_max_index, ws.first, ws.rank, m->slot_key,
-                                            unique, unique_ids, unique_inverse + seg_start, unique_offset, table_id,
-                                            ws.tmp);
+    device_scan_fn<false>(HoldsMarkIn{seg_hi, m->mark, m->init_max_index}, FlagRankOut{ws.first, ws.rank}, seg_len,
+                          ws.scan_scratch, ws.tmp + 1, st);
+    uniq_write_kernel<<<grid, 256, 0, st>>>(seg_hi, seg_len, m->mark, m->init_max_index, ws.rank, m->slot_key, unique,
+                                            unique_ids, unique_inverse + seg_start, unique_offset, table_id, ws.tmp);
     uniq_reset_kernel<<<grid, 256, 0, st>>>(seg_hi, seg_len, m->mark, m->init_max_index);
     RECSDK_CUDA_CHECK_LAUNCH();
     return RECSDK_OK;
@@ -990,13 +1002,11 @@ extern "C" int recsdk_swap_compute(const recsdk_swap_t* s, const int64_t* keys, 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = grid_for(n > 0 ? n : 1, 256);
     if (n > 0) {
-        phase_lookup_kernel<1><<<grid_for(n, 256 / kProbeLanes), 256, 0, st>>>(s->table, s->hash_capacity, keys, n, batch_offs,
-                                                                               ws.ent, ws.miss, s->slot_version, s->counters,
-                                                                               dev_status);
-        phase_claim_kernel<<<grid, 256, 0, st>>>(s->table, s->hash_capacity, keys, n, ws.ent, ws.miss, dev_status);
-        phase_first_kernel<<<grid, 256, 0, st>>>(s->table, n, ws.ent, ws.miss, ws.first);
+        phase_find_or_claim_kernel<1><<<grid_for(n, 256 / kProbeLanes), 256, 0, st>>>(
+            s->table, s->hash_capacity, keys, n, batch_offs, ws.ent, ws.miss, s->slot_version, s->counters, dev_status);
     }
-    device_scan<false>(ws.first, ws.rank, n, ws.scan_scratch, ws.tmp, st);
+    device_scan_fn<false>(WonBidIn{s->table, ws.ent, ws.miss}, FlagRankOut{ws.first, ws.rank}, n, ws.scan_scratch, ws.tmp,
+                          st);
     swap_plan_kernel<<<1, 1, 0, st>>>(*s, ws.tmp);
     if (n > 0) {
         const int64_t span = s->cache_size - s->mem_start_offset;

@@ -85,9 +85,30 @@ static __global__ void __launch_bounds__(1024) scan_tile_sums_kernel(int* __rest
     if (threadIdx.x == 0 && total_out != nullptr) *total_out = carry;
 }
 
+// Up to this many tiles the apply kernels fold the scan of the tile sums into themselves (every block adds up the
+// raw sums of the tiles before it -- a few KB out of L2 -- and the last block publishes the grand total): one launch
+// less on the short, launch-bound scans.  Larger inputs keep the one-block scan of the sums between the two passes.
+constexpr int64_t kScanFoldTiles = 1024;
+
+// Exclusive offset of this block's tile.  `fold` == 0: tile_sums was scanned by scan_tile_sums_kernel.  Else: raw
+// sums; `own_total` is this tile's sum, `sm` 33 ints of shared memory.
+__device__ __forceinline__ int scan_tile_offset(const int* __restrict__ tile_sums, int fold, int own_total, int* sm,
+                                                int64_t* __restrict__ total_out)
+{
+    if (!fold) return tile_sums[blockIdx.x];
+    int part = 0;
+    for (int t = threadIdx.x; t < static_cast<int>(blockIdx.x); t += blockDim.x) part += tile_sums[t];
+    int before;
+    block_inclusive_scan(part, sm, &before);
+    if (total_out != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0)
+        *total_out = static_cast<int64_t>(before) + own_total;
+    return before;
+}
+
 template <bool INCLUSIVE>
 __global__ void __launch_bounds__(kScanThreads) scan_apply_kernel(const int* __restrict__ in, int* __restrict__ out,
-                                                                  int64_t n, const int* __restrict__ tile_sums)
+                                                                  int64_t n, const int* __restrict__ tile_sums,
+                                                                  int fold, int64_t* __restrict__ total_out)
 {
     __shared__ int sm[33];
     const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
@@ -100,7 +121,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_apply_kernel(const int* __r
     }
     int total;
     int inc = block_inclusive_scan(s, sm, &total);
-    int run = tile_sums[blockIdx.x] + inc - s;
+    int run = scan_tile_offset(tile_sums, fold, total, sm, total_out) + inc - s;
 #pragma unroll
     for (int k = 0; k < kScanItems; ++k) {
         if (base + k < n) out[base + k] = INCLUSIVE ? run + v[k] : run;
@@ -117,9 +138,10 @@ static inline void device_scan(const int* in, int* out, int64_t n, int* scratch,
         return;
     }
     const int64_t tiles = scan_num_tiles(n);
+    const int fold = tiles <= kScanFoldTiles ? 1 : 0;
     scan_reduce_kernel<<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, n, scratch);
-    scan_tile_sums_kernel<<<1, 1024, 0, st>>>(scratch, tiles, total_out);
-    scan_apply_kernel<INCLUSIVE><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, out, n, scratch);
+    if (!fold) scan_tile_sums_kernel<<<1, 1024, 0, st>>>(scratch, tiles, total_out);
+    scan_apply_kernel<INCLUSIVE><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, out, n, scratch, fold, total_out);
 }
 
 // Functor form of the scan: the input is computed on the fly (`in(i)` -> int) and
@@ -153,7 +175,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_reduce_fn_kernel(InFn in, i
 template <bool INCLUSIVE, typename InFn, typename OutFn>
 __global__ void __launch_bounds__(kScanThreads) scan_apply_fn_kernel(InFn in, OutFn out, int64_t n,
                                                                      const int* __restrict__ tile_sums,
-                                                                     const int64_t* __restrict__ n_dev)
+                                                                     const int64_t* __restrict__ n_dev, int fold,
+                                                                     int64_t* __restrict__ total_out)
 {
     __shared__ int sm[33];
     n = effective_n(n, n_dev);
@@ -167,7 +190,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_apply_fn_kernel(InFn in, Ou
     }
     int total;
     int inc = block_inclusive_scan(s, sm, &total);
-    int run = tile_sums[blockIdx.x] + inc - s;
+    int run = scan_tile_offset(tile_sums, fold, total, sm, total_out) + inc - s;
 #pragma unroll
     for (int k = 0; k < kScanItems; ++k) {
         if (base + k < n) out(base + k, v[k], INCLUSIVE ? run + v[k] : run, n);
@@ -184,10 +207,11 @@ static inline void device_scan_fn(InFn in, OutFn out, int64_t n, int* scratch, i
         return;
     }
     const int64_t tiles = scan_num_tiles(n);
+    const int fold = tiles <= kScanFoldTiles ? 1 : 0;
     scan_reduce_fn_kernel<InFn><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, n, scratch, n_dev);
-    scan_tile_sums_kernel<<<1, 1024, 0, st>>>(scratch, tiles, total_out);
+    if (!fold) scan_tile_sums_kernel<<<1, 1024, 0, st>>>(scratch, tiles, total_out);
     scan_apply_fn_kernel<INCLUSIVE, InFn, OutFn><<<static_cast<unsigned>(tiles), kScanThreads, 0, st>>>(in, out, n, scratch,
-                                                                                                       n_dev);
+                                                                                                       n_dev, fold, total_out);
 }
 
 // ----------------------------------------------------------------------------

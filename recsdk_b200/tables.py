@@ -50,7 +50,10 @@ class IdsMapper:
         self._slot_key = torch.empty(self.initMaxIndex, dtype=torch.int64, device=self.device)
         self._mark = torch.empty(self.initMaxIndex, dtype=torch.int32, device=self.device)
         self._counters = torch.zeros(4, dtype=torch.int64, device=self.device)
-        self._status = new_status(self.device)
+        # the status block with one more word behind it: the unique count of ids2indices_unique, so that status and
+        # count come back in ONE device-to-host read
+        self._status_and_count = torch.zeros(_lib.STATUS_WORDS + 1, dtype=torch.int64, device=self.device)
+        self._status = self._status_and_count[:_lib.STATUS_WORDS]
         self._c = _lib.MapperT(_ptr(self._table), cap, _ptr(self._slot_key), _ptr(self._mark), _ptr(self._counters),
                                self.initMaxIndex, int(self.onlyDeviceMem))
         self._ws: Optional[torch.Tensor] = None
@@ -83,14 +86,15 @@ class IdsMapper:
         hi = torch.empty(n, dtype=torch.int64, device=self.device)
         uq = torch.empty(max(n, 1), dtype=torch.int64, device=self.device)
         inv = torch.empty(max(n, 1), dtype=torch.int64, device=self.device)
-        cnt = torch.zeros(1, dtype=torch.int64, device=self.device)
+        cnt = self._status_and_count[_lib.STATUS_WORDS:]
         ws = self._workspace_for(n)
         _lib.check(self._lib.recsdk_mapper_ids2indices_unique(C.byref(self._c), _ptr(ids), n, _ptr(hi), _ptr(uq),
                                                               _ptr(inv), _ptr(cnt), _ptr(self._status), _ptr(ws),
                                                               ws.numel(), _stream()), "ids2indices_unique")
-        if check:
+        host = self._status_and_count.tolist()  # the one synchronisation of the call
+        if check and host[0] != 0:
             self.raise_if_error("ids2indices_unique")
-        u = int(cnt.item())
+        u = int(host[_lib.STATUS_WORDS])
         return hi, uq[:u], inv[:n]
 
     def ids2indices_unique_out(self, ids, hash_indices, offset, unique, unique_ids, unique_inverse, unique_offset,
