@@ -573,6 +573,12 @@ def run_dedup_multi(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t
 
+    # where the fence before the owner's plan goes: measured, the side stream wins with 4 and 8 ranks (1.15 vs 1.21 and
+    # 1.19 vs 1.32 ms), the step's own stream with 2 (1.06 vs 1.08 ms)
+    owner_plan = args.owner_plan
+    if owner_plan == "auto":
+        owner_plan = "ahead" if world > 2 else "ahead_main_fence"
+
     def measure(B, profile=False):
         """One scaling mode: B samples per rank.  Returns a dict of timings.  `profile`: a profiler started with
         --profile-from-start off sees the resident loop only (not the generation of the batches)."""
@@ -606,9 +612,13 @@ def run_dedup_multi(args):
             mark()
             bag.forward(batches[i % n_batches] if ids is None else ids, offsets, out=out)
             mark()
-            if args.owner_plan == "ahead":
-                bag.fence()  # the ids of every rank are in the owners' inboxes
-                bag.plan_owner_ahead()  # the owner phase's index work runs beside the local phase, on a side stream
+            if owner_plan == "ahead":
+                # a fence (the ids of every rank are in the owners' inboxes) and the owner phase's index work, both on
+                # the side stream, beside the local phase
+                bag.plan_owner_ahead(fence=True)
+            elif owner_plan == "ahead_main_fence":
+                bag.fence()  # the same with the fence on the stream of the step
+                bag.plan_owner_ahead()
             bag.backward_local(grad)
             if args.fwd_plan == "ahead" and next_ids is not None:
                 bag.plan_forward_ahead(next_ids(), offsets)  # beside the fences and the owner phase
@@ -773,8 +783,11 @@ def run_dedup_multi(args):
                 "exchange": "device-driven dedup exchange over peer mappings: distinct ids and counts stored into the "
                             "owners' inboxes, distinct rows loaded from the owners' tables, per-row gradient sums stored "
                             "into the owners' inboxes, counts read on the device; two one-element NCCL all-reduces per "
-                            "step as fences" + (", a third one after the forward so that the owner phase's index work runs "
-                                                "beside the local backward phase" if args.owner_plan == "ahead" else ""),
+                            "step as fences" + (", a third one after the forward, on the side stream, so that the owner phase's "
+                                                "index work runs beside the local backward phase" if owner_plan == "ahead" else
+                                               (", a third one after the forward so that the owner phase's index work runs "
+                                                "beside the local backward phase" if owner_plan == "ahead_main_fence" else "")),
+                "owner_plan": owner_plan, "fwd_plan": args.fwd_plan,
             },
             "parity_check": parity,
             "step_hbm_gbs_rank0": step_bytes / (weak["ms_step"] * 1e-3) / 1e9,
@@ -794,6 +807,7 @@ def run_dedup_multi(args):
             "phases_ms_rank0": weak["phases"],
             "phases_ms_min_max_over_ranks": {k: [min(p[k] for p in weak["phases_all"]), max(p[k] for p in weak["phases_all"])]
                                              for k in weak["phases"]},
+            "phases_ms_per_rank": [{k: round(v, 4) for k, v in p.items()} for p in weak["phases_all"]],
             "fence_ms_when_idle": weak["fence_idle_ms"],
             "strong_scaling": scal(strong, "strong: global batch 65536 split over the ranks"),
             "gpu_launches": launches_per_step * args.steps,
@@ -1526,10 +1540,12 @@ def main():
     ap.add_argument("--placement", default="count", choices=["count", "load"],
                     help="N>1: which rank owns which table.  load = balance the distinct rows per table of one profile "
                          "batch (what an owner serves and updates per step); count = equal table counts, big tables apart")
-    ap.add_argument("--owner-plan", default="ahead", choices=["ahead", "inline"],
+    ap.add_argument("--owner-plan", default="auto", choices=["auto", "ahead", "ahead_main_fence", "inline"],
                     help="N>1: where the owner phase of the exchange makes its plan (sort of the received ids, runs, "
-                         "records): ahead = on a side stream beside the local backward phase, after one more fence; "
-                         "inline = inside the owner phase")
+                         "records): ahead = on a side stream beside the local backward phase, after one more fence that "
+                         "is issued on that side stream too; ahead_main_fence = the same with the fence on the step's "
+                         "stream; inline = inside the owner phase; auto = ahead with more than two ranks, else "
+                         "ahead_main_fence")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
                     help="which BASELINE config: c2 (default, the headline: 26-table DLRM step), c1 (one small table, "

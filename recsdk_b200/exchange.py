@@ -203,6 +203,7 @@ class DedupExchange:
                 ptrs.append(opened[h] + off)
             self._set_peer(r, ptrs)
         self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._side_token = torch.zeros(1, dtype=torch.float32, device=self.device)  # fences issued on the side stream
         self._connected = True
 
     def fence(self) -> None:
@@ -301,26 +302,35 @@ class DedupExchange:
         else:
             self._owner_call(0, update_events)
 
-    def plan_owner_ahead(self) -> None:
-        """Call after a fence that follows every rank's forward: the owner phase's index work (compaction of the id
-        lists, sort, runs, records) is enqueued on a high-priority side stream, where it runs beside
-        backward_local; backward_owner then only waits for it and updates the rows."""
+    def plan_owner_ahead(self, fence: bool = False) -> None:
+        """The owner phase's index work (compaction of the id lists, sort, runs, records) on a high-priority side
+        stream, where it runs beside backward_local; backward_owner then only waits for it and updates the rows.  It
+        reads the ids every rank's forward stored into this rank's inbox, so a fence must lie between those forwards
+        and it: either the caller's (``fence()`` on the current stream before this call), or -- ``fence=True``, every
+        rank alike -- one issued here ON THE SIDE STREAM, which keeps the wait for the slowest rank's forward off the
+        stream that runs backward_local (nothing there depends on it)."""
         cur = torch.cuda.current_stream(self.device)
         if self._plan_stream is None:
             self._plan_stream = torch.cuda.Stream(device=self.device, priority=-1)
             self._plan_event = torch.cuda.Event()
         self._plan_stream.wait_stream(cur)
+        if fence and self._token is not None:
+            with torch.cuda.stream(self._plan_stream):
+                dist.all_reduce(self._side_token, group=self._group)
         self._owner_call(1, stream=self._plan_stream)  # RECSDK_XCHG_OWNER_PLAN_ONLY
         self._plan_event.record(self._plan_stream)
         self._owner_planned = True
 
     def backward(self, grad_output: torch.Tensor, update_events=None, plan_ahead: bool = False) -> None:
         """All backward steps of this rank with the fences between them (every rank calls it).  ``plan_ahead``: one
-        more fence right away (the ids of all ranks are in the inboxes) and the owner phase's index work overlaps the
-        local phase."""
+        more fence (the ids of all ranks are in the inboxes; on the side stream when there are more than two ranks)
+        and the owner phase's index work behind it overlaps the local phase."""
         if plan_ahead:
-            self.fence()
-            self.plan_owner_ahead()
+            if self.world > 2:
+                self.plan_owner_ahead(fence=True)
+            else:  # two ranks are never far apart: the fence on the step's stream measured a little faster there
+                self.fence()
+                self.plan_owner_ahead()
         self.backward_local(grad_output)
         self.fence()
         self.backward_owner(update_events)
