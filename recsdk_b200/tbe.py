@@ -411,6 +411,27 @@ class HybridSplitTableBatchedEmbeddingBagsCodegen(nn.Module):
         self._backward_impl(grad_output, indices, offsets, unique_indices, unique_offset, unique_inverse,
                             int(self.iter.item()), update_events=update_events, grad_shards=grad_shards)
 
+    def capture_step(self, indices: Tensor, offsets: Tensor, out: Tensor, grad_output: Tensor) -> "torch.cuda.CUDAGraph":
+        """forward_into + backward_from on exactly these tensors as ONE CUDA graph: a step of a small table is a dozen
+        short kernels whose launches cost more than their work, and a replay launches them at once.  The caller
+        refills ``indices`` / ``offsets`` / ``grad_output`` in place and calls ``.replay()``; ``out`` holds the pooled
+        rows after it.  Nothing is executed by the capture.
+
+        Only for optimizers whose scalars do not depend on the step number (Adagrad, SGD): a graph keeps the values
+        it was captured with, and Adam's bias correction changes every step.  Call it after at least one ordinary
+        step with tensors of these sizes (workspace and side stream exist by then, so the capture allocates nothing),
+        with no backward plan pending."""
+        if self.optimizer == EmbOptimType.ADAM:
+            raise RuntimeError("capture_step: Adam's step-dependent scalars cannot be frozen into a graph")
+        if self._ws is None or self._planned_for is not None:
+            raise RuntimeError("capture_step: run one ordinary forward_into / backward_from step with these sizes first")
+        self._ensure_workspace(indices.numel())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.forward_into(indices, offsets, out)
+            self.backward_from(grad_output, indices, offsets)
+        return graph
+
     def last_plan_counters(self) -> Tuple[int, int, int]:
         """(unique rows, chunk sums, indices that live in chunked runs) of the most recent backward (synchronises)."""
         if self._ws is None:

@@ -202,6 +202,47 @@ def test_module_plan_ahead_matches_plain_module(mode):
     assert torch.equal(mods[0].momentum2_dev, mods[1].momentum2_dev)
 
 
+@pytest.mark.parametrize("plan_ahead", [False, True])
+def test_module_step_as_cuda_graph_same_bits(plan_ahead):
+    """capture_step: forward_into + backward_from replayed as one CUDA graph, the static index buffers refilled before
+    every replay -- the same outputs, weights and accumulator, bit for bit, as the module stepped call by call."""
+    from recsdk_b200.tbe import EmbOptimType, HybridSplitTableBatchedEmbeddingBagsCodegen, PoolingMode
+
+    specs = [(1000, 16), (50, 16)]
+    B = 128
+    mods = [HybridSplitTableBatchedEmbeddingBagsCodegen(specs, optimizer=EmbOptimType.EXACT_ADAGRAD,
+                                                        pooling_mode=PoolingMode.SUM, learning_rate=0.05, device=DEV,
+                                                        initial_accumulator_value=0.1, weights_init=(-0.1, 0.1), seed=9,
+                                                        plan_ahead=plan_ahead) for _ in range(2)]
+    rng = np.random.default_rng(12)
+    offs = torch.arange(2 * B + 1, dtype=torch.int64, device=DEV)  # one id per bag
+
+    def batch():
+        idx = np.concatenate([rng.integers(0, 1000, B) % np.where(rng.random(B) < 0.3, 5, 1000), rng.integers(0, 50, B)])
+        return torch.from_numpy(idx.astype(np.int64)).to(DEV), torch.randn(B, 32, device=DEV)
+
+    outs = [torch.empty(B, 32, device=DEV) for _ in range(2)]
+    idx, g = batch()
+    for m, o in zip(mods, outs):  # one ordinary step first
+        m.forward_into(idx, offs, o)
+        m.backward_from(g, idx, offs)
+    s_idx, s_g = idx.clone(), g.clone()
+    graph = mods[1].capture_step(s_idx, offs, outs[1], s_g)
+    for _ in range(5):
+        idx, g = batch()
+        mods[0].forward_into(idx, offs, outs[0])
+        mods[0].backward_from(g, idx, offs)
+        s_idx.copy_(idx)
+        s_g.copy_(g)
+        graph.replay()
+        assert torch.equal(outs[0], outs[1])
+    assert torch.equal(mods[0].weights_dev.data, mods[1].weights_dev.data)
+    assert torch.equal(mods[0].momentum1_dev, mods[1].momentum1_dev)
+    adam = HybridSplitTableBatchedEmbeddingBagsCodegen(specs, optimizer=EmbOptimType.ADAM, device=DEV)
+    with pytest.raises(RuntimeError, match="Adam"):
+        adam.capture_step(s_idx, offs, outs[0], s_g)
+
+
 def test_registered_ops_plan_ahead_same_bits():
     """recsdk::set_plan_ahead(True): the registered lookup operators enqueue their backward's index work on a side
     stream during the forward.  Same weights, bit for bit, as with the switch off."""
