@@ -555,7 +555,8 @@ def run_dedup_multi(args):
         owner = greedy_table_placement(rows_all, [DIM] * F, world)
     bag = TableWiseDedupEmbeddingBag(rows_all, DIM, owner, world, rank, batch_size=BATCH, optimizer=EmbOptimType.ADAM,
                                      device=dev, learning_rate=LR, eps=EPS, beta1=BETA1, beta2=BETA2,
-                                     weights_init=(-0.01, 0.01), seed=SEED + rank, one_hot=True)
+                                     weights_init=(-0.01, 0.01), seed=SEED + rank, one_hot=True,
+                                     double_buffer=(args.fwd_plan == "early"))
     state_bytes = bag.local_rows * DIM * 4 * 3
     gen = torch.Generator(device=dev)
     gen.manual_seed(SEED + 17 * rank)
@@ -610,6 +611,10 @@ def run_dedup_multi(args):
                 ev_pairs.append(evs)
                 marks_all.append(marks)
             mark()
+            if timed and bag._fwd_planned is not None:
+                # what the forward would wait for anyway, timed on its own: the sort-dedup made ahead on the side stream
+                main_stream.wait_event(bag._fwd_plan_event)
+            mark()
             bag.forward(batches[i % n_batches] if ids is None else ids, offsets, out=out)
             mark()
             if owner_plan == "ahead":
@@ -619,6 +624,8 @@ def run_dedup_multi(args):
             elif owner_plan == "ahead_main_fence":
                 bag.fence()  # the same with the fence on the stream of the step
                 bag.plan_owner_ahead()
+            if args.fwd_plan == "early" and next_ids is not None:
+                bag.plan_forward_ahead(next_ids(), offsets)  # second scratch: beside the local phase already
             bag.backward_local(grad)
             if args.fwd_plan == "ahead" and next_ids is not None:
                 bag.plan_forward_ahead(next_ids(), offsets)  # beside the fences and the owner phase
@@ -650,7 +657,7 @@ def run_dedup_multi(args):
         if profile:
             torch.cuda.cudart().cudaProfilerStop()
         ms_total = t0.elapsed_time(t1)
-        names = ("forward", "backward_local", "fence", "backward_owner", "fence2")
+        names = ("wait_for_forward_plan", "forward", "backward_local", "fence", "backward_owner", "fence2")
         phases = {n: sum(m[k].elapsed_time(m[k + 1]) for m in marks_all) / len(marks_all) for k, n in enumerate(names)}
         upd_ms = sum(a.elapsed_time(b) for a, b in ev_pairs) / len(ev_pairs)
         counters = bag.counters()
@@ -1560,9 +1567,11 @@ def main():
                          "rows they need from the table owners and pool locally.  Kept as baselines: pooled rows / "
                          "gradients through NCCL all-to-alls (nccl, the reference's scheme) or stored / loaded inside "
                          "the owners' kernels over peer mappings (fused)")
-    ap.add_argument("--fwd-plan", default="ahead", choices=["ahead", "inline"],
+    ap.add_argument("--fwd-plan", default="ahead", choices=["ahead", "early", "inline"],
                     help="N>1: ahead = the sort-dedup of the next batch's ids runs on a side stream beside the owner phase "
-                         "and the fences of the current step (it touches no table); inline = inside the forward")
+                         "and the fences of the current step (it touches no table); early = the same in a second scratch, "
+                         "enqueued right after the forward, so it runs beside the local phase as well; inline = inside "
+                         "the forward")
     ap.add_argument("--placement", default="count", choices=["count", "load"],
                     help="N>1: which rank owns which table.  load = balance the distinct rows per table of one profile "
                          "batch (what an owner serves and updates per step); count = equal table counts, big tables apart")

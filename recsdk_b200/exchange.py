@@ -78,7 +78,8 @@ class DedupExchange:
                  pooling_mode: PoolingMode = PoolingMode.SUM, device="cuda", learning_rate: float = 0.01,
                  eps: float = 1e-8, beta1: float = 0.9, beta2: float = 0.999, gradient_clipping: bool = False,
                  max_gradient: float = 1.0, initial_accumulator_value: float = 0.0,
-                 weights_init: Optional[tuple] = None, seed: int = 0, one_hot: bool = False, **_ignored):
+                 weights_init: Optional[tuple] = None, seed: int = 0, one_hot: bool = False,
+                 double_buffer: bool = False, **_ignored):
         if not 1 <= world <= _lib.MAX_SHARDS:
             raise ValueError(f"1..{_lib.MAX_SHARDS} ranks supported")
         if dim <= 0 or dim % 4:
@@ -139,7 +140,11 @@ class DedupExchange:
         self.inbox_grads = torch.zeros(world * self.inbox_cap * self.dim, dtype=torch.float32, device=dev)
         lib = _lib.load()
         ws_bytes = lib.recsdk_xchg_workspace_bytes(self.max_ids, self.inbox_cap, world, self.dim, self.F)
-        self._ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        # the scratch of a step (plan, records, chunk sums, owner-side buffers).  ``double_buffer``: a second one, so
+        # that the plan of the NEXT batch (plan_forward_ahead) can be made while the current step still uses its own
+        self._wss = [torch.empty(ws_bytes, dtype=torch.uint8, device=dev) for _ in range(2 if double_buffer else 1)]
+        self._cur = 0
+        self._ws = self._wss[0]
         self._status = new_status(dev)
         self._x = _lib.XchgT()
         x = self._x
@@ -244,9 +249,10 @@ class DedupExchange:
             out = torch.empty(shape, dtype=torch.float32, device=self.device)
         flags = 0
         if self._fwd_planned is not None:
-            if self._fwd_planned != (indices.data_ptr(), N, offsets.data_ptr()):
+            if self._fwd_planned[:3] != (indices.data_ptr(), N, offsets.data_ptr()):
                 raise RuntimeError("the forward plan made ahead belongs to other indices / offsets")
             torch.cuda.current_stream(self.device).wait_event(self._fwd_plan_event)
+            self._use(self._fwd_planned[3])  # the scratch the plan was made in is this step's from here on
             self._fwd_planned = None
             flags = 2  # RECSDK_XCHG_FWD_FETCH_ONLY
         check(_lib.load().recsdk_xchg_forward(C.byref(self._x), indices.data_ptr(), offsets.data_ptr(), N, mode,
@@ -254,11 +260,17 @@ class DedupExchange:
         self._offsets, self._N = offsets, N
         return out
 
+    def _use(self, which: int) -> None:
+        self._cur = which
+        self._ws = self._wss[which]
+        self._x.workspace = self._ws.data_ptr()
+
     def plan_forward_ahead(self, indices: torch.Tensor, offsets: torch.Tensor) -> None:
         """The sort-dedup of the NEXT batch's ids on the side stream, ordered after what is enqueued on the current
-        stream so far (call it after backward_local of the current batch: the plan reuses that scratch).  It touches
-        no table and no inbox, so it runs beside the owner phase and the fences; the next forward(indices, offsets)
-        -- exactly these tensors -- then only waits for it and fetches."""
+        stream so far.  It touches no table and no inbox, so it runs beside whatever the current step still has to do;
+        the next forward(indices, offsets) -- exactly these tensors -- then only waits for it and fetches.  Without
+        ``double_buffer`` the plan reuses the current step's scratch: call it after backward_local of the current
+        batch.  With it the plan goes to the other scratch and may be made any time after the current forward."""
         if not self._connected:
             raise RuntimeError("connect_processes / connect_local first")
         cur = torch.cuda.current_stream(self.device)
@@ -270,11 +282,18 @@ class DedupExchange:
         self._plan_stream.wait_stream(cur)
         indices.record_stream(self._plan_stream)
         offsets.record_stream(self._plan_stream)
-        check(_lib.load().recsdk_xchg_forward(C.byref(self._x), indices.data_ptr(), offsets.data_ptr(), indices.numel(),
-                                              int(self.pooling_mode), None, 1, self._plan_stream.cuda_stream),
-              "recsdk_xchg_forward")  # RECSDK_XCHG_FWD_PLAN_ONLY
+        mine = self._cur
+        target = (mine + 1) % len(self._wss)
+        self._use(target)
+        try:
+            check(_lib.load().recsdk_xchg_forward(C.byref(self._x), indices.data_ptr(), offsets.data_ptr(),
+                                                  indices.numel(), int(self.pooling_mode), None, 1,
+                                                  self._plan_stream.cuda_stream),
+                  "recsdk_xchg_forward")  # RECSDK_XCHG_FWD_PLAN_ONLY
+        finally:
+            self._use(mine)  # the rest of the current step goes on in its own scratch
         self._fwd_plan_event.record(self._plan_stream)
-        self._fwd_planned = (indices.data_ptr(), indices.numel(), offsets.data_ptr())
+        self._fwd_planned = (indices.data_ptr(), indices.numel(), offsets.data_ptr(), target)
 
     def backward_local(self, grad_output: torch.Tensor) -> None:
         check(_lib.load().recsdk_xchg_backward_local(C.byref(self._x), grad_output.data_ptr(), self._offsets.data_ptr(),

@@ -49,7 +49,8 @@ def _batches(rng, rows, world, B, max_len, hot=7, one_hot=False):
     return out
 
 
-def _run_and_compare(ranks, orc, batches, grads, B, mode, steps=2, plan_ahead=False, fwd_plan_ahead=False):
+def _run_and_compare(ranks, orc, batches, grads, B, mode, steps=2, plan_ahead=False, fwd_plan_ahead=False,
+                     fwd_plan_early=False):
     world = len(ranks)
     dev_b = [(torch.from_numpy(i).to(DEV), torch.from_numpy(o).to(DEV)) for i, o in batches]
     dev_g = [torch.from_numpy(g).to(DEV) for g in grads]
@@ -59,6 +60,9 @@ def _run_and_compare(ranks, orc, batches, grads, B, mode, steps=2, plan_ahead=Fa
         if plan_ahead:  # every rank's ids are in the inboxes: the owners' index work goes to their side streams
             for q in range(world):
                 ranks[q].plan_owner_ahead()
+        if fwd_plan_early and step_no + 1 < steps:  # double-buffered scratch: the next plan beside the local phase already
+            for q in range(world):
+                ranks[q].plan_forward_ahead(*dev_b[q])
         for q in range(world):
             ranks[q].backward_local(dev_g[q])
         if fwd_plan_ahead and step_no + 1 < steps:  # the next step's sort-dedup, beside this step's owner phase
@@ -165,6 +169,12 @@ def test_exchange_forward_plan_ahead_bit_exact(mode):
     batches = _batches(rng, ROWS, world, B, 3)
     grads = [rng.standard_normal((b[0].size, D) if mode == 2 else (B, F * D)).astype(np.float32) for b in batches]
     _run_and_compare(ranks, orc, batches, grads, B, mode, steps=3, plan_ahead=True, fwd_plan_ahead=True)
+    # the same with a second scratch per rank: the next plan is made right after the forward, beside the local phase
+    ranks2 = _make_ranks(ROWS, D, world, "row", None, B, F * B * 3, 2, mode, inbox_cap=F * B * 3, double_buffer=True)
+    orc2 = port.ShardedDedupOracle(ROWS, D, world, "row", optimizer=2, lr=0.05)
+    rng2 = np.random.default_rng(33)
+    _load(ranks2, orc2, [rng2.uniform(-0.1, 0.1, (r, D)).astype(np.float32) for r in ROWS])
+    _run_and_compare(ranks2, orc2, batches, grads, B, mode, steps=4, plan_ahead=True, fwd_plan_early=True)
     idx, offs = (torch.from_numpy(a).to(DEV) for a in batches[0])
     ranks[0].plan_forward_ahead(idx, offs)
     with pytest.raises(RuntimeError, match="other indices"):
