@@ -302,7 +302,7 @@ static __global__ void __launch_bounds__(256) sort_scan_kernel(uint32_t* __restr
 }
 
 template <typename KeyT, int BITS>
-__global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* __restrict__ keys_in,
+__global__ void __launch_bounds__(kSortThreads, 3) sort_scatter_kernel(const KeyT* __restrict__ keys_in,
                                                                     const uint32_t* __restrict__ vals_in,
                                                                     KeyT* __restrict__ keys_out,
                                                                     uint32_t* __restrict__ vals_out, int64_t n,
@@ -325,11 +325,26 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
     const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * kSortTile + warp * (kSortRounds * 32);
     KeyT key[kSortRounds];
     uint32_t rank[kSortRounds];
+    // everything the block reads from global memory is requested up front, in one wave: its keys, its values, the
+    // digit totals and its own row of the scanned histogram (none of these depends on the ranking below)
+    uint32_t val[kSortRounds];
+#pragma unroll
+    for (int r = 0; r < kSortRounds; ++r) {
+        const int64_t i = tile0 + r * 32 + lane;
+        key[r] = i < n ? keys_in[i] : KeyT(0);
+        val[r] = i < n ? vals_in[i] : 0u;
+    }
+    int tot[PER];
+    uint32_t mine_hist[PER];
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+        tot[q] = static_cast<int>(totals[threadIdx.x * PER + q]);
+        mine_hist[q] = hist[static_cast<int64_t>(threadIdx.x * PER + q) * tiles + blockIdx.x];
+    }
 #pragma unroll
     for (int r = 0; r < kSortRounds; ++r) {
         const int64_t i = tile0 + r * 32 + lane;
         const bool valid = i < n;
-        key[r] = valid ? keys_in[i] : KeyT(0);
         // invalid lanes get a tag no valid lane can have, so they match nobody valid
         const unsigned tag = valid ? static_cast<unsigned>((key[r] >> shift) & (RADIX - 1)) : (RADIX + lane);
         const unsigned peers = __match_any_sync(kFullMask, tag);
@@ -346,20 +361,16 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
     // digit base for this tile: exclusive scan of digit totals + this tile's prefix inside the digit;
     // thread t owns the PER consecutive digits [t*PER, t*PER+PER)
     {
-        int tot[PER];
         int mine = 0;
 #pragma unroll
-        for (int q = 0; q < PER; ++q) {
-            tot[q] = static_cast<int>(totals[threadIdx.x * PER + q]);
-            mine += tot[q];
-        }
+        for (int q = 0; q < PER; ++q) mine += tot[q];
         int total_all;
         const int inc = block_inclusive_scan(mine, sm, &total_all);
         uint32_t digit_base = static_cast<uint32_t>(inc - mine);
 #pragma unroll
         for (int q = 0; q < PER; ++q) {
             const int d = threadIdx.x * PER + q;
-            uint32_t run = digit_base + hist[static_cast<int64_t>(d) * tiles + blockIdx.x];
+            uint32_t run = digit_base + mine_hist[q];
 #pragma unroll
             for (int w = 0; w < kSortThreads / 32; ++w) {
                 const uint32_t c = warp_cnt[w][d];
@@ -379,7 +390,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const KeyT* 
             const unsigned d = static_cast<unsigned>((key[r] >> shift) & (RADIX - 1));
             pos = warp_cnt[warp][d] + rank[r];
             keys_out[pos] = key[r];
-            vals_out[pos] = vals_in[i];
+            vals_out[pos] = val[r];
         }
         next.add_warp(i < n, key[r], static_cast<int64_t>(pos));
     }
