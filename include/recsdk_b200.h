@@ -535,7 +535,9 @@ RECSDK_API size_t recsdk_xchg_workspace_bytes(int64_t max_ids, int64_t inbox_cap
  * the ids and this rank's scratch, so the plan of step k+1 can run on a second stream beside the owner phase of step k
  * and BEFORE the fence that makes the tables final, once this rank's recsdk_xchg_backward_local of step k is done with
  * the scratch; the fetch call (same arguments; counts and ids to the owners' inboxes, rows from the owners' tables,
- * output) follows that fence and an event wait on the plan.  `out` may be NULL in the plan call. */
+ * output) follows that fence and an event wait on the plan.  `out` may be NULL in the plan call.  A caller that gives
+ * the steps two workspaces in turn (x->workspace is read at every call) may make the plan of step k+1 in the other one
+ * at any time after the forward of step k.  The fetch may be repeated on the plan it belongs to. */
 #define RECSDK_XCHG_FWD_PLAN_ONLY 1
 #define RECSDK_XCHG_FWD_FETCH_ONLY 2
 RECSDK_API int recsdk_xchg_forward(const recsdk_xchg_t* x, const int64_t* indices, const int64_t* offsets, int64_t N,
