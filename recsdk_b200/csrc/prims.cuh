@@ -302,7 +302,7 @@ static __global__ void __launch_bounds__(256) sort_scan_kernel(uint32_t* __restr
 }
 
 template <typename KeyT, int BITS>
-__global__ void __launch_bounds__(kSortThreads, 3) sort_scatter_kernel(const KeyT* __restrict__ keys_in,
+__global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(const KeyT* __restrict__ keys_in,
                                                                     const uint32_t* __restrict__ vals_in,
                                                                     KeyT* __restrict__ keys_out,
                                                                     uint32_t* __restrict__ vals_out, int64_t n,
