@@ -119,8 +119,8 @@ template <int G, int K>
 static void launch_partial(const BwdParams& p, int64_t N, cudaStream_t st)
 {
     const int groups_per_block = 256 / G;
-    // one resident wave (80 registers: 3 blocks per SM)
-    const int grid = grid_for(static_cast<int64_t>(chunk_slots_cap(N)), groups_per_block, 3);
+    // one resident wave (64 registers under the launch bounds: 4 blocks per SM)
+    const int grid = grid_for(static_cast<int64_t>(chunk_slots_cap(N)), groups_per_block, 4);
     partial_kernel<G, K><<<grid, 256, 0, st>>>(p);
 }
 

@@ -368,7 +368,7 @@ __device__ __forceinline__ unsigned group_mask();
 // lanes resolve G gradient tags at a time to addresses in parallel, then the group
 // walks them in order with several independent 128-bit loads in flight.
 template <int G, int K>
-__global__ void __launch_bounds__(256) partial_kernel(BwdParams p)
+__global__ void __launch_bounds__(256, 4) partial_kernel(BwdParams p)
 {
     const int groups_per_block = blockDim.x / G;
     const int lane = threadIdx.x % G;
