@@ -702,7 +702,7 @@ static int xchg_forward_impl(const recsdk_xchg_t* x, const XchgWorkspace& ws, co
 template <int G, int K>
 static void xchg_launch_partial(const BwdParams& p, int64_t n, cudaStream_t st)
 {
-    partial_kernel<G, K><<<grid_for(static_cast<int64_t>(chunk_slots_cap(n)), 256 / G, 3), 256, 0, st>>>(p);
+    partial_kernel<G, K><<<grid_for(static_cast<int64_t>(chunk_slots_cap(n)), 256 / G, 4), 256, 0, st>>>(p);
 }
 
 template <int G, int K>
