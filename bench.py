@@ -915,7 +915,7 @@ def run_tbe_config(args, name):
         o.backward(grad)
         result_host.copy_(o.detach().reshape(-1)[:result_host.numel()], non_blocking=True)
 
-    e2e_ms, issue_ms = _time_loop(torch, step_e2e, args.steps, max(args.warmup, 3))
+    e2e_ms, issue_ms = _time_loop(torch, step_e2e, args.steps, max(args.warmup, 3, args.steps))  # pool warm, see run_ours
     without_graph = None
     if name == "c1":
         # the step is a dozen kernels of a few microseconds: replayed as ONE CUDA graph (static index / offset buffers
